@@ -1,0 +1,195 @@
+"""ctypes front end of the CPU oracle (oracle/fused_oracle.c).
+
+TEST INFRASTRUCTURE ONLY.  The shipped package never imports this module; the
+tests, the smoke check and the benchmark's CPU legs do.  It takes and returns
+numpy arrays so that it has no dependency on the package under test.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_build", "libta_oracle.so")
+_lib = None
+
+CONTRAST_FAST = 0
+CONTRAST_MEAN = 1
+
+
+class _Params(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_int32),
+        ("n", C.c_int32), ("c", C.c_int32), ("h", C.c_int32), ("w", C.c_int32),
+        ("oh", C.c_int32), ("ow", C.c_int32),
+        ("inp", C.c_void_p), ("out", C.c_void_p),
+        ("top", C.c_void_p), ("left", C.c_void_p), ("flip", C.c_void_p),
+        ("matrix", C.c_void_p),
+        ("fill", C.c_float), ("interp", C.c_int32),
+        ("apply_brightness", C.c_int32), ("apply_contrast", C.c_int32),
+        ("apply_saturation", C.c_int32), ("apply_grayscale", C.c_int32),
+        ("apply_normalize", C.c_int32),
+        ("brightness", C.c_void_p), ("contrast", C.c_void_p), ("saturation", C.c_void_p),
+        ("gray", C.c_void_p), ("mean", C.c_void_p), ("std", C.c_void_p),
+        ("fma_coords", C.c_int32), ("contrast_mode", C.c_int32),
+        ("gray_mean", C.c_void_p), ("src_index", C.c_void_p),
+        ("threads", C.c_int32),
+    ]
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile next to it (gcc only)."""
+    src = os.path.join(_HERE, "fused_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        env = dict(os.environ)
+        env.pop("CC", None)
+        subprocess.run(["make", "-C", _HERE, "CC=gcc"], check=True, env=env,
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    return _LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.ta_oracle_fused_augment.argtypes = [C.POINTER(_Params)]
+        _lib.ta_oracle_fused_augment.restype = C.c_int
+        _lib.ta_oracle_gray_mean.argtypes = [C.POINTER(_Params), C.c_void_p]
+        _lib.ta_oracle_gray_mean.restype = C.c_int
+        _lib.ta_oracle_inverse_affine_matrix.argtypes = [C.c_int] + [C.c_void_p] * 6
+        _lib.ta_oracle_inverse_affine_matrix.restype = None
+        _lib.ta_oracle_max_threads.restype = C.c_int
+    return _lib
+
+
+def max_threads() -> int:
+    return int(lib().ta_oracle_max_threads())
+
+
+def _vec(x, n, dtype):
+    a = np.asarray(x)
+    if a.ndim == 0:
+        a = np.full((n,), a)
+    a = np.ascontiguousarray(a.astype(dtype, copy=False))
+    if a.shape != (n,):
+        raise ValueError(f"expected shape ({n},), got {a.shape}")
+    return a
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _prepare(image, top, left, height, width, flip, matrix, interpolation, fill, brightness,
+             contrast, saturation, grayscale, mean, std, flags, fma_coords, contrast_mode,
+             gray_mean, want_index, threads):
+    image = np.ascontiguousarray(image)
+    if image.dtype not in (np.float32, np.float16):
+        raise TypeError("image must be float32 or float16")
+    n, c, h, w = image.shape
+    dt = image.dtype
+    keep = {}
+    keep["image"] = image
+    keep["top"] = _vec(top, n, np.float32)
+    keep["left"] = _vec(left, n, np.float32)
+    keep["flip"] = _vec(flip, n, np.uint8)
+    keep["matrix"] = None if matrix is None else np.ascontiguousarray(np.asarray(matrix, np.float32).reshape(n, 6))
+    keep["b"] = _vec(brightness, n, dt)
+    keep["c"] = _vec(contrast, n, dt)
+    keep["s"] = _vec(saturation, n, dt)
+    keep["g"] = _vec(grayscale, n, np.uint8)
+    apply_norm = mean is not None and std is not None
+    keep["mean"] = np.asarray(mean if apply_norm else (0, 0, 0), dtype=dt)
+    keep["std"] = np.asarray(std if apply_norm else (1, 1, 1), dtype=dt)
+    if flags is None:
+        # Same value-based decisions as triton_augment/functional.py:1341-1344, 1356.
+        flags = dict(brightness=bool(np.any(keep["b"] != 1)), contrast=bool(np.any(keep["c"] != 1)),
+                     saturation=bool(np.any(keep["s"] != 1)), grayscale=bool(np.any(keep["g"])))
+    keep["out"] = np.empty((n, c, height, width), dtype=dt)
+    keep["gm"] = None if gray_mean is None else _vec(gray_mean, n, np.float32)
+    keep["idx"] = np.empty((n, height, width), dtype=np.int32) if want_index else None
+    p = _Params()
+    p.dtype = 1 if dt == np.float16 else 0
+    p.n, p.c, p.h, p.w, p.oh, p.ow = n, c, h, w, height, width
+    p.inp, p.out = _ptr(image), _ptr(keep["out"])
+    p.top, p.left, p.flip = _ptr(keep["top"]), _ptr(keep["left"]), _ptr(keep["flip"])
+    p.matrix = _ptr(keep["matrix"])
+    p.fill = float(fill)
+    p.interp = 1 if str(interpolation).lower() == "bilinear" else 0
+    p.apply_brightness = int(flags["brightness"])
+    p.apply_contrast = int(flags["contrast"])
+    p.apply_saturation = int(flags["saturation"])
+    p.apply_grayscale = int(flags["grayscale"])
+    p.apply_normalize = int(apply_norm)
+    p.brightness, p.contrast, p.saturation = _ptr(keep["b"]), _ptr(keep["c"]), _ptr(keep["s"])
+    p.gray, p.mean, p.std = _ptr(keep["g"]), _ptr(keep["mean"]), _ptr(keep["std"])
+    p.fma_coords = int(fma_coords)
+    p.contrast_mode = int(contrast_mode)
+    p.gray_mean = _ptr(keep["gm"])
+    p.src_index = _ptr(keep["idx"])
+    p.threads = int(threads)
+    return p, keep
+
+
+def fused_augment(image, top, left, height, width, flip=0, matrix=None, interpolation="nearest",
+                  fill=0.0, brightness=1.0, contrast=1.0, saturation=1.0, grayscale=0,
+                  mean=None, std=None, *, flags=None, fma_coords=True,
+                  contrast_mode=CONTRAST_FAST, gray_mean=None, want_index=False, threads=0):
+    """The reference's fused pass on the CPU.
+
+    Arguments follow the kernel launch at triton_augment/functional.py:1399-1431:
+    per-image vectors (or scalars, broadcast) and an already-built inverse
+    affine matrix ``[n, 6]`` (``None`` means the crop/flip-only path).  ``flags``
+    overrides the value-based apply_* decisions with a dict of four booleans.
+    Returns the output array, or ``(output, src_index)`` with ``want_index``.
+    """
+    p, keep = _prepare(image, top, left, height, width, flip, matrix, interpolation, fill,
+                       brightness, contrast, saturation, grayscale, mean, std, flags,
+                       fma_coords, contrast_mode, gray_mean, want_index, threads)
+    if contrast_mode == CONTRAST_MEAN and p.apply_contrast and gray_mean is None:
+        gm = np.empty((p.n,), np.float32)
+        rc = lib().ta_oracle_gray_mean(C.byref(p), _ptr(gm))
+        if rc != 0:
+            raise RuntimeError(f"ta_oracle_gray_mean failed: {rc}")
+        keep["gm"] = gm
+        p.gray_mean = _ptr(gm)
+    rc = lib().ta_oracle_fused_augment(C.byref(p))
+    if rc != 0:
+        raise RuntimeError(f"ta_oracle_fused_augment failed: {rc}")
+    return (keep["out"], keep["idx"]) if want_index else keep["out"]
+
+
+def gray_mean(image, top, left, height, width, flip=0, matrix=None, interpolation="nearest",
+              fill=0.0, brightness=1.0, *, apply_brightness=None, fma_coords=True):
+    """Per-image grayscale mean of the geometry+brightness result (exact contrast)."""
+    n = np.asarray(image).shape[0]
+    b = _vec(brightness, n, np.asarray(image).dtype)
+    flags = dict(brightness=bool(np.any(b != 1)) if apply_brightness is None else bool(apply_brightness),
+                 contrast=False, saturation=False, grayscale=False)
+    p, keep = _prepare(image, top, left, height, width, flip, matrix, interpolation, fill,
+                       brightness, 1.0, 1.0, 0, None, None, flags, fma_coords, CONTRAST_FAST,
+                       None, False, 0)
+    gm = np.empty((p.n,), np.float32)
+    rc = lib().ta_oracle_gray_mean(C.byref(p), _ptr(gm))
+    if rc != 0:
+        raise RuntimeError(f"ta_oracle_gray_mean failed: {rc}")
+    return gm
+
+
+def inverse_affine_matrix(center, angle, translate, scale, shear):
+    """fp32/libm evaluation of triton_augment/functional.py:824-892; returns [n, 6]."""
+    angle = np.ascontiguousarray(angle, np.float32)
+    n = angle.shape[0]
+    center = np.ascontiguousarray(center, np.float32).reshape(n, 2)
+    translate = np.ascontiguousarray(translate, np.float32).reshape(n, 2)
+    scale = np.ascontiguousarray(scale, np.float32).reshape(n)
+    shear = np.ascontiguousarray(shear, np.float32).reshape(n, 2)
+    out = np.empty((n, 6), np.float32)
+    lib().ta_oracle_inverse_affine_matrix(n, _ptr(center), _ptr(angle), _ptr(translate), _ptr(scale),
+                                          _ptr(shear), _ptr(out))
+    return out
