@@ -1,0 +1,178 @@
+/*
+ * ta_b200.h - C ABI of the B200 (sm_100a) fused image-augmentation library.
+ *
+ * The reference project (yuhezhang-ai/triton-augment v0.3.0) has no FFI layer:
+ * its seam is a Python call that launches a Triton kernel.  This header is the
+ * same seam as a C ABI.  Each entry point names the reference interface it
+ * replaces (paths relative to the reference project's root).
+ *
+ * Conventions
+ *   - Every function returns TA_B200_OK (0) or a negative ta_b200_status.  Nothing
+ *     throws, exits, or synchronises the device unless the comment says so.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *     Work is enqueued on it and the call returns immediately.
+ *   - The caller owns every buffer.  Images are contiguous NCHW.  Device pointers
+ *     must belong to the device that is current when the call is made.
+ *   - Calls may be made concurrently from several host threads as long as their
+ *     output buffers do not overlap.
+ */
+#ifndef TA_B200_H
+#define TA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TA_B200_ABI_VERSION 1
+
+typedef enum ta_b200_status {
+    TA_B200_OK = 0,
+    TA_B200_ERR_NULL = -1,         /* a required pointer is NULL */
+    TA_B200_ERR_SHAPE = -2,        /* sizes not positive, or channels not in {1, 3} */
+    TA_B200_ERR_DTYPE = -3,        /* dtype not TA_B200_F32 / TA_B200_F16 */
+    TA_B200_ERR_UNSUPPORTED = -4,  /* e.g. saturation/grayscale on 1-channel images */
+    TA_B200_ERR_CUDA = -5,         /* a CUDA runtime call failed; see ta_b200_last_error() */
+    TA_B200_ERR_SCRATCH = -6,      /* scratch buffer missing or too small */
+    TA_B200_ERR_DEVICE = -7,       /* current device is not compute capability 10.x */
+    TA_B200_ERR_TOO_LARGE = -8     /* a size exceeds what the entry point supports */
+} ta_b200_status;
+
+enum { TA_B200_F32 = 0, TA_B200_F16 = 1 };
+enum { TA_B200_NEAREST = 0, TA_B200_BILINEAR = 1 };
+enum { TA_B200_CONTRAST_FAST = 0, TA_B200_CONTRAST_MEAN = 1 };
+
+/* Which colour operations are compiled in.  The reference derives these from the
+ * parameter VALUES (triton_augment/functional.py:1341-1344, 1356): an operation
+ * is skipped only when its factor is exactly 1.0 for every image (mask all-false,
+ * mean/std None).  An enabled operation clamps to [0, 1] even for images whose
+ * factor is 1.0, so the caller must make the same decision to get the same
+ * output for pixels outside [0, 1]. */
+enum {
+    TA_B200_APPLY_BRIGHTNESS = 1u << 0,
+    TA_B200_APPLY_CONTRAST   = 1u << 1,
+    TA_B200_APPLY_SATURATION = 1u << 2,
+    TA_B200_APPLY_GRAYSCALE  = 1u << 3,
+    TA_B200_APPLY_NORMALIZE  = 1u << 4
+};
+
+/*
+ * Arguments of one fused pass.  Field for field this is the 27-argument kernel
+ * launch at triton_augment/functional.py:1399-1431 (kernel signature
+ * triton_augment/kernels/fused_kernel.py:60-98); mean/std travel by value
+ * instead of as 3-element device tensors.
+ */
+typedef struct ta_b200_fused_params {
+    uint32_t struct_size;     /* sizeof(ta_b200_fused_params), for ABI checking */
+    int32_t  dtype;           /* TA_B200_F32 / TA_B200_F16: type of in, out and the factor vectors */
+    int32_t  n, c, h, w;      /* input  [n, c, h, w]; c in {1, 3} */
+    int32_t  oh, ow;          /* output [n, c, oh, ow] (the crop size) */
+    const void *in;
+    void       *out;
+    const float   *top;       /* [n] crop offsets held as fp32, NULL = 0 */
+    const float   *left;      /* [n], NULL = 0 */
+    const uint8_t *flip;      /* [n] 0/1, NULL = no flip */
+    const float   *matrix;    /* [n, 6] inverse affine rows (a b c d e f), NULL = crop/flip only
+                                 (has_affine=False in the reference) */
+    float    fill;            /* value of texels outside the image (affine only) */
+    int32_t  interp;          /* TA_B200_NEAREST / TA_B200_BILINEAR (affine only) */
+    uint32_t apply;           /* TA_B200_APPLY_* bits */
+    const void    *brightness; /* [n] image dtype; may be NULL when its bit is clear */
+    const void    *contrast;   /* [n] */
+    const void    *saturation; /* [n] */
+    const uint8_t *gray;       /* [n] 0/1 */
+    float    mean[3];         /* already rounded to the image dtype by the caller */
+    float    std[3];          /* (triton_augment/functional.py:1350-1351) */
+    int32_t  contrast_mode;   /* FAST: (x-0.5)*f+0.5, the reference's fused behaviour
+                                 (fused_kernel.py:245-250).  MEAN: x*f+mean_n*(1-f), the
+                                 torchvision-exact formula of its stand-alone contrast kernel
+                                 (kernels/color_normalize_kernel.py:37-77); needs gray_mean. */
+    const float   *gray_mean; /* [n] per-image means written by ta_b200_gray_mean() */
+} ta_b200_fused_params;
+
+/* ABI version of the loaded library (TA_B200_ABI_VERSION it was built with). */
+int ta_b200_abi_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *ta_b200_last_error(void);
+
+/*
+ * The fused pass on device buffers: inverse-affine / crop / flip gather with
+ * nearest or bilinear sampling, then brightness, contrast, saturation,
+ * per-image grayscale and normalize, one read of the source footprint and one
+ * write of the output.
+ * Replaces: the launch of fused_augment_kernel, triton_augment/functional.py:1399-1431
+ * (kernel: triton_augment/kernels/fused_kernel.py:55-376 with the helpers of
+ * triton_augment/kernels/geometric_kernel.py:178-283, 349-420).  With no-op arguments
+ * it also replaces the stand-alone kernels launched at functional.py:254, 318, 462,
+ * 530, 591, 675, 809 and 960.
+ */
+int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream);
+
+/*
+ * Per-image mean of the grayscale of the image that contrast would see in a
+ * sequential pipeline: geometry (as described by *p) followed by brightness (if
+ * its bit is set).  Writes mean_out[n] (device, fp32 holding image-dtype-rounded
+ * values).  `scratch` is device memory of at least ta_b200_gray_mean_scratch_bytes(p)
+ * bytes, 256-byte aligned; it needs no initialisation and may be reused by the next
+ * call on the same stream.
+ * Replaces: rgb_to_grayscale + torch.mean + cast, triton_augment/functional.py:366-376.
+ */
+int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out,
+                      void *scratch, size_t scratch_bytes, void *stream);
+size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p);
+
+/*
+ * Host-buffer variant of ta_b200_fused_augment(): p->in and p->out are HOST
+ * pointers (pinned memory gives full PCIe speed); every per-image vector and the
+ * matrix are host pointers too.  The batch is cut into slices that flow through
+ * upload -> kernel -> download on three streams, so copies overlap the kernel.
+ * Device staging buffers are allocated on first use and cached per device.
+ * Synchronous: returns when p->out is complete.
+ * Replaces: the host-tensor path of the transform classes, which upload with
+ * .cuda() before calling the kernel (triton_augment/transforms.py:1498-1504).
+ */
+int ta_b200_fused_augment_host(const ta_b200_fused_params *p);
+
+/*
+ * Inverse affine matrices on the device in one launch: angle[n], translate[n,2],
+ * scale[n], shear[n,2] (degrees / pixels, device fp32; center may be NULL = image
+ * centre) -> matrix[n,6].  Same operation order as
+ * triton_augment/functional.py:853-890 (_get_inverse_affine_matrix).
+ */
+int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *angle,
+                                  const float *translate, const float *scale,
+                                  const float *shear, float *matrix, void *stream);
+
+/*
+ * Diagnostics.  ta_b200_debug_counters copies {tiles staged through shared memory,
+ * tiles that took the direct-gather path, staging violations seen by a checked
+ * build, barrier waits that ran out} accumulated on the current device since the
+ * last reset into out[4] (synchronises the device).
+ */
+int ta_b200_debug_counters(uint64_t out[4], int reset);
+
+/* ta_b200_fused_augment() with assertions on every shared-memory tap compiled in
+ * (affine only, p->apply must be 0); violations show up in ta_b200_debug_counters()[2]. */
+int ta_b200_debug_fused_checked(const ta_b200_fused_params *p, void *stream);
+
+/*
+ * Host-only helper for tests: the source rows and per-row column ranges that the
+ * staged affine kernel would fetch for one output tile.  Returns the number of rows
+ * (0 if the tile would not be staged), writes the first row to *row0 and per-row
+ * [xs, xe) to xs[]/xe[] (capacity `cap` rows).
+ */
+int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, int32_t w,
+                                 int32_t oh, int32_t ow, float top, float left, int32_t flip,
+                                 const float matrix[6], int32_t tile_x, int32_t tile_y,
+                                 int32_t *row0, int32_t *xs, int32_t *xe, int32_t cap);
+/* Tile shape of the staged affine kernel: out[0] = width, out[1] = height,
+ * out[2] = row capacity, out[3] = row pitch in elements. */
+void ta_b200_debug_tile_shape(int32_t out[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TA_B200_H */

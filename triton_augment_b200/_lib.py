@@ -1,0 +1,167 @@
+"""ctypes binding of libta_b200.so (C ABI in include/ta_b200.h).
+
+There is no fallback: if the library is missing or the device is not a B200-class
+GPU the call raises.  Pointers handed to the library are raw ``data_ptr()`` values
+and the stream is torch's current stream on the tensor's device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libta_b200.so")
+
+ABI_VERSION = 1
+F32, F16 = 0, 1
+NEAREST, BILINEAR = 0, 1
+CONTRAST_FAST, CONTRAST_MEAN = 0, 1
+APPLY_BRIGHTNESS, APPLY_CONTRAST, APPLY_SATURATION, APPLY_GRAYSCALE, APPLY_NORMALIZE = 1, 2, 4, 8, 16
+
+# Every symbol include/ta_b200.h declares.
+SYMBOLS = (
+    "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
+    "ta_b200_gray_mean_scratch_bytes", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
+    "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
+    "ta_b200_debug_tile_shape",
+)
+
+
+class FusedParams(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32),
+        ("n", C.c_int32), ("c", C.c_int32), ("h", C.c_int32), ("w", C.c_int32),
+        ("oh", C.c_int32), ("ow", C.c_int32),
+        ("inp", C.c_void_p), ("out", C.c_void_p),
+        ("top", C.c_void_p), ("left", C.c_void_p), ("flip", C.c_void_p), ("matrix", C.c_void_p),
+        ("fill", C.c_float), ("interp", C.c_int32), ("apply", C.c_uint32),
+        ("brightness", C.c_void_p), ("contrast", C.c_void_p), ("saturation", C.c_void_p), ("gray", C.c_void_p),
+        ("mean", C.c_float * 3), ("std", C.c_float * 3),
+        ("contrast_mode", C.c_int32), ("gray_mean", C.c_void_p),
+    ]
+
+
+class LibraryError(RuntimeError):
+    """A call into libta_b200.so returned a negative status."""
+
+
+_lib = None
+
+
+def load():
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m triton_augment_b200.build` "
+            "(needs nvcc; the library targets sm_100a and has no CPU or other-GPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    lib.ta_b200_abi_version.restype = C.c_int
+    lib.ta_b200_last_error.restype = C.c_char_p
+    lib.ta_b200_fused_augment.argtypes = [C.POINTER(FusedParams), C.c_void_p]
+    lib.ta_b200_fused_augment.restype = C.c_int
+    lib.ta_b200_debug_fused_checked.argtypes = [C.POINTER(FusedParams), C.c_void_p]
+    lib.ta_b200_debug_fused_checked.restype = C.c_int
+    lib.ta_b200_gray_mean.argtypes = [C.POINTER(FusedParams), C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ta_b200_gray_mean.restype = C.c_int
+    lib.ta_b200_gray_mean_scratch_bytes.argtypes = [C.POINTER(FusedParams)]
+    lib.ta_b200_gray_mean_scratch_bytes.restype = C.c_size_t
+    lib.ta_b200_fused_augment_host.argtypes = [C.POINTER(FusedParams)]
+    lib.ta_b200_fused_augment_host.restype = C.c_int
+    lib.ta_b200_inverse_affine_matrix.argtypes = [C.c_int32] + [C.c_void_p] * 7
+    lib.ta_b200_inverse_affine_matrix.restype = C.c_int
+    lib.ta_b200_debug_counters.argtypes = [C.POINTER(C.c_uint64), C.c_int]
+    lib.ta_b200_debug_counters.restype = C.c_int
+    lib.ta_b200_debug_tile_footprint.argtypes = (
+        [C.c_int32] * 6 + [C.c_float, C.c_float, C.c_int32, C.POINTER(C.c_float), C.c_int32, C.c_int32,
+                           C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int32])
+    lib.ta_b200_debug_tile_footprint.restype = C.c_int
+    lib.ta_b200_debug_tile_shape.argtypes = [C.POINTER(C.c_int32)]
+    lib.ta_b200_debug_tile_shape.restype = None
+    if lib.ta_b200_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"libta_b200.so has ABI {lib.ta_b200_abi_version()}, this package expects {ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().ta_b200_last_error().decode("utf-8", "replace")
+        raise LibraryError(f"{what} failed with status {rc}: {msg}")
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness, contrast,
+                saturation, gray, mean, std, contrast_mode=CONTRAST_FAST, gray_mean=None) -> FusedParams:
+    """Fill a FusedParams from tensors (device or host; the caller picks the entry point)."""
+    p = FusedParams()
+    p.struct_size = C.sizeof(FusedParams)
+    p.dtype = F16 if image.dtype == torch.float16 else F32
+    p.n, p.c, p.h, p.w = image.shape
+    p.oh, p.ow = out.shape[2], out.shape[3]
+    p.inp, p.out = _ptr(image), _ptr(out)
+    p.top, p.left, p.flip, p.matrix = _ptr(top), _ptr(left), _ptr(flip), _ptr(matrix)
+    p.fill = float(fill)
+    p.interp = BILINEAR if bilinear else NEAREST
+    p.apply = int(apply_bits)
+    p.brightness, p.contrast, p.saturation, p.gray = _ptr(brightness), _ptr(contrast), _ptr(saturation), _ptr(gray)
+    m = mean if mean is not None else (0.0, 0.0, 0.0)
+    s = std if std is not None else (1.0, 1.0, 1.0)
+    for i in range(3):
+        p.mean[i] = float(m[i])
+        p.std[i] = float(s[i])
+    p.contrast_mode = int(contrast_mode)
+    p.gray_mean = _ptr(gray_mean)
+    return p
+
+
+def launch_fused(params: FusedParams, device: torch.device, checked: bool = False) -> None:
+    lib = load()
+    with torch.cuda.device(device):
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        fn = lib.ta_b200_debug_fused_checked if checked else lib.ta_b200_fused_augment
+        check(fn(C.byref(params), stream), "ta_b200_fused_augment")
+
+
+def launch_gray_mean(params: FusedParams, device: torch.device) -> torch.Tensor:
+    """Run the grayscale-mean pre-pass; returns the fp32 ``[n]`` means on ``device``."""
+    lib = load()
+    with torch.cuda.device(device):
+        need = int(lib.ta_b200_gray_mean_scratch_bytes(C.byref(params)))
+        scratch = torch.empty(need, dtype=torch.uint8, device=device)
+        means = torch.empty(params.n, dtype=torch.float32, device=device)
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        check(lib.ta_b200_gray_mean(C.byref(params), _ptr(means), _ptr(scratch), need, stream), "ta_b200_gray_mean")
+    return means
+
+
+def debug_counters(reset: bool = False):
+    """(staged tiles, direct tiles, staging violations, barrier time-outs) on the current device."""
+    buf = (C.c_uint64 * 4)()
+    check(load().ta_b200_debug_counters(buf, int(reset)), "ta_b200_debug_counters")
+    return tuple(int(x) for x in buf)
+
+
+def tile_shape():
+    buf = (C.c_int32 * 4)()
+    load().ta_b200_debug_tile_shape(buf)
+    return tuple(int(x) for x in buf)
+
+
+def tile_footprint(bilinear, elem_bytes, h, w, oh, ow, top, left, flip, matrix, tile_x, tile_y):
+    """Host-side evaluation of the staged kernel's footprint for one tile (tests)."""
+    cap = tile_shape()[2]
+    row0 = C.c_int32(0)
+    xs = (C.c_int32 * cap)()
+    xe = (C.c_int32 * cap)()
+    m = (C.c_float * 6)(*[float(v) for v in matrix])
+    rows = load().ta_b200_debug_tile_footprint(int(bool(bilinear)), elem_bytes, h, w, oh, ow, float(top), float(left),
+                                               int(bool(flip)), m, tile_x, tile_y, C.byref(row0), xs, xe, cap)
+    return rows, int(row0.value), [int(v) for v in xs[:rows]], [int(v) for v in xe[:rows]]

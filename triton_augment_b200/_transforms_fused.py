@@ -1,0 +1,124 @@
+"""TritonFusedAugment: every augmentation in one kernel launch (re-exported by transforms.py)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import functional as F
+from . import transforms as T
+from ._transforms_color import TritonColorJitterNormalize
+from ._transforms_geometric import TritonRandomAffine
+from .functional import InterpolationMode
+
+__all__ = ["TritonFusedAugment"]
+
+
+class TritonFusedAugment(T._BatchAware):
+    """RandomAffine -> RandomCrop -> RandomHorizontalFlip -> ColorJitter -> RandomGrayscale ->
+    Normalize as ONE pass over the image.
+
+    Constructor arguments, defaults and the order of random draws are the reference's
+    (transforms.py:1252-1580).  Draw order per call, each a separate draw of ``param_count``
+    values from the device's default generator: the affine draws (only if any affine
+    argument was given), crop top and left as fp32 ``randint`` (only with ``crop_size``),
+    the flip mask (only if ``horizontal_flip_p > 0``), brightness, contrast, saturation
+    (only those that are set), and the grayscale mask (always).
+
+    ``contrast_mode="torchvision"`` (extra) uses torchvision's mean-based contrast instead
+    of the reference's fast formula, at the cost of one more read of the source footprint.
+    """
+
+    def __init__(self, crop_size=None, horizontal_flip_p: float = 0.0, degrees=0, translate=None, scale=None,
+                 shear=None, interpolation=InterpolationMode.NEAREST, fill: float = 0.0, brightness=0, contrast=0,
+                 saturation=0, grayscale_p: float = 0.0, mean=None, std=None, same_on_batch: bool = False,
+                 same_on_frame: bool = True, contrast_mode: str = "fast"):
+        super().__init__(same_on_batch, same_on_frame)
+        if crop_size is None:
+            self.crop_height = self.crop_width = None
+        elif isinstance(crop_size, int):
+            self.crop_height = self.crop_width = crop_size
+        else:
+            self.crop_height, self.crop_width = crop_size
+        self.horizontal_flip_p = horizontal_flip_p
+        self.has_affine = any([degrees != 0, translate is not None, scale is not None, shear is not None])
+        if self.has_affine:
+            self.affine_helper = TritonRandomAffine(degrees=degrees, translate=translate, scale=scale, shear=shear,
+                                                    interpolation=interpolation, fill=fill,
+                                                    same_on_batch=same_on_batch, same_on_frame=same_on_frame)
+            self.interpolation = interpolation
+            self.fill = fill
+        self.color_helper = TritonColorJitterNormalize(brightness=brightness, contrast=contrast, saturation=saturation,
+                                                       grayscale_p=grayscale_p, mean=mean, std=std,
+                                                       same_on_batch=same_on_batch, same_on_frame=same_on_frame,
+                                                       contrast_mode=contrast_mode)
+        self.contrast_mode = contrast_mode
+
+    def _check_input(self, value, name, center=1.0, bound=(0, float("inf")), clip_first_on_zero=True):
+        return T._check_range(value, name, center, bound, clip_first_on_zero)
+
+    def _get_params(self, param_count: int, device, img_size: Tuple[int, int]):
+        """All parameters of one call: (angle, translate, scale, shear, top, left, flip,
+        brightness, contrast, saturation, grayscale mask).  Reference: transforms.py:1431-1481."""
+        img_height, img_width = img_size
+        angle, translate, scale, shear = 0.0, [0.0, 0.0], 1.0, [0.0, 0.0]
+        if self.has_affine:
+            angle, translate, scale, shear = self.affine_helper._get_params(param_count, device, (img_height, img_width))
+        if self.crop_height is None:
+            top = torch.zeros(param_count, device=device, dtype=torch.float32)
+            left = torch.zeros(param_count, device=device, dtype=torch.float32)
+        else:
+            top = torch.randint(0, img_height - self.crop_height + 1, (param_count,), device=device, dtype=torch.float32)
+            left = torch.randint(0, img_width - self.crop_width + 1, (param_count,), device=device, dtype=torch.float32)
+        if self.horizontal_flip_p > 0:
+            flip = F._sample_bernoulli_tensor(param_count, self.horizontal_flip_p, device)
+        else:
+            flip = torch.zeros(param_count, device=device, dtype=torch.bool)
+        b, c, s, g = self.color_helper._get_params(param_count, device)
+        return angle, translate, scale, shear, top, left, flip, b, c, s, g
+
+    def _spread_all(self, lay, params):
+        """Sampled parameter sets -> one value per flattened sample."""
+        angle, translate, scale, shear, top, left, flip, b, c, s, g = params
+        if self.has_affine:
+            angle, scale = lay.spread(angle), lay.spread(scale)
+            translate, shear = lay.spread2(translate), lay.spread2(shear)
+        return (angle, translate, scale, shear, lay.spread(top), lay.spread(left), lay.spread(flip),
+                lay.spread(b), lay.spread(c), lay.spread(s), lay.spread(g))
+
+    def _apply(self, image4d, spread_params):
+        """Run the kernel on a (slice of a) flattened batch with per-sample parameters."""
+        angle, translate, scale, shear, top, left, flip, b, c, s, g = spread_params
+        h, w = image4d.shape[2:]
+        return F.fused_augment(
+            image4d, top=top, left=left,
+            height=self.crop_height if self.crop_height is not None else h,
+            width=self.crop_width if self.crop_width is not None else w,
+            flip_horizontal=flip, angle=angle, translate=translate, scale=scale, shear=shear,
+            interpolation=self.interpolation if self.has_affine else "nearest",
+            fill=self.fill if self.has_affine else 0.0,
+            brightness_factor=b, contrast_factor=c, saturation_factor=s, grayscale=g,
+            mean=self.color_helper.mean, std=self.color_helper.std, contrast_mode=self.contrast_mode,
+            _flags=self.color_helper._colour_flags(affine=self.has_affine))
+
+    def forward(self, image: torch.Tensor) -> torch.Tensor:
+        lay = self._layout(image)
+        h, w = lay.image.shape[2:]
+        params = self._get_params(lay.count, lay.image.device, (h, w))
+        return lay.restore(self._apply(lay.image, self._spread_all(lay, params)))
+
+    def __repr__(self):
+        ch = self.color_helper
+        parts = [f"crop_size=({self.crop_height}, {self.crop_width})" if self.crop_height is not None
+                 else "crop_size=None", f"horizontal_flip_p={self.horizontal_flip_p}"]
+        if self.has_affine:
+            ah = self.affine_helper
+            parts.append(f"degrees={ah.degrees}, translate={ah.translate}, scale={ah.scale}, shear={ah.shear}")
+        for name in ("brightness", "contrast", "saturation"):
+            if getattr(ch, name):
+                parts.append(f"{name}={getattr(ch, name)}")
+        if ch.grayscale_p > 0:
+            parts.append(f"grayscale_p={ch.grayscale_p}")
+        if ch.mean is not None:
+            parts.append(f"mean={ch.mean}, std={ch.std}")
+        return f"{self.__class__.__name__}(" + ", ".join(parts) + ")"

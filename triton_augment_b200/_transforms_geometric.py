@@ -1,0 +1,209 @@
+"""Geometric transform classes (re-exported by transforms.py)."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import functional as F
+from . import transforms as T
+from .functional import InterpolationMode
+
+__all__ = ["TritonRandomCrop", "TritonCenterCrop", "TritonRandomHorizontalFlip", "TritonRandomCropFlip",
+           "TritonRandomAffine", "TritonRandomRotation"]
+
+_NO_COLOUR = dict(brightness=False, contrast=False, saturation=False, grayscale=False)
+
+
+def _draw_offsets(lay, h, w, th, tw, dtype):
+    """Two ``randint`` draws, top then left (transforms.py:972-973, 1210-1211, 1464-1465)."""
+    dev = lay.image.device
+    top = torch.randint(0, h - th + 1, (lay.count,), device=dev, dtype=dtype)
+    left = torch.randint(0, w - tw + 1, (lay.count,), device=dev, dtype=dtype)
+    return top, left
+
+
+class TritonRandomCrop(T._BatchAware):
+    """Random ``size`` window per image.  Reference: transforms.py:899-989."""
+
+    def __init__(self, size, same_on_batch: bool = False, same_on_frame: bool = True):
+        super().__init__(same_on_batch, same_on_frame)
+        self.size = T._size_pair(size)
+
+    def forward(self, image: torch.Tensor) -> torch.Tensor:
+        lay = self._layout(image)
+        h, w = lay.image.shape[2:]
+        th, tw = self.size
+        if h < th or w < tw:
+            raise ValueError(f"Image size ({h}, {w}) is smaller than crop size ({th}, {tw}). "
+                             f"Padding not yet supported in MVP.")
+        top, left = _draw_offsets(lay, h, w, th, tw, torch.int32)
+        return lay.restore(F.crop(lay.image, lay.spread(top), lay.spread(left), th, tw))
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}(size={self.size}, " + self._tail()
+
+
+class TritonCenterCrop(nn.Module):
+    """Central ``size`` window.  Reference: transforms.py:992-1041 (no upload of host tensors)."""
+
+    def __init__(self, size):
+        super().__init__()
+        self.size = T._size_pair(size)
+
+    def forward(self, image: torch.Tensor) -> torch.Tensor:
+        lay = T._Layout(image, False, True, upload=False)
+        return lay.restore(F.center_crop(lay.image, self.size))
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}(size={self.size})"
+
+
+class TritonRandomHorizontalFlip(T._BatchAware):
+    """Mirror with probability ``p`` per image; ``p == 0`` returns the input object without
+    drawing.  Reference: transforms.py:1044-1114."""
+
+    def __init__(self, p: float = 0.5, same_on_batch: bool = False, same_on_frame: bool = True):
+        super().__init__(same_on_batch, same_on_frame)
+        if not (0.0 <= p <= 1.0):
+            raise ValueError(f"p ({p}) must be in [0, 1]")
+        self.p = p
+
+    def forward(self, image: torch.Tensor) -> torch.Tensor:
+        if self.p == 0:
+            return image
+        lay = self._layout(image)
+        mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.image.device))
+        return lay.restore(F.horizontal_flip(lay.image, flip_mask=mask))
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}(p={self.p}, " + self._tail()
+
+
+class TritonRandomCropFlip(T._BatchAware):
+    """Random crop + random mirror in one launch.  Draws: int32 top, int32 left, then the
+    flip mask - always, also for ``horizontal_flip_p == 0``.  Reference: transforms.py:1117-1249."""
+
+    def __init__(self, size, horizontal_flip_p: float = 0.5, same_on_batch: bool = False, same_on_frame: bool = True):
+        super().__init__(same_on_batch, same_on_frame)
+        self.size = T._size_pair(size)
+        if not (0.0 <= horizontal_flip_p <= 1.0):
+            raise ValueError(f"horizontal_flip_p ({horizontal_flip_p}) must be in [0, 1]")
+        self.horizontal_flip_p = horizontal_flip_p
+
+    def forward(self, image: torch.Tensor) -> torch.Tensor:
+        lay = self._layout(image)
+        h, w = lay.image.shape[2:]
+        th, tw = self.size
+        if th > h or tw > w:
+            raise ValueError(f"Crop size ({th}, {tw}) is larger than image size ({h}, {w})")
+        top, left = _draw_offsets(lay, h, w, th, tw, torch.int32)
+        flip = F._sample_bernoulli_tensor(lay.count, self.horizontal_flip_p, lay.image.device)
+        out = F.fused_augment(lay.image, top=lay.spread(top), left=lay.spread(left), height=th, width=tw,
+                              flip_horizontal=lay.spread(flip), brightness_factor=1.0, contrast_factor=1.0,
+                              saturation_factor=1.0, grayscale=False, mean=None, std=None,
+                              _flags=dict(affine=False, **_NO_COLOUR))
+        return lay.restore(out)
+
+    def __repr__(self):
+        return (f"{self.__class__.__name__}(size={self.size}, horizontal_flip_p={self.horizontal_flip_p}, "
+                + self._tail())
+
+
+class TritonRandomAffine(T._BatchAware):
+    """Random rotation / translation / scale / shear with a constant-size output.
+
+    Ranges follow torchvision's RandomAffine; unlike torchvision the sampled translation is
+    not rounded to whole pixels (reference: transforms.py:1722-1727).  Draw order: angle
+    (always), tx, ty (if translate), scale (if scale), shear x, shear y (if shear, the y draw
+    happens even for a zero-width range).  Reference: transforms.py:1582-1817.
+    """
+
+    def __init__(self, degrees, translate=None, scale=None, shear=None, interpolation=InterpolationMode.NEAREST,
+                 fill: float = 0.0, center=None, same_on_batch: bool = False, same_on_frame: bool = True):
+        super().__init__(same_on_batch, same_on_frame)
+        if isinstance(degrees, (int, float)):
+            if degrees < 0:
+                raise ValueError("If degrees is a single number, it must be positive.")
+            self.degrees = (-float(degrees), float(degrees))
+        else:
+            if len(degrees) != 2:
+                raise ValueError("If degrees is a sequence, it must be of length 2.")
+            self.degrees = (float(degrees[0]), float(degrees[1]))
+        self.translate = None
+        if translate is not None:
+            if len(translate) != 2:
+                raise ValueError("translate should be a sequence of length 2.")
+            if not (0.0 <= translate[0] <= 1.0 and 0.0 <= translate[1] <= 1.0):
+                raise ValueError("translation values should be between 0 and 1")
+            self.translate = (float(translate[0]), float(translate[1]))
+        self.scale = None
+        if scale is not None:
+            if len(scale) != 2:
+                raise ValueError("scale should be a sequence of length 2.")
+            if scale[0] > scale[1]:
+                raise ValueError("scale should be (min, max)")
+            self.scale = (float(scale[0]), float(scale[1]))
+        self.shear = None
+        if shear is not None:
+            if isinstance(shear, (int, float)):
+                if shear < 0:
+                    raise ValueError("If shear is a single number, it must be positive.")
+                self.shear = (-float(shear), float(shear), 0.0, 0.0)
+            elif len(shear) == 2:
+                self.shear = (float(shear[0]), float(shear[1]), 0.0, 0.0)
+            elif len(shear) == 4:
+                self.shear = tuple(float(v) for v in shear)
+            else:
+                raise ValueError("shear should be a single number or a sequence of length 2 or 4.")
+        self.interpolation = interpolation
+        self.fill = float(fill)
+        self.center = center
+
+    def _get_params(self, param_count: int, device, img_size):
+        height, width = img_size
+        u = F._sample_uniform_tensor
+        angle = u(param_count, self.degrees[0], self.degrees[1], device)
+        if self.translate is not None:
+            max_dx, max_dy = float(self.translate[0] * width), float(self.translate[1] * height)
+            tx = u(param_count, -max_dx, max_dx, device)
+            ty = u(param_count, -max_dy, max_dy, device)
+            translate = torch.stack([tx, ty], dim=1)
+        else:
+            translate = torch.zeros((param_count, 2), device=device)
+        scale = u(param_count, self.scale[0], self.scale[1], device) if self.scale is not None \
+            else torch.ones(param_count, device=device)
+        if self.shear is not None:
+            sx = u(param_count, self.shear[0], self.shear[1], device)
+            sy = u(param_count, self.shear[2], self.shear[3], device)
+            shear = torch.stack([sx, sy], dim=1)
+        else:
+            shear = torch.zeros((param_count, 2), device=device)
+        return angle, translate, scale, shear
+
+    def forward(self, img: torch.Tensor) -> torch.Tensor:
+        lay = self._layout(img)
+        h, w = lay.image.shape[2:]
+        angle, translate, scale, shear = self._get_params(lay.count, lay.image.device, (h, w))
+        out = F.affine(lay.image, angle=lay.spread(angle), translate=lay.spread2(translate), scale=lay.spread(scale),
+                       shear=lay.spread2(shear), interpolation=self.interpolation, fill=self.fill, center=self.center)
+        return lay.restore(out)
+
+    def __repr__(self):
+        return (f"{self.__class__.__name__}(degrees={self.degrees}, translate={self.translate}, scale={self.scale}, "
+                f"shear={self.shear}, interpolation={self.interpolation}, fill={self.fill}, center={self.center}, "
+                + self._tail())
+
+
+class TritonRandomRotation(TritonRandomAffine):
+    """Random rotation only.  Reference: transforms.py:1822-1902."""
+
+    def __init__(self, degrees, interpolation=InterpolationMode.NEAREST, expand: bool = False, center=None,
+                 fill: float = 0.0, same_on_batch: bool = False, same_on_frame: bool = True):
+        if expand:
+            raise NotImplementedError("expand=True is not yet supported in Triton-Augment")
+        super().__init__(degrees=degrees, translate=None, scale=None, shear=None, interpolation=interpolation,
+                         fill=fill, center=center, same_on_batch=same_on_batch, same_on_frame=same_on_frame)
+
+    def __repr__(self):
+        return (f"{self.__class__.__name__}(degrees={self.degrees}, interpolation={self.interpolation}, "
+                f"fill={self.fill}, " + self._tail())

@@ -1,0 +1,230 @@
+// extern "C" entry points of libta_b200.so (declared in include/ta_b200.h):
+// argument checking, kernel selection, launch shapes, and the two small helper
+// kernels (per-image grayscale mean, inverse affine matrices).
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "../../include/ta_b200.h"
+#include "ta_tables.cuh"
+
+namespace ta {
+
+// ----------------------------------------------------------------------------- errors
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static int cuda_fail(cudaError_t e, const char *what)
+{
+    return fail(TA_B200_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// ----------------------------------------------------------------------------- per-device state
+constexpr int kMaxDevices = 16;
+constexpr int kNumKinds = 3, kNumDtypes = 2;
+
+struct DeviceState {
+    std::mutex mu;
+    bool probed = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    unsigned long long *counters = nullptr;          // 4 words of device memory
+    // launch shape per kernel: resident CTAs per SM (0 = not prepared yet)
+    unsigned char blocks_per_sm[kNumKinds][kNumDtypes][2][kNumFlagCombos + 1] = {};
+};
+static DeviceState g_dev[kMaxDevices];
+
+static int current_device(DeviceState **out, int *index)
+{
+    int d = -1;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (d < 0 || d >= kMaxDevices) return fail(TA_B200_ERR_DEVICE, "device index %d not supported", d);
+    DeviceState &s = g_dev[d];
+    std::lock_guard<std::mutex> lock(s.mu);
+    if (!s.probed) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, d);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+        s.sm_count = prop.multiProcessorCount;
+        s.cc_major = prop.major;
+        if (prop.major != 10)
+            return fail(TA_B200_ERR_DEVICE, "device %d is compute capability %d.%d; this library is built for 10.x only",
+                        d, prop.major, prop.minor);
+        e = cudaMalloc(&s.counters, 4 * sizeof(unsigned long long));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(counters)");
+        e = cudaMemset(s.counters, 0, 4 * sizeof(unsigned long long));
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(counters)");
+        s.probed = true;
+    }
+    *out = &s;
+    if (index) *index = d;
+    return TA_B200_OK;
+}
+
+static const KernelTable &table_for(int kind, int dtype)
+{
+    if (dtype == TA_B200_F32)
+        return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : table_f32_bilinear();
+    return kind == 0 ? table_f16_direct() : kind == 1 ? table_f16_nearest() : table_f16_bilinear();
+}
+
+static size_t smem_for(int kind, int dtype, int c)
+{
+    if (kind == 0) return 0;
+    const size_t es = dtype == TA_B200_F32 ? 4 : 2;
+    return (size_t)c * kMaxRows * kPitch * es + (size_t)(kMaxRows + 4) * sizeof(int);
+}
+
+// Resident CTAs per SM for a kernel, computed once per device; also opts the kernel in
+// to its dynamic shared memory size on that device.
+static int prepare_kernel(DeviceState &s, const void *fn, int kind, int dtype, int c, unsigned slot, int *blocks)
+{
+    std::lock_guard<std::mutex> lock(s.mu);
+    unsigned char &cached = s.blocks_per_sm[kind][dtype][c == 3][slot];
+    if (cached == 0) {
+        const size_t smem = smem_for(kind, dtype, c);
+        cudaError_t e;
+        if (smem > 0) {
+            e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
+        }
+        int nb = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, kThreads, smem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
+        if (nb < 1) return fail(TA_B200_ERR_CUDA, "kernel does not fit on an SM");
+        cached = (unsigned char)(nb > 255 ? 255 : nb);
+    }
+    *blocks = cached;
+    return TA_B200_OK;
+}
+
+// ----------------------------------------------------------------------------- validation
+static int validate(const ta_b200_fused_params *p, bool for_mean = false)
+{
+    if (!p) return fail(TA_B200_ERR_NULL, "params is NULL");
+    if (p->struct_size != sizeof(ta_b200_fused_params))
+        return fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", p->struct_size,
+                    sizeof(ta_b200_fused_params));
+    if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16) return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
+    if (p->c != 1 && p->c != 3)
+        return fail(TA_B200_ERR_SHAPE, "channels must be 1 or 3, got %d", p->c);
+    if (p->n < 0 || p->h <= 0 || p->w <= 0 || p->oh <= 0 || p->ow <= 0)
+        return fail(TA_B200_ERR_SHAPE, "bad sizes n=%d h=%d w=%d oh=%d ow=%d", p->n, p->h, p->w, p->oh, p->ow);
+    if ((double)p->h * p->w >= 2147483648.0 || (double)p->oh * p->ow >= 2147483648.0)
+        return fail(TA_B200_ERR_TOO_LARGE, "one image plane must stay below 2^31 elements");
+    if (p->n > 0 && (!p->in || !p->out)) return fail(TA_B200_ERR_NULL, "in/out is NULL");
+    if (p->c == 1 && (p->apply & (TA_B200_APPLY_SATURATION | TA_B200_APPLY_GRAYSCALE)))
+        return fail(TA_B200_ERR_UNSUPPORTED, "saturation / grayscale need 3 channels");
+    if ((p->apply & TA_B200_APPLY_BRIGHTNESS) && !p->brightness) return fail(TA_B200_ERR_NULL, "brightness is NULL");
+    if (p->matrix && p->interp != TA_B200_NEAREST && p->interp != TA_B200_BILINEAR)
+        return fail(TA_B200_ERR_UNSUPPORTED, "interp %d", p->interp);
+    if (for_mean) return TA_B200_OK;     // the pre-pass reads geometry and brightness only
+    if ((p->apply & TA_B200_APPLY_CONTRAST) && !p->contrast) return fail(TA_B200_ERR_NULL, "contrast is NULL");
+    if ((p->apply & TA_B200_APPLY_SATURATION) && !p->saturation) return fail(TA_B200_ERR_NULL, "saturation is NULL");
+    if ((p->apply & TA_B200_APPLY_GRAYSCALE) && !p->gray) return fail(TA_B200_ERR_NULL, "gray is NULL");
+    if (p->apply & ~31u) return fail(TA_B200_ERR_UNSUPPORTED, "unknown apply bits 0x%x", p->apply);
+    if (p->contrast_mode != TA_B200_CONTRAST_FAST && p->contrast_mode != TA_B200_CONTRAST_MEAN)
+        return fail(TA_B200_ERR_UNSUPPORTED, "contrast_mode %d", p->contrast_mode);
+    if ((p->apply & TA_B200_APPLY_CONTRAST) && p->contrast_mode == TA_B200_CONTRAST_MEAN && !p->gray_mean)
+        return fail(TA_B200_ERR_NULL, "contrast_mode MEAN needs gray_mean");
+    return TA_B200_OK;
+}
+
+static int validate_geometry_only(const ta_b200_fused_params *p) { return validate(p, true); }
+
+static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
+{
+    memset(&k, 0, sizeof(k));
+    k.in = p->in; k.out = p->out;
+    k.top = p->top; k.left = p->left; k.flip = p->flip; k.matrix = p->matrix;
+    k.bf = p->brightness; k.cf = p->contrast; k.sf = p->saturation; k.gray = p->gray;
+    k.gray_mean = p->gray_mean;
+    k.counters = s.counters;
+    k.n = p->n; k.h = p->h; k.w = p->w; k.oh = p->oh; k.ow = p->ow;
+    k.fill = p->fill;
+    for (int i = 0; i < 3; ++i) {
+        const bool norm = (p->apply & TA_B200_APPLY_NORMALIZE) != 0;
+        k.mean[i] = norm ? p->mean[i] : 0.0f;
+        k.stdv[i] = norm ? p->std[i] : 1.0f;
+        k.inv_std[i] = 1.0f / k.stdv[i];
+        k.nbias[i] = -k.mean[i] * k.inv_std[i];
+    }
+    const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
+    k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
+                  ((size_t)p->h * p->w * es) % 16 == 0;
+}
+
+static unsigned template_flags(const ta_b200_fused_params *p)
+{
+    unsigned f = p->apply & 31u;
+    if ((f & kC) && p->contrast_mode == TA_B200_CONTRAST_MEAN) f |= kMean;
+    return f;
+}
+
+static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool checked)
+{
+    int rc = validate(p);
+    if (rc != TA_B200_OK) return rc;
+    if (p->n == 0) return TA_B200_OK;
+    DeviceState *s = nullptr;
+    rc = current_device(&s, nullptr);
+    if (rc != TA_B200_OK) return rc;
+
+    const int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    unsigned f = template_flags(p);
+    const KernelTable &tab = table_for(kind, p->dtype);
+    const void *fn;
+    unsigned slot = f;
+    if (checked && kind != 0) {
+        if (f != 0) return fail(TA_B200_ERR_UNSUPPORTED, "checked staging build exists for apply == 0 only");
+        fn = p->c == 3 ? tab.c3_checked : tab.c1_checked;
+        slot = kNumFlagCombos;
+    } else {
+        fn = p->c == 3 ? tab.c3[f] : tab.c1[f];
+    }
+    if (!fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
+    int blocks = 0;
+    rc = prepare_kernel(*s, fn, kind, p->dtype, p->c, slot, &blocks);
+    if (rc != TA_B200_OK) return rc;
+
+    KArgs k;
+    fill_kargs(k, p, *s);
+    long long work;
+    if (kind == 0) {
+        k.tiles_x = (p->ow + 31) / 32;
+        k.tiles_y = (p->oh + kDirectRows - 1) / kDirectRows;
+        work = ((long long)p->n * k.tiles_x * k.tiles_y + kWarps - 1) / kWarps;      // CTAs needed at one strip per warp
+    } else {
+        k.tiles_x = (p->ow + kTileW - 1) / kTileW;
+        k.tiles_y = (p->oh + kTileH - 1) / kTileH;
+        work = (long long)p->n * k.tiles_x * k.tiles_y;
+    }
+    const long long tiles = (long long)p->n * k.tiles_x * k.tiles_y;
+    if (tiles >= 2147483647LL) return fail(TA_B200_ERR_TOO_LARGE, "too many tiles (%lld)", tiles);
+    k.num_tiles = (int)tiles;
+    // Persistent launch: one wave of resident CTAs, fewer when there is less work.
+    long long grid = (long long)s->sm_count * blocks;
+    if (grid > work) grid = work;
+    if (grid < 1) grid = 1;
+    void *args[] = {&k};
+    cudaError_t e = cudaLaunchKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem_for(kind, p->dtype, p->c), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernel(fused)");
+    return TA_B200_OK;
+}
+
+}  // namespace ta
+
+#include "ta_api_helpers.cuh"

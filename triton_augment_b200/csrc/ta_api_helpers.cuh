@@ -1,0 +1,198 @@
+// Second half of ta_api.cu: the two helper kernels and the extern "C" functions.
+#pragma once
+
+namespace ta {
+
+// ----------------------------------------------------------------------------- grayscale mean
+// Mean over the output window of gray(clamp(brightness * sample)), i.e. of the image that
+// torchvision-exact contrast blends towards (triton_augment/functional.py:366-376 applied
+// after geometry and brightness).  grid = (blocks per image, images).  Each block sums a
+// fixed set of pixels in a fixed order, writes one partial, and the block that finishes
+// last for an image adds that image's partials in index order, so the result does not
+// depend on scheduling.  Nothing waits on anything.
+constexpr int kMeanMaxBlocks = 128;
+
+__host__ __device__ inline int mean_blocks_per_image(int oh, int ow)
+{
+    const long long px = (long long)oh * ow;
+    long long b = (px + 4095) / 4096;
+    return (int)(b < 1 ? 1 : b > kMeanMaxBlocks ? kMeanMaxBlocks : b);
+}
+
+// scratch layout: [n] unsigned counters, padded to 256 bytes, then [n][bpi] float partials
+__host__ __device__ inline size_t mean_partials_offset(int n)
+{
+    return (((size_t)n * sizeof(unsigned)) + 255) / 256 * 256;
+}
+
+template <typename T, int C, int KIND, bool BRIGHT>
+__global__ void __launch_bounds__(kThreads) gray_mean_kernel(const __grid_constant__ KArgs k, float *mean_out,
+                                                              unsigned *counters, float *partials)
+{
+    const int n = blockIdx.y, blk = blockIdx.x, bpi = gridDim.x;
+    Geom g;
+    load_geom(g, k, n, KIND != 0);
+    const T *img = (const T *)k.in + (size_t)n * C * k.h * k.w;
+    const size_t plane = (size_t)k.h * k.w;
+    const T fillv = Elem<T>::from_f(KIND != 0 ? k.fill : 0.0f);
+    float bf = 1.0f;
+    __half bh = __float2half_rn(1.0f);
+    if (BRIGHT) {
+        if (sizeof(T) == 4) bf = ((const float *)k.bf)[n];
+        else bh = ((const __half *)k.bf)[n];
+    }
+    const int total = k.oh * k.ow;
+    float acc = 0.0f;
+    for (int p = blk * kThreads + threadIdx.x; p < total; p += bpi * kThreads) {
+        const int y = p / k.ow, x = p - y * k.ow;
+        float v[C];
+        if (KIND == 0) {
+            const int xin = (int)img_x(g, k.ow, x), yin = (int)img_y(g, y);
+#pragma unroll
+            for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xin, yin, fillv));
+        } else {
+            const float xc = centred(img_x(g, k.ow, x), g.half_w), yc = centred(img_y(g, y), g.half_h);
+            const float sx = src_coord(xc, g.a, __fmul_rn(g.b, yc), g.c, g.half_w);
+            const float sy = src_coord(xc, g.d, __fmul_rn(g.e, yc), g.f, g.half_h);
+            if (KIND == 1) {
+                const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
+#pragma unroll
+                for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xn, yn, fillv));
+            } else {
+                const int x0 = __float2int_rd(sx), y0 = __float2int_rd(sy);
+                const float dx = sx - (float)x0, dy = sy - (float)y0;
+#pragma unroll
+                for (int c = 0; c < C; ++c) {
+                    const T *pl = img + c * plane;
+                    const float b4 = blend4(Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0, fillv)),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0, fillv)),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0 + 1, fillv)),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0 + 1, fillv)), dx, dy);
+                    v[c] = Elem<T>::to_f(Elem<T>::from_f(b4));
+                }
+            }
+        }
+        if (BRIGHT) {
+#pragma unroll
+            for (int c = 0; c < C; ++c)
+                v[c] = sizeof(T) == 4 ? __saturatef(v[c] * bf)
+                                      : __saturatef(__half2float(__hmul(__float2half_rn(v[c]), bh)));
+        }
+        float gr = C == 3 ? 0.2989f * v[0] + 0.587f * v[1] + 0.114f * v[C - 1] : v[0];
+        if (sizeof(T) == 2) gr = __half2float(__float2half_rn(gr));
+        acc += gr;
+    }
+    // block sum: shuffle within warps, then across warps through shared memory
+    __shared__ float warp_sum[kWarps];
+    __shared__ bool is_last;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float s = 0.0f;
+        for (int i = 0; i < kWarps; ++i) s += warp_sum[i];
+        partials[(size_t)n * bpi + blk] = s;
+        __threadfence();
+        is_last = atomicAdd(counters + n, 1u) == (unsigned)(bpi - 1);
+    }
+    __syncthreads();
+    if (is_last && threadIdx.x == 0) {
+        __threadfence();
+        double s = 0.0;
+        for (int i = 0; i < bpi; ++i) s += (double)__ldcg(partials + (size_t)n * bpi + i);
+        float m = (float)(s / (double)total);
+        if (sizeof(T) == 2) m = __half2float(__float2half_rn(m));
+        mean_out[n] = m;
+        counters[n] = 0;        // leave the scratch ready for the next call
+    }
+}
+
+template <typename T, int C, int KIND>
+static cudaError_t launch_gray_mean_t(const KArgs &k, bool bright, float *mean_out, unsigned *counters,
+                                      float *partials, int bpi, cudaStream_t stream)
+{
+    dim3 grid(bpi, k.n);
+    if (bright) gray_mean_kernel<T, C, KIND, true><<<grid, kThreads, 0, stream>>>(k, mean_out, counters, partials);
+    else gray_mean_kernel<T, C, KIND, false><<<grid, kThreads, 0, stream>>>(k, mean_out, counters, partials);
+    return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_gray_mean(const KArgs &k, int c, int kind, bool bright, float *mean_out,
+                                    unsigned *counters, float *partials, int bpi, cudaStream_t stream)
+{
+#define TA_GM(CC, KK) launch_gray_mean_t<T, CC, KK>(k, bright, mean_out, counters, partials, bpi, stream)
+    if (c == 3) return kind == 0 ? TA_GM(3, 0) : kind == 1 ? TA_GM(3, 1) : TA_GM(3, 2);
+    return kind == 0 ? TA_GM(1, 0) : kind == 1 ? TA_GM(1, 1) : TA_GM(1, 2);
+#undef TA_GM
+}
+
+// Checks, scratch carving and launch of the grayscale-mean pre-pass.
+static int gray_mean_on(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,
+                        cudaStream_t stream, bool clear_counters)
+{
+    int rc = validate_geometry_only(p);
+    if (rc != TA_B200_OK) return rc;
+    if (!mean_out) return fail(TA_B200_ERR_NULL, "mean_out is NULL");
+    if (p->n == 0) return TA_B200_OK;
+    if (p->n > 65535) return fail(TA_B200_ERR_TOO_LARGE, "gray_mean handles at most 65535 images per call");
+    const int bpi = mean_blocks_per_image(p->oh, p->ow);
+    const size_t need = mean_partials_offset(p->n) + (size_t)p->n * bpi * sizeof(float);
+    if (!scratch || scratch_bytes < need || ((uintptr_t)scratch % 256) != 0)
+        return fail(TA_B200_ERR_SCRATCH, "scratch must be 256-byte aligned and >= %zu bytes (got %zu)", need,
+                    scratch_bytes);
+    DeviceState *s = nullptr;
+    rc = current_device(&s, nullptr);
+    if (rc != TA_B200_OK) return rc;
+    KArgs k;
+    fill_kargs(k, p, *s);
+    unsigned *counters = (unsigned *)scratch;
+    float *partials = (float *)((char *)scratch + mean_partials_offset(p->n));
+    cudaError_t e;
+    if (clear_counters) {
+        e = cudaMemsetAsync(counters, 0, (size_t)p->n * sizeof(unsigned), stream);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(scratch)");
+    }
+    const int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    const bool bright = (p->apply & TA_B200_APPLY_BRIGHTNESS) != 0;
+    e = p->dtype == TA_B200_F32
+            ? launch_gray_mean<float>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream)
+            : launch_gray_mean<__half>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(gray_mean)");
+    return TA_B200_OK;
+}
+
+// ----------------------------------------------------------------------------- inverse affine matrices
+// One thread per image; every operation individually rounded, in the order of
+// triton_augment/functional.py:853-890 (which runs each line as its own elementwise op).
+__global__ void inverse_matrix_kernel(int n, const float *center, const float *angle, const float *translate,
+                                      const float *scale, const float *shear, float *matrix)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float d2r = (float)(3.141592653589793 / 180.0);
+    const float rot = __fmul_rn(angle[i], d2r);
+    const float sx = __fmul_rn(shear[2 * i], d2r), sy = __fmul_rn(shear[2 * i + 1], d2r);
+    const float cx = center ? center[2 * i] : 0.0f, cy = center ? center[2 * i + 1] : 0.0f;
+    const float tx = translate[2 * i], ty = translate[2 * i + 1];
+    const float cos_sy = cosf(sy);
+    const float rms = __fsub_rn(rot, sy);
+    const float a = __fdiv_rn(cosf(rms), cos_sy);
+    const float b = __fsub_rn(__fdiv_rn(__fmul_rn(-cosf(rms), tanf(sx)), cos_sy), sinf(rot));
+    const float c = __fdiv_rn(sinf(rms), cos_sy);
+    const float d = __fadd_rn(__fdiv_rn(__fmul_rn(-sinf(rms), tanf(sx)), cos_sy), cosf(rot));
+    const float sc = scale[i];
+    const float m0 = __fdiv_rn(d, sc), m1 = __fdiv_rn(-b, sc), m3 = __fdiv_rn(-c, sc), m4 = __fdiv_rn(a, sc);
+    const float ux = __fsub_rn(-cx, tx), uy = __fsub_rn(-cy, ty);
+    float m2 = __fadd_rn(__fmul_rn(m0, ux), __fmul_rn(m1, uy));
+    float m5 = __fadd_rn(__fmul_rn(m3, ux), __fmul_rn(m4, uy));
+    m2 = __fadd_rn(m2, cx);
+    m5 = __fadd_rn(m5, cy);
+    float *m = matrix + 6 * (size_t)i;
+    m[0] = m0; m[1] = m1; m[2] = m2; m[3] = m3; m[4] = m4; m[5] = m5;
+}
+
+}  // namespace ta
+
+#include "ta_api_host.cuh"

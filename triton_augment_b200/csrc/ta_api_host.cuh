@@ -1,0 +1,239 @@
+// Third part of ta_api.cu: the host-buffer pipeline and the extern "C" functions.
+#pragma once
+
+namespace ta {
+
+// ----------------------------------------------------------------------------- host-buffer pipeline
+// Images are independent, so a host batch is cut into slices; slice i uploads while
+// slice i-1 runs and slice i-2 downloads.  Two input and two output device buffers per
+// device, three streams, events between them.  Buffers and streams are created on first
+// use and kept (grown when a later call needs more).
+struct HostPipe {
+    std::mutex mu;
+    bool ready = false;
+    cudaStream_t up = nullptr, run = nullptr, down = nullptr;
+    cudaEvent_t uploaded[2] = {}, computed[2] = {}, downloaded[2] = {};
+    void *d_in[2] = {}, *d_out[2] = {};
+    size_t in_cap = 0, out_cap = 0;
+    void *d_params = nullptr;
+    size_t params_cap = 0;
+    void *d_scratch = nullptr;
+    size_t scratch_cap = 0;
+};
+static HostPipe g_pipe[kMaxDevices];
+
+static cudaError_t grow(void **ptr, size_t *cap, size_t need)
+{
+    if (need <= *cap) return cudaSuccess;
+    if (*ptr) { cudaError_t e = cudaFree(*ptr); if (e != cudaSuccess) return e; *ptr = nullptr; *cap = 0; }
+    cudaError_t e = cudaMalloc(ptr, need);
+    if (e == cudaSuccess) *cap = need;
+    return e;
+}
+
+#define TA_CU(call, what) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return cuda_fail(e_, what); } while (0)
+
+static int fused_host(const ta_b200_fused_params *hp)
+{
+    // Validate with the device checks relaxed: gray_mean may be computed here.
+    ta_b200_fused_params v = *hp;
+    static const float dummy = 0.0f;
+    const bool need_mean = (hp->apply & TA_B200_APPLY_CONTRAST) && hp->contrast_mode == TA_B200_CONTRAST_MEAN;
+    if (need_mean && !v.gray_mean) v.gray_mean = &dummy;
+    int rc = validate(&v);
+    if (rc != TA_B200_OK) return rc;
+    if (hp->n == 0) return TA_B200_OK;
+    DeviceState *s = nullptr;
+    int dev = 0;
+    rc = current_device(&s, &dev);
+    if (rc != TA_B200_OK) return rc;
+    HostPipe &P = g_pipe[dev];
+    std::lock_guard<std::mutex> lock(P.mu);
+    if (!P.ready) {
+        TA_CU(cudaStreamCreateWithFlags(&P.up, cudaStreamNonBlocking), "cudaStreamCreate");
+        TA_CU(cudaStreamCreateWithFlags(&P.run, cudaStreamNonBlocking), "cudaStreamCreate");
+        TA_CU(cudaStreamCreateWithFlags(&P.down, cudaStreamNonBlocking), "cudaStreamCreate");
+        for (int i = 0; i < 2; ++i) {
+            TA_CU(cudaEventCreateWithFlags(&P.uploaded[i], cudaEventDisableTiming), "cudaEventCreate");
+            TA_CU(cudaEventCreateWithFlags(&P.computed[i], cudaEventDisableTiming), "cudaEventCreate");
+            TA_CU(cudaEventCreateWithFlags(&P.downloaded[i], cudaEventDisableTiming), "cudaEventCreate");
+        }
+        P.ready = true;
+    }
+    const size_t es = hp->dtype == TA_B200_F32 ? 4 : 2;
+    const size_t in_img = (size_t)hp->c * hp->h * hp->w * es, out_img = (size_t)hp->c * hp->oh * hp->ow * es;
+    // Slice size: about 48 MiB of input per slice, at least 1 image, at least 4 slices when possible.
+    long long per = (long long)((48ull << 20) / (in_img ? in_img : 1));
+    if (per < 1) per = 1;
+    if (per > (hp->n + 3) / 4) per = (hp->n + 3) / 4;
+    if (per < 1) per = 1;
+    const int slice = (int)per;
+    // d_in[0]/d_in[1] share one capacity value: grow both when needed.
+    if ((size_t)slice * in_img > P.in_cap) {
+        for (int i = 0; i < 2; ++i) {
+            if (P.d_in[i]) TA_CU(cudaFree(P.d_in[i]), "cudaFree");
+            P.d_in[i] = nullptr;
+            TA_CU(cudaMalloc(&P.d_in[i], (size_t)slice * in_img), "cudaMalloc(input slice)");
+        }
+        P.in_cap = (size_t)slice * in_img;
+    }
+    if ((size_t)slice * out_img > P.out_cap) {
+        for (int i = 0; i < 2; ++i) {
+            if (P.d_out[i]) TA_CU(cudaFree(P.d_out[i]), "cudaFree");
+            P.d_out[i] = nullptr;
+            TA_CU(cudaMalloc(&P.d_out[i], (size_t)slice * out_img), "cudaMalloc(output slice)");
+        }
+        P.out_cap = (size_t)slice * out_img;
+    }
+    // Per-image parameters: one device block, each vector 256-byte aligned.
+    const size_t n = (size_t)hp->n;
+    auto al = [](size_t x) { return (x + 255) / 256 * 256; };
+    const size_t o_top = 0, o_left = o_top + al(n * 4), o_flip = o_left + al(n * 4), o_mat = o_flip + al(n),
+                 o_b = o_mat + al(n * 24), o_c = o_b + al(n * es), o_s = o_c + al(n * es), o_g = o_s + al(n * es),
+                 o_gm = o_g + al(n), total = o_gm + al(n * 4);
+    TA_CU(grow(&P.d_params, &P.params_cap, total), "cudaMalloc(params)");
+    char *dp = (char *)P.d_params;
+    auto up = [&](const void *src, size_t off, size_t bytes) -> cudaError_t {
+        return src ? cudaMemcpyAsync(dp + off, src, bytes, cudaMemcpyHostToDevice, P.run) : cudaSuccess;
+    };
+    TA_CU(up(hp->top, o_top, n * 4), "upload top");
+    TA_CU(up(hp->left, o_left, n * 4), "upload left");
+    TA_CU(up(hp->flip, o_flip, n), "upload flip");
+    TA_CU(up(hp->matrix, o_mat, n * 24), "upload matrix");
+    TA_CU(up(hp->brightness, o_b, n * es), "upload brightness");
+    TA_CU(up(hp->contrast, o_c, n * es), "upload contrast");
+    TA_CU(up(hp->saturation, o_s, n * es), "upload saturation");
+    TA_CU(up(hp->gray, o_g, n), "upload gray");
+    if (need_mean && hp->gray_mean) TA_CU(up(hp->gray_mean, o_gm, n * 4), "upload gray_mean");
+    if (need_mean && !hp->gray_mean) {
+        const size_t need = mean_partials_offset(slice) + (size_t)slice * mean_blocks_per_image(hp->oh, hp->ow) * 4;
+        TA_CU(grow(&P.d_scratch, &P.scratch_cap, need), "cudaMalloc(scratch)");
+    }
+
+    const int slices = (hp->n + slice - 1) / slice;
+    for (int i = 0; i < slices; ++i) {
+        const int b = i & 1, first = i * slice, cnt = (first + slice <= hp->n) ? slice : hp->n - first;
+        // upload: the input buffer is free once the kernel of slice i-2 has run
+        if (i >= 2) TA_CU(cudaStreamWaitEvent(P.up, P.computed[b], 0), "cudaStreamWaitEvent");
+        TA_CU(cudaMemcpyAsync(P.d_in[b], (const char *)hp->in + (size_t)first * in_img, (size_t)cnt * in_img,
+                              cudaMemcpyHostToDevice, P.up), "cudaMemcpyAsync(upload)");
+        TA_CU(cudaEventRecord(P.uploaded[b], P.up), "cudaEventRecord");
+        // run: needs its upload, and its output buffer back from the download of slice i-2
+        TA_CU(cudaStreamWaitEvent(P.run, P.uploaded[b], 0), "cudaStreamWaitEvent");
+        if (i >= 2) TA_CU(cudaStreamWaitEvent(P.run, P.downloaded[b], 0), "cudaStreamWaitEvent");
+        ta_b200_fused_params q = *hp;
+        q.n = cnt;
+        q.in = P.d_in[b];
+        q.out = P.d_out[b];
+        q.top = hp->top ? (const float *)(dp + o_top) + first : nullptr;
+        q.left = hp->left ? (const float *)(dp + o_left) + first : nullptr;
+        q.flip = hp->flip ? (const uint8_t *)(dp + o_flip) + first : nullptr;
+        q.matrix = hp->matrix ? (const float *)(dp + o_mat) + (size_t)first * 6 : nullptr;
+        q.brightness = hp->brightness ? dp + o_b + (size_t)first * es : nullptr;
+        q.contrast = hp->contrast ? dp + o_c + (size_t)first * es : nullptr;
+        q.saturation = hp->saturation ? dp + o_s + (size_t)first * es : nullptr;
+        q.gray = hp->gray ? (const uint8_t *)(dp + o_g) + first : nullptr;
+        q.gray_mean = need_mean ? (const float *)(dp + o_gm) + first : nullptr;
+        if (need_mean && !hp->gray_mean) {
+            rc = gray_mean_on(&q, (float *)(dp + o_gm) + first, P.d_scratch, P.scratch_cap, P.run, true);
+            if (rc != TA_B200_OK) return rc;
+        }
+        rc = launch_fused(&q, P.run, false);
+        if (rc != TA_B200_OK) return rc;
+        TA_CU(cudaEventRecord(P.computed[b], P.run), "cudaEventRecord");
+        // download
+        TA_CU(cudaStreamWaitEvent(P.down, P.computed[b], 0), "cudaStreamWaitEvent");
+        TA_CU(cudaMemcpyAsync((char *)hp->out + (size_t)first * out_img, P.d_out[b], (size_t)cnt * out_img,
+                              cudaMemcpyDeviceToHost, P.down), "cudaMemcpyAsync(download)");
+        TA_CU(cudaEventRecord(P.downloaded[b], P.down), "cudaEventRecord");
+    }
+    TA_CU(cudaStreamSynchronize(P.down), "cudaStreamSynchronize");
+    TA_CU(cudaStreamSynchronize(P.run), "cudaStreamSynchronize");
+    return TA_B200_OK;
+}
+
+}  // namespace ta
+
+// ----------------------------------------------------------------------------- C ABI
+extern "C" {
+
+int ta_b200_abi_version(void) { return TA_B200_ABI_VERSION; }
+
+const char *ta_b200_last_error(void) { return ta::g_err; }
+
+int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream)
+{
+    return ta::launch_fused(p, (cudaStream_t)stream, false);
+}
+
+size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p)
+{
+    if (!p || p->n <= 0 || p->oh <= 0 || p->ow <= 0) return 256;
+    return ta::mean_partials_offset(p->n) + (size_t)p->n * ta::mean_blocks_per_image(p->oh, p->ow) * sizeof(float);
+}
+
+int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,
+                      void *stream)
+{
+    return ta::gray_mean_on(p, mean_out, scratch, scratch_bytes, (cudaStream_t)stream, true);
+}
+
+int ta_b200_fused_augment_host(const ta_b200_fused_params *p) { return ta::fused_host(p); }
+
+int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *angle, const float *translate,
+                                  const float *scale, const float *shear, float *matrix, void *stream)
+{
+    if (n < 0) return ta::fail(TA_B200_ERR_SHAPE, "n = %d", n);
+    if (n == 0) return TA_B200_OK;
+    if (!angle || !translate || !scale || !shear || !matrix) return ta::fail(TA_B200_ERR_NULL, "NULL argument");
+    ta::inverse_matrix_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(n, center, angle, translate, scale,
+                                                                                 shear, matrix);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return ta::cuda_fail(e, "launch(inverse_matrix)");
+    return TA_B200_OK;
+}
+
+int ta_b200_debug_counters(uint64_t out[4], int reset)
+{
+    ta::DeviceState *s = nullptr;
+    int rc = ta::current_device(&s, nullptr);
+    if (rc != TA_B200_OK) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return ta::cuda_fail(e, "cudaDeviceSynchronize");
+    if (out) {
+        e = cudaMemcpy(out, s->counters, 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return ta::cuda_fail(e, "cudaMemcpy(counters)");
+    }
+    if (reset) {
+        e = cudaMemset(s->counters, 0, 4 * sizeof(uint64_t));
+        if (e != cudaSuccess) return ta::cuda_fail(e, "cudaMemset(counters)");
+    }
+    return TA_B200_OK;
+}
+
+// Same as ta_b200_fused_augment but with the staging assertions compiled in (apply must be 0).
+int ta_b200_debug_fused_checked(const ta_b200_fused_params *p, void *stream)
+{
+    return ta::launch_fused(p, (cudaStream_t)stream, true);
+}
+
+int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, int32_t w, int32_t oh, int32_t ow,
+                                 float top, float left, int32_t flip, const float matrix[6], int32_t tile_x,
+                                 int32_t tile_y, int32_t *row0, int32_t *xs, int32_t *xe, int32_t cap)
+{
+    ta::TileFootprint fp;
+    const int chunk = 16 / (elem_bytes == 2 ? 2 : 4);
+    ta::tile_footprint(fp, interp == TA_B200_BILINEAR ? 1 : 0, chunk, h, w, oh, ow, top, left, flip != 0, matrix,
+                       tile_x, tile_y);
+    if (row0) *row0 = fp.row0;
+    for (int r = 0; r < fp.rows && r < cap; ++r)
+        ta::tile_row_range(fp, interp == TA_B200_BILINEAR ? 1 : 0, chunk, r, xs[r], xe[r]);
+    return fp.rows;
+}
+
+void ta_b200_debug_tile_shape(int32_t out[4])
+{
+    out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows; out[3] = ta::kPitch;
+}
+
+}  // extern "C"

@@ -1,0 +1,345 @@
+// Shared device-side pieces of the sm_100a augmentation kernels: kernel argument
+// block, mbarrier / bulk-copy PTX wrappers, exact coordinate arithmetic, texel
+// sampling and the colour tier.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ta_footprint.h"
+
+namespace ta {
+
+// Colour flags as template bits (same values as TA_B200_APPLY_*), plus the contrast mode.
+constexpr unsigned kB = 1u, kC = 2u, kS = 4u, kG = 8u, kN = 16u, kMean = 32u;
+
+constexpr int kThreads = 256;          // per CTA, every kernel
+constexpr int kWarps = kThreads / 32;
+
+// Device status words (one block per device, see ta_api.cu).
+enum { kCntStaged = 0, kCntDirect = 1, kCntViolation = 2, kCntTimeout = 3 };
+
+struct KArgs {
+    const void *in;
+    void *out;
+    const float *top, *left;
+    const uint8_t *flip;
+    const float *matrix;
+    const void *bf, *cf, *sf;
+    const uint8_t *gray;
+    const float *gray_mean;
+    unsigned long long *counters;
+    int n, h, w, oh, ow;
+    int tiles_x, tiles_y, num_tiles;
+    int staged_ok;                     // source rows can be bulk-copied (16-byte aligned pitch and base)
+    float fill;
+    float mean[3], stdv[3];            // image-dtype-rounded values
+    float inv_std[3], nbias[3];        // 1/std and -mean/std (fp32 path)
+};
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: false when the phase did not complete within the poll budget.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity)
+{
+    for (int i = 0; i < (1 << 20); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// Bulk asynchronous copy global -> this CTA's shared memory, completion counted in
+// bytes on an mbarrier.  Addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------- element access
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float v) { return v; }
+    static __device__ __forceinline__ void store(float *p, float v) { __stcs(p, v); }
+};
+template <> struct Elem<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ void store(__half *p, float v)
+    {
+        __stcs(reinterpret_cast<unsigned short *>(p), __half_as_ushort(__float2half_rn(v)));
+    }
+};
+
+// ----------------------------------------------------------------------------- geometry
+// Per-image geometry, loaded once per tile.
+struct Geom {
+    float top, left;
+    bool flip;
+    float a, b, c, d, e, f;
+    float half_w, half_h;
+};
+
+__device__ __forceinline__ void load_geom(Geom &g, const KArgs &k, int n, bool affine)
+{
+    g.top = k.top ? __ldg(k.top + n) : 0.0f;
+    g.left = k.left ? __ldg(k.left + n) : 0.0f;
+    g.flip = k.flip ? __ldg(k.flip + n) != 0 : false;
+    g.half_w = (float)k.w * 0.5f;
+    g.half_h = (float)k.h * 0.5f;
+    if (affine) {
+        const float *m = k.matrix + (size_t)n * 6;
+        g.a = __ldg(m + 0); g.b = __ldg(m + 1); g.c = __ldg(m + 2);
+        g.d = __ldg(m + 3); g.e = __ldg(m + 4); g.f = __ldg(m + 5);
+    }
+}
+
+// x_img / y_img of triton_augment/kernels/geometric_kernel.py:390-394.
+__device__ __forceinline__ float img_x(const Geom &g, int ow, int x)
+{
+    return __fadd_rn((float)(g.flip ? ow - 1 - x : x), g.left);
+}
+__device__ __forceinline__ float img_y(const Geom &g, int y) { return __fadd_rn((float)y, g.top); }
+
+// Centred coordinate, geometric_kernel.py:410-411: (v - half) + 0.5.
+__device__ __forceinline__ float centred(float v, float half) { return __fadd_rn(__fsub_rn(v, half), 0.5f); }
+
+// Source coordinate, geometric_kernel.py:414-415, in the operation order and with the one
+// contraction the reference's GPU build performs: ((fma(xc, a, b*yc) + c) + half) + (-0.5).
+// Every step is an explicitly rounded intrinsic so the compiler cannot re-associate or fuse.
+__device__ __forceinline__ float src_coord(float xc, float a, float b_yc, float c, float half)
+{
+    float u = __fmaf_rn(xc, a, b_yc);
+    u = __fadd_rn(u, c);
+    u = __fadd_rn(half, u);
+    return __fadd_rn(u, -0.5f);
+}
+
+// ----------------------------------------------------------------------------- colour tier
+// Restates triton_augment/kernels/fused_kernel.py:234-283.  F holds the compiled-in operations.
+template <typename T, int C, unsigned F> struct Colour;
+
+__device__ __forceinline__ float gray_of(float r, float g, float b)
+{
+    return __fmaf_rn(0.114f, b, __fmaf_rn(0.587f, g, 0.2989f * r));
+}
+
+template <int C, unsigned F> struct Colour<float, C, F> {
+    float bf, cf, sf, oms, gmt;
+    bool gray;
+    __device__ __forceinline__ void init(const KArgs &k, int n)
+    {
+        bf = cf = sf = 1.0f; oms = gmt = 0.0f; gray = false;
+        if (F & kB) bf = __ldg((const float *)k.bf + n);
+        if (F & kC) {
+            cf = __ldg((const float *)k.cf + n);
+            if (F & kMean) gmt = __ldg(k.gray_mean + n) * (1.0f - cf);
+        }
+        if (F & kS) { sf = __ldg((const float *)k.sf + n); oms = 1.0f - sf; }
+        if (F & kG) gray = __ldg(k.gray + n) != 0;
+    }
+    // v: texels as sampled; returns values ready to store.
+    __device__ __forceinline__ void apply(const KArgs &k, const float (&in)[C], float (&v)[C]) const
+    {
+#pragma unroll
+        for (int i = 0; i < C; ++i) v[i] = in[i];
+        if (F & kB) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __saturatef(v[i] * bf);
+        }
+        if (F & kC) {
+#pragma unroll
+            for (int i = 0; i < C; ++i)
+                v[i] = (F & kMean) ? __saturatef(__fmaf_rn(v[i], cf, gmt))
+                                   : __saturatef(__fmaf_rn(v[i] - 0.5f, cf, 0.5f));
+        }
+        if (C == 3 && (F & kS)) {
+            const float gg = gray_of(v[0], v[1], v[2]) * oms;
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __saturatef(__fmaf_rn(v[i], sf, gg));
+        }
+        if (C == 3 && (F & kG)) {
+            if (gray) {
+                const float g = gray_of(v[0], v[1], v[2]);
+#pragma unroll
+                for (int i = 0; i < C; ++i) v[i] = g;
+            }
+        }
+        if (F & kN) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __fmaf_rn(v[i], k.inv_std[i], k.nbias[i]);
+        }
+    }
+};
+
+// fp16 images: the reference's GPU build keeps a value in fp16 until the first clamp of
+// an enabled operation and in fp32 from there to the store; factors, mean and std are
+// fp16 values and (1 - saturation) is an fp16 subtraction.
+template <int C, unsigned F> struct Colour<__half, C, F> {
+    __half bh, ch, sh, omsh, gmth;
+    float cf, sf, oms, gmt;
+    bool gray;
+    __device__ __forceinline__ void init(const KArgs &k, int n)
+    {
+        const __half one = __float2half_rn(1.0f);
+        bh = ch = sh = one; omsh = gmth = __float2half_rn(0.0f);
+        cf = sf = 1.0f; oms = gmt = 0.0f; gray = false;
+        if (F & kB) bh = ((const __half *)k.bf)[n];
+        if (F & kC) {
+            ch = ((const __half *)k.cf)[n];
+            cf = __half2float(ch);
+            if (F & kMean) {
+                const __half omc = __hsub(one, ch);
+                const float m = __ldg(k.gray_mean + n);
+                gmth = __hmul(__float2half_rn(m), omc);
+                gmt = m * __half2float(omc);
+            }
+        }
+        if (F & kS) {
+            sh = ((const __half *)k.sf)[n];
+            sf = __half2float(sh);
+            omsh = __hsub(one, sh);
+            oms = __half2float(omsh);
+        }
+        if (F & kG) gray = __ldg(k.gray + n) != 0;
+    }
+    static __device__ __forceinline__ __half gray_h(__half r, __half g, __half b)
+    {
+        return __hadd(__hadd(__hmul(__float2half_rn(0.2989f), r), __hmul(__float2half_rn(0.587f), g)),
+                      __hmul(__float2half_rn(0.114f), b));
+    }
+    __device__ __forceinline__ void apply(const KArgs &k, const __half (&in)[C], float (&v)[C]) const
+    {
+        __half hv[C];
+#pragma unroll
+        for (int i = 0; i < C; ++i) hv[i] = in[i];
+        constexpr bool wide_after_b = (F & kB) != 0;
+        constexpr bool wide_after_c = wide_after_b || (F & kC) != 0;
+        constexpr bool wide_after_s = wide_after_c || (C == 3 && (F & kS) != 0);
+        if (F & kB) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __saturatef(__half2float(__hmul(hv[i], bh)));
+        }
+        if (F & kC) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                if (wide_after_b) {
+                    v[i] = (F & kMean) ? __saturatef(__fmaf_rn(v[i], cf, gmt))
+                                       : __saturatef(__fmaf_rn(v[i] - 0.5f, cf, 0.5f));
+                } else if (F & kMean) {
+                    v[i] = __saturatef(__half2float(__hadd(__hmul(hv[i], ch), gmth)));
+                } else {
+                    const __half hh = __float2half_rn(0.5f);
+                    v[i] = __saturatef(__half2float(__hadd(__hmul(__hsub(hv[i], hh), ch), hh)));
+                }
+            }
+        }
+        if (C == 3 && (F & kS)) {
+            if (wide_after_c) {
+                const float gg = gray_of(v[0], v[1], v[2]) * oms;
+#pragma unroll
+                for (int i = 0; i < C; ++i) v[i] = __saturatef(__fmaf_rn(v[i], sf, gg));
+            } else {
+                const __half gg = __hmul(gray_h(hv[0], hv[1], hv[2]), omsh);
+#pragma unroll
+                for (int i = 0; i < C; ++i) v[i] = __saturatef(__half2float(__hadd(__hmul(hv[i], sh), gg)));
+            }
+        }
+        if (C == 3 && (F & kG)) {
+            if (gray) {
+                if (wide_after_s) {
+                    const float g = gray_of(v[0], v[1], v[2]);
+#pragma unroll
+                    for (int i = 0; i < C; ++i) v[i] = g;
+                } else {
+                    const __half g = gray_h(hv[0], hv[1], hv[2]);
+#pragma unroll
+                    for (int i = 0; i < C; ++i) hv[i] = g;
+                }
+            }
+        }
+        if (F & kN) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                if (wide_after_s)
+                    v[i] = (v[i] - k.mean[i]) * k.inv_std[i];
+                else
+                    v[i] = __half2float(__hdiv(__hsub(hv[i], __float2half_rn(k.mean[i])),
+                                               __float2half_rn(k.stdv[i])));
+            }
+        } else if (!wide_after_s) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __half2float(hv[i]);
+        }
+    }
+};
+
+// ----------------------------------------------------------------------------- global-memory taps
+// Used by the crop/flip kernel and by affine tiles that are not staged.  Bounds-checked;
+// texels outside the image read as `fill` (affine) or 0 (crop/flip).
+template <typename T>
+__device__ __forceinline__ T tap_global(const T *plane, int w, int h, int x, int y, T fillv)
+{
+    const bool ok = (unsigned)x < (unsigned)w && (unsigned)y < (unsigned)h;
+    return ok ? __ldg(plane + (size_t)y * w + x) : fillv;
+}
+
+// Bilinear blend, triton_augment/kernels/geometric_kernel.py:239-246 with the fma chain of
+// the reference's GPU build: p00*w00, then three fused accumulations.
+__device__ __forceinline__ float blend4(float p00, float p10, float p01, float p11, float dx, float dy)
+{
+    const float omx = 1.0f - dx, omy = 1.0f - dy;
+    float r = p00 * (omx * omy);
+    r = __fmaf_rn(p10, dx * omy, r);
+    r = __fmaf_rn(p01, omx * dy, r);
+    r = __fmaf_rn(p11, dx * dy, r);
+    return r;
+}
+
+}  // namespace ta

@@ -1,0 +1,133 @@
+// Source footprint of one output tile under flip -> crop offset -> inverse affine.
+//
+// The staged affine kernel copies, for every source row an output tile touches,
+// only the columns it touches, into shared memory.  This header computes those
+// rows and column ranges.  It is plain arithmetic shared by the device code and
+// by a host-side test hook, so the ranges can be checked on a CPU against a brute
+// force walk over the tile's pixels.
+//
+// Geometry restated from triton_augment/kernels/geometric_kernel.py:386-415: an
+// output pixel (x, y) maps to x_img = (flip ? ow-1-x : x) + left, y_img = y + top,
+// is centred on the input image, multiplied by the 2x3 inverse matrix and
+// un-centred.  The map is affine, so a tile (a rectangle) lands on a
+// parallelogram; the rows a sampling mode reads from it form a slab in source y,
+// and rectangle-intersect-slab is a convex polygon whose extreme source x lie on
+// the rectangle's edges.
+#pragma once
+
+#if defined(__CUDACC__)
+#define TA_HD __host__ __device__ __forceinline__
+#else
+#define TA_HD inline
+#endif
+
+#include <math.h>
+
+namespace ta {
+
+constexpr int kTileW = 64;       // output tile, pixels
+constexpr int kTileH = 32;
+constexpr int kMaxRows = 60;     // source rows one staged tile may span
+constexpr int kPitch = 96;       // elements reserved per staged source row
+constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
+constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
+
+struct TileFootprint {
+    float sx[4], sy[4];   // source coordinates of the tile's corners (x0y0, x1y0, x1y1, x0y1)
+    float inv[4];         // 1 / (sy[j] - sy[i]) per edge, 0 when the edge is level
+    int row0;             // first source row
+    int rows;             // number of source rows (0 = do not stage)
+};
+
+// mode: 0 nearest (reads row rint(sy)), 1 bilinear (reads rows floor(sy), floor(sy)+1)
+TA_HD void tile_footprint(TileFootprint &t, int mode, int chunk, int h, int w, int oh, int ow,
+                          float top, float left, bool flip, const float *m, int tile_x, int tile_y)
+{
+    const int x_first = tile_x * kTileW, y_first = tile_y * kTileH;
+    const int x_last = (x_first + kTileW < ow ? x_first + kTileW : ow) - 1;
+    const int y_last = (y_first + kTileH < oh ? y_first + kTileH : oh) - 1;
+    const float half_w = 0.5f * (float)w, half_h = 0.5f * (float)h;
+    const float xi0 = (float)(flip ? ow - 1 - x_last : x_first) + left;
+    const float xi1 = (float)(flip ? ow - 1 - x_first : x_last) + left;
+    const float xc0 = xi0 - half_w + 0.5f, xc1 = xi1 - half_w + 0.5f;
+    const float yc0 = (float)y_first + top - half_h + 0.5f, yc1 = (float)y_last + top - half_h + 0.5f;
+    const float cx[4] = {xc0, xc1, xc1, xc0}, cy[4] = {yc0, yc0, yc1, yc1};
+    float ymin = INFINITY, ymax = -INFINITY, xmin = INFINITY, xmax = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        t.sx[i] = (m[0] * cx[i] + m[1] * cy[i] + m[2]) + half_w - 0.5f;
+        t.sy[i] = (m[3] * cx[i] + m[4] * cy[i] + m[5]) + half_h - 0.5f;
+        ymin = fminf(ymin, t.sy[i]); ymax = fmaxf(ymax, t.sy[i]);
+        xmin = fminf(xmin, t.sx[i]); xmax = fmaxf(xmax, t.sx[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float d = t.sy[(i + 1) & 3] - t.sy[i];
+        t.inv[i] = d != 0.0f ? 1.0f / d : 0.0f;
+    }
+    t.rows = 0;
+    t.row0 = 0;
+    // Per corner and written so that a NaN fails (fminf/fmaxf above drop NaNs).
+    bool sane = true;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sane = sane && fabsf(t.sx[i]) < kCoordLimit && fabsf(t.sy[i]) < kCoordLimit;
+    if (!sane) return;
+    int r0, r1;
+    if (mode == 0) { r0 = (int)ceilf(ymin - kEps - 0.5f); r1 = (int)floorf(ymax + kEps + 0.5f); }
+    else           { r0 = (int)floorf(ymin - kEps);       r1 = (int)floorf(ymax + kEps) + 1; }
+    const int rows = r1 - r0 + 1;
+    if (rows < 1 || rows > kMaxRows) return;
+    // Upper bound of any row's column span.  Inside a slab of height s in source y,
+    // eliminating yc gives sx = (a - b d / e) xc + (b / e) sy + const and eliminating xc
+    // gives sx = (b - a e / d) yc + (a / d) sy + const; either bounds the span.
+    const float s = (mode == 0 ? 1.0f : 2.0f) + 2.0f * kEps;
+    const float dx = xc1 - xc0, dy = yc1 - yc0;
+    float span = INFINITY;
+    if (m[4] != 0.0f) span = fminf(span, fabsf(m[0] - m[1] * m[3] / m[4]) * dx + fabsf(m[1] / m[4]) * s);
+    if (m[3] != 0.0f) span = fminf(span, fabsf(m[1] - m[0] * m[4] / m[3]) * dy + fabsf(m[0] / m[3]) * s);
+    span = fminf(span, xmax - xmin);
+    // + 2 eps, + the second tap / rounding to nearest, + rounding both ends to whole chunks
+    if (!(span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)kPitch)) return;
+    t.row0 = r0;
+    t.rows = rows;
+}
+
+// Columns [xs, xe) of source row row0 + r that the tile reads, rounded outward to
+// whole chunks.  xs is a multiple of `chunk` (floor division, so also for negative
+// columns).  A row no pixel reads gets xe == xs.
+TA_HD void tile_row_range(const TileFootprint &t, int mode, int chunk, int r, int &xs, int &xe)
+{
+    const float yr = (float)(t.row0 + r);
+    const float ya = yr - (mode == 0 ? 0.5f : 1.0f) - kEps;
+    const float yb = yr + (mode == 0 ? 0.5f : 1.0f) + kEps;
+    float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int j = (i + 1) & 3;
+        const float yi = t.sy[i], yj = t.sy[j];
+        if ((yi < ya && yj < ya) || (yi > yb && yj > yb)) continue;
+        float t0 = 0.0f, t1 = 1.0f;
+        if (t.inv[i] != 0.0f) {
+            const float ta = (ya - yi) * t.inv[i], tb = (yb - yi) * t.inv[i];
+            t0 = fmaxf(0.0f, fminf(ta, tb));
+            t1 = fminf(1.0f, fmaxf(ta, tb));
+            if (!(t0 <= t1)) continue;
+        }
+        const float dxs = t.sx[j] - t.sx[i];
+        const float xa = t.sx[i] + t0 * dxs, xb = t.sx[i] + t1 * dxs;
+        lo = fminf(lo, fminf(xa, xb));
+        hi = fmaxf(hi, fmaxf(xa, xb));
+    }
+    if (!(lo <= hi)) { xs = 0; xe = 0; return; }
+    int c0, c1;   // inclusive column range
+    if (mode == 0) { c0 = (int)ceilf(lo - kEps - 0.5f); c1 = (int)floorf(hi + kEps + 0.5f); }
+    else           { c0 = (int)floorf(lo - kEps);       c1 = (int)floorf(hi + kEps) + 1; }
+    // floor / ceil to chunk multiples, valid for negative columns
+    int q0 = c0 >= 0 ? c0 / chunk : -((-c0 + chunk - 1) / chunk);
+    int q1 = c1 + 1 >= 0 ? (c1 + 1 + chunk - 1) / chunk : -((-(c1 + 1)) / chunk);
+    xs = q0 * chunk;
+    xe = q1 * chunk;
+    if (xe - xs > kPitch) xe = xs + kPitch;   // cannot happen when tile_footprint() accepted the tile
+}
+
+}  // namespace ta
