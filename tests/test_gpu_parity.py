@@ -96,7 +96,8 @@ def test_golden_cases_vs_reference_outputs(fused_golden):
         a = _run_oracle(case, fma=True).astype(np.float32)
         b = _run_oracle(case, fma=False).astype(np.float32)
         same = np.abs(a - b) <= 1e-7
-        assert same.mean() > 0.97, name
+        # nearest: a flipped rounding moves a few texels; bilinear: any coordinate ulp shows
+        assert same.mean() > (0.80 if str(case["interp"]) == "bilinear" else 0.97), name
         assert float(np.abs(got - want)[same].max()) <= tol, name
 
 

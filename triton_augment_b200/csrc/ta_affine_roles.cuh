@@ -1,0 +1,163 @@
+// Producer and consumer roles of the staged affine kernel, and the kernel itself.
+#pragma once
+
+namespace ta {
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+// Two source coordinates at once with the packed fp32 pipe; per lane the operation order of
+// src_coord(): ((fma(xc, a, b*yc) + c) + half) + (-0.5), each step rounded to nearest.
+__device__ __forceinline__ float2 src_coord2(float xc, float a, float b, float2 yc, float c, float half)
+{
+    float2 u = __ffma2_rn(f2(xc, xc), f2(a, a), __fmul2_rn(f2(b, b), yc));
+    u = __fadd2_rn(u, f2(c, c));
+    u = __fadd2_rn(f2(half, half), u);
+    return __fadd2_rn(u, f2(-0.5f, -0.5f));
+}
+
+}  // namespace ta
+
+#include "ta_affine_producer.cuh"
+
+namespace ta {
+
+// ----------------------------------------------------------------------------- consumer
+template <typename T, int C, int MODE, unsigned F, bool CHECK>
+__device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
+                                                volatile int *abort_flag)
+{
+    using Info = TileInfo<T, C, F>;
+    constexpr size_t STAGE = AffineSmem<T, C, F>::stage;
+    constexpr int ROWS_PER_WARP = kTileH / (kConsumerWarps / 2);     // 4
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wx = warp & 1, wy = warp >> 1;
+    const unsigned oplane = (unsigned)(k.oh * k.ow);
+    unsigned long long n_viol = 0;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
+        const int s = it % kStages, use = it / kStages;
+        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
+        const T *stage = reinterpret_cast<const T *>(smem + s * STAGE);
+        const Info *ti = reinterpret_cast<const Info *>(smem + s * STAGE + (size_t)C * kPlane * sizeof(T));
+        const Geom g = ti->g;
+        const Colour<T, C, F> col = ti->col;
+        const int n = ti->n, rows = ti->rows, row0 = ti->row0;
+        const int x = ti->x0 + wx * 32 + lane;
+        const int y_first = ti->y0 + wy * ROWS_PER_WARP;
+
+        if (rows == 0) {
+            affine_rows_direct<T, C, MODE, F>(k, g, col, n, x, y_first, ROWS_PER_WARP);
+        } else if (x < k.ow) {
+            T *out = (T *)k.out + (size_t)n * C * oplane;
+            const float xc = centred(img_x(g, k.ow, x), g.half_w);
+#pragma unroll
+            for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
+                const int ya = y_first + 2 * pr;
+                if (ya >= k.oh) break;
+                const bool b_ok = ya + 1 < k.oh;
+                const int yb = b_ok ? ya + 1 : ya;           // keep the second lane on valid geometry
+                const float2 yc = f2(centred(img_y(g, ya), g.half_h), centred(img_y(g, yb), g.half_h));
+                const float2 sx = src_coord2(xc, g.a, g.b, yc, g.c, g.half_w);
+                const float2 sy = src_coord2(xc, g.d, g.e, yc, g.f, g.half_h);
+                T smp[2][C];
+                if (MODE == 1) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int xn = __float2int_rn(j ? sx.y : sx.x);
+                        int r = __float2int_rn(j ? sy.y : sy.x) - row0;
+                        if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
+                        int idx = ti->rowoff[r] + xn;
+                        if (CHECK && (unsigned)(idx - r * ti->bw) >= (unsigned)ti->bw) { ++n_viol; idx = 0; }
+#pragma unroll
+                        for (int c = 0; c < C; ++c) smp[j][c] = stage[c * kPlane + idx];
+                    }
+                } else {
+                    int i0[2], i1[2];
+                    float2 dx, dy;
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const float fx = j ? sx.y : sx.x, fy = j ? sy.y : sy.x;
+                        const int x0 = __float2int_rd(fx), y0 = __float2int_rd(fy);
+                        (j ? dx.y : dx.x) = fx - (float)x0;
+                        (j ? dy.y : dy.x) = fy - (float)y0;
+                        int r = y0 - row0;
+                        if (CHECK && (unsigned)r >= (unsigned)(rows - 1)) { ++n_viol; r = 0; }
+                        i0[j] = ti->rowoff[r] + x0;
+                        i1[j] = ti->rowoff[r + 1] + x0;
+                        if (CHECK && ((unsigned)(i0[j] - r * ti->bw) >= (unsigned)(ti->bw - 1) ||
+                                      (unsigned)(i1[j] - (r + 1) * ti->bw) >= (unsigned)(ti->bw - 1))) {
+                            ++n_viol; i0[j] = i1[j] = 0;
+                        }
+                    }
+                    const float2 one = f2(1.0f, 1.0f), neg = f2(-1.0f, -1.0f);
+                    const float2 omx = __ffma2_rn(dx, neg, one), omy = __ffma2_rn(dy, neg, one);   // 1 - d, one rounding
+                    const float2 w00 = __fmul2_rn(omx, omy), w10 = __fmul2_rn(dx, omy);
+                    const float2 w01 = __fmul2_rn(omx, dy), w11 = __fmul2_rn(dx, dy);
+#pragma unroll
+                    for (int c = 0; c < C; ++c) {
+                        const T *pl = stage + c * kPlane;
+                        float2 acc = __fmul2_rn(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
+                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
+                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
+                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
+                        smp[0][c] = Elem<T>::from_f(acc.x);
+                        smp[1][c] = Elem<T>::from_f(acc.y);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    float v[C];
+                    col.apply(k, smp[j], v);
+                    if (j == 0 || b_ok) {
+                        const unsigned o = (unsigned)((ya + j) * k.ow + x);
+#pragma unroll
+                        for (int c = 0; c < C; ++c) Elem<T>::store(out + (size_t)c * oplane + o, v[c]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
+}
+
+// ----------------------------------------------------------------------------- kernel
+template <typename T, int C, int MODE, unsigned F, bool CHECK>
+__global__ void __launch_bounds__(kAffineThreads, 1)
+affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
+{
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) uint64_t full[kStages];
+    __shared__ __align__(8) uint64_t empty[kStages];
+    __shared__ int abort_flag;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], kConsumerWarps);
+        }
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if ((threadIdx.x >> 5) >= kConsumerWarps)
+        affine_producer<T, C, MODE, F>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
+    else
+        affine_consumer<T, C, MODE, F, CHECK>(k, smem, full, empty, &abort_flag);
+
+    // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
+    // memory: give each stage one more bounded chance to settle before the memory is released.
+    __syncthreads();
+    if (abort_flag) {
+        if (threadIdx.x == 0 && k.counters) atomicAdd(k.counters + kCntTimeout, 1ull);
+        if (threadIdx.x < kStages) {
+            for (int i = 0; i < 4096; ++i)
+                if (mbar_try_wait(&full[threadIdx.x], 0) || mbar_try_wait(&full[threadIdx.x], 1)) break;
+        }
+    }
+}
+
+}  // namespace ta

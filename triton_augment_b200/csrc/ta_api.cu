@@ -1,7 +1,9 @@
 // extern "C" entry points of libta_b200.so (declared in include/ta_b200.h):
 // argument checking, kernel selection, launch shapes, and the two small helper
 // kernels (per-image grayscale mean, inverse affine matrices).
+#include <cuda.h>
 #include <cuda_runtime.h>
+#include <limits.h>
 #include <math.h>
 #include <stdarg.h>
 #include <stdio.h>
@@ -81,28 +83,22 @@ static const KernelTable &table_for(int kind, int dtype)
     return kind == 0 ? table_f16_direct() : kind == 1 ? table_f16_nearest() : table_f16_bilinear();
 }
 
-static size_t smem_for(int kind, int dtype, int c)
-{
-    if (kind == 0) return 0;
-    const size_t es = dtype == TA_B200_F32 ? 4 : 2;
-    return (size_t)c * kMaxRows * kPitch * es + (size_t)(kMaxRows + 4) * sizeof(int);
-}
-
 // Resident CTAs per SM for a kernel, computed once per device; also opts the kernel in
 // to its dynamic shared memory size on that device.
-static int prepare_kernel(DeviceState &s, const void *fn, int kind, int dtype, int c, unsigned slot, int *blocks)
+static int prepare_kernel(DeviceState &s, const KernelEntry &ke, int kind, int dtype, int c, unsigned slot, int *blocks)
 {
     std::lock_guard<std::mutex> lock(s.mu);
     unsigned char &cached = s.blocks_per_sm[kind][dtype][c == 3][slot];
     if (cached == 0) {
-        const size_t smem = smem_for(kind, dtype, c);
+        const size_t smem = ke.smem;
+        const void *fn = ke.fn;
         cudaError_t e;
         if (smem > 0) {
             e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(shared memory)");
         }
         int nb = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, kThreads, smem);
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, fn, ke.threads, smem);
         if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor");
         if (nb < 1) return fail(TA_B200_ERR_CUDA, "kernel does not fit on an SM");
         cached = (unsigned char)(nb > 255 ? 255 : nb);
@@ -174,6 +170,44 @@ static unsigned template_flags(const ta_b200_fused_params *p)
     return f;
 }
 
+// cuTensorMapEncodeTiled, fetched through the runtime so the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return (EncodeTiledFn)sym;
+    }();
+    return fn;
+}
+
+// Tensor maps over the input seen as [n*c, h, w]: boxes of box_width(i) x 8 rows x 1 plane,
+// out-of-range elements read as zero.
+static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
+{
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
+    const cuuint64_t dims[3] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->n * p->c};
+    const cuuint64_t strides[2] = {(cuuint64_t)p->w * es, (cuuint64_t)p->w * p->h * es};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    for (int i = 0; i < kNumBoxWidths; ++i) {
+        const cuuint32_t box[3] = {(cuuint32_t)box_width(i), (cuuint32_t)kGroupRows, 1};
+        CUresult r = enc(&maps.m[i], p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         3, const_cast<void *>(p->in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    }
+    return TA_B200_OK;
+}
+
 static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool checked)
 {
     int rc = validate(p);
@@ -186,18 +220,18 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     const int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
     unsigned f = template_flags(p);
     const KernelTable &tab = table_for(kind, p->dtype);
-    const void *fn;
     unsigned slot = f;
+    const KernelEntry *ke;
     if (checked && kind != 0) {
         if (f != 0) return fail(TA_B200_ERR_UNSUPPORTED, "checked staging build exists for apply == 0 only");
-        fn = p->c == 3 ? tab.c3_checked : tab.c1_checked;
+        ke = p->c == 3 ? &tab.c3_checked : &tab.c1_checked;
         slot = kNumFlagCombos;
     } else {
-        fn = p->c == 3 ? tab.c3[f] : tab.c1[f];
+        ke = p->c == 3 ? &tab.c3[f] : &tab.c1[f];
     }
-    if (!fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
+    if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;
-    rc = prepare_kernel(*s, fn, kind, p->dtype, p->c, slot, &blocks);
+    rc = prepare_kernel(*s, *ke, kind, p->dtype, p->c, slot, &blocks);
     if (rc != TA_B200_OK) return rc;
 
     KArgs k;
@@ -219,8 +253,24 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     long long grid = (long long)s->sm_count * blocks;
     if (grid > work) grid = work;
     if (grid < 1) grid = 1;
-    void *args[] = {&k};
-    cudaError_t e = cudaLaunchKernel(fn, dim3((unsigned)grid), dim3(kThreads), args, smem_for(kind, p->dtype, p->c), stream);
+    cudaError_t e;
+    if (kind == 0) {
+        void *args[] = {&k};
+        e = cudaLaunchKernel(ke->fn, dim3((unsigned)grid), dim3(ke->threads), args, ke->smem, stream);
+    } else {
+        TMaps maps;
+        memset(&maps, 0, sizeof(maps));
+        if (k.staged_ok) {
+            // dimensions beyond what a tensor map can describe: gather everything directly
+            if ((double)p->n * p->c >= 2147483648.0) k.staged_ok = 0;
+            else {
+                rc = build_tensor_maps(maps, p);
+                if (rc != TA_B200_OK) return rc;
+            }
+        }
+        void *args[] = {&k, &maps};
+        e = cudaLaunchKernel(ke->fn, dim3((unsigned)grid), dim3(ke->threads), args, ke->smem, stream);
+    }
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernel(fused)");
     return TA_B200_OK;
 }

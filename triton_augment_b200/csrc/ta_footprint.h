@@ -27,8 +27,11 @@ namespace ta {
 
 constexpr int kTileW = 64;       // output tile, pixels
 constexpr int kTileH = 32;
-constexpr int kMaxRows = 60;     // source rows one staged tile may span
-constexpr int kPitch = 96;       // elements reserved per staged source row
+constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 groups of 8 rows)
+constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
+constexpr int kPitch = 96;       // widest staged row, in elements
+constexpr int kNumBoxWidths = 3; // tensor-copy box widths to choose from per tile
+TA_HD int box_width(int i) { return i == 0 ? 72 : i == 1 ? 80 : kPitch; }
 constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
 constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
 
@@ -94,12 +97,20 @@ TA_HD void tile_footprint(TileFootprint &t, int mode, int chunk, int h, int w, i
 
 // Columns [xs, xe) of source row row0 + r that the tile reads, rounded outward to
 // whole chunks.  xs is a multiple of `chunk` (floor division, so also for negative
-// columns).  A row no pixel reads gets xe == xs.
-TA_HD void tile_row_range(const TileFootprint &t, int mode, int chunk, int r, int &xs, int &xe)
+// columns).  Returns false (and xe == xs == 0) for a row no pixel reads.
+TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_first, int r_last, int &xs, int &xe);
+
+TA_HD bool tile_row_range(const TileFootprint &t, int mode, int chunk, int r, int &xs, int &xe)
 {
-    const float yr = (float)(t.row0 + r);
-    const float ya = yr - (mode == 0 ? 0.5f : 1.0f) - kEps;
-    const float yb = yr + (mode == 0 ? 0.5f : 1.0f) + kEps;
+    return tile_rows_range(t, mode, chunk, r, r, xs, xe);
+}
+
+// Same for the union of rows row0 + r_first .. row0 + r_last: the pixels that read any of
+// them lie in one (thicker) slab, so it is the same clip.
+TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_first, int r_last, int &xs, int &xe)
+{
+    const float ya = (float)(t.row0 + r_first) - (mode == 0 ? 0.5f : 1.0f) - kEps;
+    const float yb = (float)(t.row0 + r_last) + (mode == 0 ? 0.5f : 1.0f) + kEps;
     float lo = INFINITY, hi = -INFINITY;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -118,7 +129,7 @@ TA_HD void tile_row_range(const TileFootprint &t, int mode, int chunk, int r, in
         lo = fminf(lo, fminf(xa, xb));
         hi = fmaxf(hi, fmaxf(xa, xb));
     }
-    if (!(lo <= hi)) { xs = 0; xe = 0; return; }
+    if (!(lo <= hi)) { xs = 0; xe = 0; return false; }
     int c0, c1;   // inclusive column range
     if (mode == 0) { c0 = (int)ceilf(lo - kEps - 0.5f); c1 = (int)floorf(hi + kEps + 0.5f); }
     else           { c0 = (int)floorf(lo - kEps);       c1 = (int)floorf(hi + kEps) + 1; }
@@ -127,7 +138,27 @@ TA_HD void tile_row_range(const TileFootprint &t, int mode, int chunk, int r, in
     int q1 = c1 + 1 >= 0 ? (c1 + 1 + chunk - 1) / chunk : -((-(c1 + 1)) / chunk);
     xs = q0 * chunk;
     xe = q1 * chunk;
-    if (xe - xs > kPitch) xe = xs + kPitch;   // cannot happen when tile_footprint() accepted the tile
+    return true;
+}
+
+// What is actually fetched: rows in groups of kGroupRows, every group one box whose first
+// column is the smallest xs of its rows and whose width is the narrowest box_width() that
+// covers the widest group.  Scalar restatement of what the producer warp computes with
+// shuffles; returns the box width, or 0 when some group is wider than the widest box
+// (then the tile is not staged).  group_xs has kMaxRows / kGroupRows entries.
+TA_HD int tile_group_plan(const TileFootprint &t, int mode, int chunk, int *group_xs)
+{
+    int wmax = 0;
+    for (int g = 0; g < kMaxRows / kGroupRows; ++g) {
+        int lo = 0, hi = chunk;
+        const int r_first = g * kGroupRows;
+        const int r_last = r_first + kGroupRows - 1 < t.rows - 1 ? r_first + kGroupRows - 1 : t.rows - 1;
+        if (r_first >= t.rows || !tile_rows_range(t, mode, chunk, r_first, r_last, lo, hi)) { lo = 0; hi = chunk; }
+        group_xs[g] = lo;
+        wmax = hi - lo > wmax ? hi - lo : wmax;
+    }
+    if (wmax > kPitch) return 0;
+    return wmax <= box_width(0) ? box_width(0) : wmax <= box_width(1) ? box_width(1) : box_width(2);
 }
 
 }  // namespace ta

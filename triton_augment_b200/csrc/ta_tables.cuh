@@ -1,7 +1,7 @@
 // Kernel tables.  Every (element type, kind, channels, colour flags) combination is its
 // own kernel so that disabled operations cost nothing; each translation unit
 // instantiates one (element type, kind) slice and exposes it as a table of function
-// pointers indexed by the flag bits.
+// pointers (and their dynamic shared memory sizes) indexed by the flag bits.
 #pragma once
 
 #include <utility>
@@ -13,11 +13,17 @@ namespace ta {
 
 constexpr int kNumFlagCombos = 64;   // kB | kC | kS | kG | kN | kMean
 
+struct KernelEntry {
+    const void *fn;      // nullptr: combination does not exist
+    size_t smem;         // dynamic shared memory
+    int threads;         // CTA size
+};
+
 struct KernelTable {
-    const void *c3[kNumFlagCombos];
-    const void *c1[kNumFlagCombos];
-    const void *c3_checked;          // affine only, flags 0, staging asserts on
-    const void *c1_checked;
+    KernelEntry c3[kNumFlagCombos];
+    KernelEntry c1[kNumFlagCombos];
+    KernelEntry c3_checked;          // affine only, flags 0, staging assertions on
+    KernelEntry c1_checked;
 };
 
 constexpr bool flags_valid(int channels, unsigned f)
@@ -28,23 +34,24 @@ constexpr bool flags_valid(int channels, unsigned f)
 }
 
 // KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear
-template <typename T, int C, int KIND, unsigned F> const void *kernel_ptr()
+template <typename T, int C, int KIND, unsigned F, bool CHECK = false> KernelEntry kernel_entry()
 {
-    if constexpr (!flags_valid(C, F)) return nullptr;
-    else if constexpr (KIND == 0) return (const void *)&direct_kernel<T, C, F>;
-    else return (const void *)&affine_kernel<T, C, KIND, F, false>;
+    if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
+    else if constexpr (KIND == 0) return KernelEntry{(const void *)&direct_kernel<T, C, F>, 0, kThreads};
+    else return KernelEntry{(const void *)&affine_kernel<T, C, KIND, F, CHECK>, AffineSmem<T, C, F>::total,
+                            kAffineThreads};
 }
 
 template <typename T, int KIND, unsigned... Fs>
 void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
 {
-    ((t.c3[Fs] = kernel_ptr<T, 3, KIND, Fs>()), ...);
-    ((t.c1[Fs] = kernel_ptr<T, 1, KIND, Fs>()), ...);
+    ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs>()), ...);
+    ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs>()), ...);
     if constexpr (KIND != 0) {
-        t.c3_checked = (const void *)&affine_kernel<T, 3, KIND, 0u, true>;
-        t.c1_checked = (const void *)&affine_kernel<T, 1, KIND, 0u, true>;
+        t.c3_checked = kernel_entry<T, 3, KIND, 0u, true>();
+        t.c1_checked = kernel_entry<T, 1, KIND, 0u, true>();
     } else {
-        t.c3_checked = t.c1_checked = nullptr;
+        t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
     }
 }
 
