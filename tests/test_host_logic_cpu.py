@@ -1,0 +1,150 @@
+"""Host-side logic that needs no GPU: random-draw order against parameters captured from the
+reference's classes, shape / broadcast rules, argument validation, sharding arithmetic, and
+that the C-ABI library exports everything its header declares."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import triton_augment_b200 as ta
+from triton_augment_b200 import _lib, transforms as T
+from triton_augment_b200.multi_gpu import shard_bounds, slice_params
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SPEC_PATH = os.path.join(ROOT, "tests", "golden", "make_golden.py")
+
+
+def _class_specs():
+    """CLASS_SPECS of the generator script, read without importing it (it needs the reference)."""
+    src = open(SPEC_PATH).read()
+    start = src.index("CLASS_SPECS = {")
+    end = src.index("\n}\n", start) + 3
+    ns = {"MEAN": (0.485, 0.456, 0.406), "STD": (0.229, 0.224, 0.225)}
+    exec(src[start:end], ns)
+    return ns["CLASS_SPECS"]
+
+
+SPECS = _class_specs()
+
+
+@pytest.mark.parametrize("key", sorted(SPECS))
+def test_random_draw_order_matches_reference(class_golden, key):
+    """Same seed on the CPU generator -> bit-identical sampled parameters (count 7, 20x24 image)."""
+    cls_name, kwargs = SPECS[key]
+    tr = getattr(ta, cls_name)(**kwargs)
+    if not hasattr(tr, "_get_params") or f"params|{key}|seed" not in class_golden.files:
+        pytest.skip("class draws inside forward only")
+    torch.manual_seed(int(class_golden[f"params|{key}|seed"]))
+    try:
+        params = tr._get_params(7, torch.device("cpu"), (20, 24))
+    except TypeError:
+        params = tr._get_params(7, torch.device("cpu"))
+    for i, p in enumerate(params):
+        want = class_golden[f"params|{key}|{i}"]
+        assert np.array_equal(np.asarray(p), want), (key, i)
+
+
+def test_param_count_and_broadcast_rules():
+    cnt = T._compute_param_count
+    assert cnt(None, None, False, True) == 1
+    assert (cnt(4, None, False, True), cnt(4, None, True, True)) == (4, 1)
+    assert [cnt(2, 3, sb, sf) for sb, sf in ((True, True), (True, False), (False, True), (False, False))] == [1, 3, 2, 6]
+    p = torch.tensor([10.0, 20.0])
+    out = T._broadcast_params_to_all_samples(p, 2, 3, 6, False, True)       # per video, video-major
+    assert out.tolist() == [10, 10, 10, 20, 20, 20]
+    q = torch.tensor([1.0, 2.0, 3.0])
+    out = T._broadcast_params_to_all_samples(q, 2, 3, 6, True, False)       # per frame index
+    assert out.tolist() == [1, 2, 3, 1, 2, 3]
+    assert T._broadcast_params_to_all_samples(torch.tensor([7.0]), 2, 3, 6, True, True).tolist() == [7.0] * 6
+    full = torch.arange(6.0)
+    assert T._broadcast_params_to_all_samples(full, 2, 3, 6, False, False) is full
+    with pytest.raises(ValueError):
+        T._broadcast_params_to_all_samples(torch.zeros(4), 2, 3, 6, False, True)
+    two = T._broadcast_2d_params(torch.tensor([[1.0, 2.0], [3.0, 4.0]]), 2, 2, 4, False, True)
+    assert two.tolist() == [[1, 2], [1, 2], [3, 4], [3, 4]]
+    with pytest.raises(ValueError):
+        T._normalize_video_shape(torch.zeros(2, 2))
+
+
+def test_constructor_validation_matches_reference():
+    with pytest.raises(ValueError):
+        ta.TritonColorJitter(brightness=-0.1)
+    with pytest.raises(TypeError):
+        ta.TritonColorJitter(contrast="x")
+    with pytest.raises(ValueError):
+        ta.TritonColorJitterNormalize(grayscale_p=1.5)
+    with pytest.raises(ValueError):
+        ta.TritonColorJitterNormalize(mean=(0.5, 0.5, 0.5))
+    with pytest.raises(ValueError):
+        ta.TritonRandomAffine(degrees=-1)
+    with pytest.raises(ValueError):
+        ta.TritonRandomAffine(degrees=10, translate=(0.5, 1.5))
+    with pytest.raises(ValueError):
+        ta.TritonRandomAffine(degrees=10, scale=(1.2, 0.8))
+    with pytest.raises(ValueError):
+        ta.TritonRandomAffine(degrees=10, shear=(1, 2, 3))
+    with pytest.raises(NotImplementedError):
+        ta.TritonRandomRotation(10, expand=True)
+    with pytest.raises(ValueError):
+        ta.TritonRandomHorizontalFlip(p=2)
+    with pytest.raises(ValueError):
+        ta.TritonGrayscale(num_output_channels=2)
+    with pytest.raises(ValueError):
+        ta.TritonFusedAugment(contrast_mode="nope")
+    assert ta.TritonColorJitter(brightness=0).brightness is None            # (1, 1) cannot change anything
+    assert ta.TritonColorJitter(brightness=0.2).brightness == (0.8, 1.2)
+    assert ta.TritonRandomAffine(5, shear=3).shear == (-3.0, 3.0, 0.0, 0.0)
+    assert "TritonFusedAugment(" in repr(ta.TritonFusedAugment(crop_size=8, brightness=0.1))   # reference's repr raises
+
+
+def test_functional_argument_errors_without_a_gpu():
+    img = torch.rand(1, 3, 4, 4)
+    with pytest.raises(TypeError):
+        ta.fused_augment([1, 2], 0, 0, 4, 4)
+    with pytest.raises(ValueError, match="CUDA"):
+        ta.fused_augment(img, 0, 0, 4, 4)                 # no CPU fallback, same error as the reference
+    with pytest.raises(ValueError):
+        ta.adjust_brightness(img, 1.2)
+    with pytest.raises(ValueError):
+        ta.TritonGrayscale()(img)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            ta.TritonFusedAugment(crop_size=2)(img)       # class API uploads host tensors; needs CUDA
+
+
+def test_inverse_matrix_matches_torchvision_and_golden(functional_golden):
+    z = functional_golden
+    t = lambda k: torch.from_numpy(z[k])
+    got = ta.functional._get_inverse_affine_matrix(t("mat_center"), t("mat_angle"), t("mat_translate"),
+                                                   t("mat_scale"), t("mat_shear"))
+    assert np.array_equal(got.numpy(), z["mat_out"])     # same torch ops, same order, same device -> same bits
+    from torchvision.transforms.functional import _get_inverse_affine_matrix as tv_inv
+    for i in range(4):
+        want = tv_inv(z["mat_center"][i].tolist(), float(z["mat_angle"][i]), z["mat_translate"][i].tolist(),
+                      float(z["mat_scale"][i]), z["mat_shear"][i].tolist())
+        np.testing.assert_allclose(got[i].numpy(), np.array(want, np.float32), rtol=1e-4, atol=1e-4)
+
+
+def test_shard_bounds():
+    assert shard_bounds(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert shard_bounds(4096, 8) == [(i * 512, (i + 1) * 512) for i in range(8)]
+    assert shard_bounds(2, 4) == [(0, 1), (1, 2), (2, 2), (2, 2)]
+    assert shard_bounds(8 * 16, 3, group=16) == [(0, 48), (48, 96), (96, 128)]      # whole videos per GPU
+    with pytest.raises(ValueError):
+        shard_bounds(10, 2, group=4)
+    p = slice_params((torch.arange(6.0), 1.0, torch.arange(12.0).reshape(6, 2)), 2, 5)
+    assert p[0].tolist() == [2, 3, 4] and p[1] == 1.0 and p[2].shape == (3, 2)
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "ta_b200.h")).read()
+    declared = set(re.findall(r"\b(ta_b200_[a-z_0-9]+)\s*\(", header))
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert _lib.load().ta_b200_abi_version() == _lib.ABI_VERSION
+    assert ctypes.sizeof(_lib.FusedParams) == 168       # sizeof(ta_b200_fused_params) on LP64

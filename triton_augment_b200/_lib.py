@@ -130,6 +130,13 @@ def launch_fused(params: FusedParams, device: torch.device, checked: bool = Fals
         check(fn(C.byref(params), stream), "ta_b200_fused_augment")
 
 
+def launch_fused_host(params: FusedParams, device: torch.device) -> None:
+    """Host-buffer entry point: every pointer in ``params`` is a host pointer; uploads, runs
+    and downloads slice by slice on ``device`` and returns when the output is complete."""
+    with torch.cuda.device(device):
+        check(load().ta_b200_fused_augment_host(C.byref(params)), "ta_b200_fused_augment_host")
+
+
 def launch_gray_mean(params: FusedParams, device: torch.device) -> torch.Tensor:
     """Run the grayscale-mean pre-pass; returns the fp32 ``[n]`` means on ``device``."""
     lib = load()

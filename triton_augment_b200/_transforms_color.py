@@ -56,7 +56,7 @@ class TritonColorJitter(_JitterBase):
 
     def forward(self, img: torch.Tensor) -> torch.Tensor:
         lay = self._layout(img)
-        b, c, s = (lay.spread(p) for p in self._get_params(lay.count, lay.image.device))
+        b, c, s = (lay.spread(p) for p in self._get_params(lay.count, lay.param_device))
         h, w = lay.image.shape[2:]
         out = F.fused_augment(lay.image, top=0, left=0, height=h, width=w, flip_horizontal=False,
                               brightness_factor=b, contrast_factor=c, saturation_factor=s, grayscale=False,
@@ -119,7 +119,7 @@ class TritonColorJitterNormalize(_JitterBase):
 
     def forward(self, img: torch.Tensor) -> torch.Tensor:
         lay = self._layout(img)
-        b, c, s, g = (lay.spread(p) for p in self._get_params(lay.count, lay.image.device))
+        b, c, s, g = (lay.spread(p) for p in self._get_params(lay.count, lay.param_device))
         h, w = lay.image.shape[2:]
         out = F.fused_augment(lay.image, top=0, left=0, height=h, width=w, flip_horizontal=False,
                               brightness_factor=b, contrast_factor=c, saturation_factor=s, grayscale=g,
@@ -168,7 +168,7 @@ class TritonRandomGrayscale(T._BatchAware):
         if self.p == 0:
             return image
         lay = self._layout(image, upload=False)
-        mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.image.device))
+        mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.param_device))
         if not torch.any(mask).item():
             return image
         out = F.rgb_to_grayscale(lay.image, num_output_channels=self.num_output_channels, grayscale_mask=mask)

@@ -104,8 +104,54 @@ class TritonFusedAugment(T._BatchAware):
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         lay = self._layout(image)
         h, w = lay.image.shape[2:]
-        params = self._get_params(lay.count, lay.image.device, (h, w))
+        params = self._get_params(lay.count, lay.param_device, (h, w))
         return lay.restore(self._apply(lay.image, self._spread_all(lay, params)))
+
+    def forward_host(self, image: torch.Tensor, out: Optional[torch.Tensor] = None, device=None) -> torch.Tensor:
+        """Host tensor in, host tensor out (extra; the reference's ``forward`` uploads a host
+        batch and leaves the result on the GPU).  Parameters are drawn on ``device`` exactly
+        as in ``forward``; the images then flow host -> GPU -> host in slices through the
+        library's pipelined entry point, so the copies in both directions overlap the kernel.
+        Use pinned memory for ``image`` and ``out`` to get full PCIe speed."""
+        from . import _lib
+        if image.is_cuda:
+            raise ValueError("forward_host takes a host tensor; use forward() for CUDA tensors")
+        if not torch.cuda.is_available():
+            raise RuntimeError("Triton-Augment requires CUDA, but CUDA is not available.")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        lay = T._Layout(image, self.same_on_batch, self.same_on_frame, upload=False)
+        flat = lay.image.contiguous()
+        F_ = F
+        if flat.ndim != 4 or flat.shape[1] not in (1, 3) or flat.dtype not in (torch.float32, torch.float16):
+            raise ValueError(f"expected float32/float16 images with 1 or 3 channels, got {tuple(image.shape)} {image.dtype}")
+        n, c, h, w = flat.shape
+        oh = self.crop_height if self.crop_height is not None else h
+        ow = self.crop_width if self.crop_width is not None else w
+        params = self._spread_all(lay, self._get_params(lay.count, dev, (h, w)))
+        angle, translate, scale, shear, top, left, flip, b, cf, s, g = params
+        matrix = None
+        if self.has_affine:
+            matrix = F_._prepare_affine_matrix_only(n, dev, h, w, angle, translate, scale, shear, None).cpu().contiguous()
+        flags = self.color_helper._colour_flags(affine=self.has_affine)
+        mean, std = self.color_helper.mean, self.color_helper.std
+        bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
+                | (_lib.APPLY_SATURATION if flags["saturation"] else 0) | (_lib.APPLY_GRAYSCALE if flags["grayscale"] else 0)
+                | (_lib.APPLY_NORMALIZE if mean is not None else 0))
+        if out is None:
+            out = torch.empty((n, c, oh, ow), dtype=flat.dtype, pin_memory=True)
+        elif out.is_cuda or not out.is_contiguous() or out.numel() != n * c * oh * ow or out.dtype != flat.dtype:
+            raise ValueError("out must be a contiguous host tensor with the output's size and dtype")
+        host = lambda t, dt: t.to(dtype=dt).cpu().contiguous()
+        keep = [host(top, torch.float32), host(left, torch.float32), host(flip, torch.uint8), matrix,
+                host(b, flat.dtype), host(cf, flat.dtype), host(s, flat.dtype), host(g, torch.uint8)]
+        p = _lib.make_params(flat, out.view(n, c, oh, ow), keep[0], keep[1], keep[2], keep[3],
+                             self.fill if self.has_affine else 0.0,
+                             self.has_affine and F_._is_bilinear(self.interpolation), bits, keep[4], keep[5], keep[6],
+                             keep[7], F_._rounded_triple(mean, flat.dtype) if mean is not None else None,
+                             F_._rounded_triple(std, flat.dtype) if std is not None else None,
+                             F_._contrast_mode(self.contrast_mode))
+        _lib.launch_fused_host(p, dev)
+        return lay.restore(out.view(n, c, oh, ow))
 
     def __repr__(self):
         ch = self.color_helper

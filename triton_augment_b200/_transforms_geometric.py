@@ -16,7 +16,7 @@ _NO_COLOUR = dict(brightness=False, contrast=False, saturation=False, grayscale=
 
 def _draw_offsets(lay, h, w, th, tw, dtype):
     """Two ``randint`` draws, top then left (transforms.py:972-973, 1210-1211, 1464-1465)."""
-    dev = lay.image.device
+    dev = lay.param_device
     top = torch.randint(0, h - th + 1, (lay.count,), device=dev, dtype=dtype)
     left = torch.randint(0, w - tw + 1, (lay.count,), device=dev, dtype=dtype)
     return top, left
@@ -72,7 +72,7 @@ class TritonRandomHorizontalFlip(T._BatchAware):
         if self.p == 0:
             return image
         lay = self._layout(image)
-        mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.image.device))
+        mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.param_device))
         return lay.restore(F.horizontal_flip(lay.image, flip_mask=mask))
 
     def __repr__(self):
@@ -97,7 +97,7 @@ class TritonRandomCropFlip(T._BatchAware):
         if th > h or tw > w:
             raise ValueError(f"Crop size ({th}, {tw}) is larger than image size ({h}, {w})")
         top, left = _draw_offsets(lay, h, w, th, tw, torch.int32)
-        flip = F._sample_bernoulli_tensor(lay.count, self.horizontal_flip_p, lay.image.device)
+        flip = F._sample_bernoulli_tensor(lay.count, self.horizontal_flip_p, lay.param_device)
         out = F.fused_augment(lay.image, top=lay.spread(top), left=lay.spread(left), height=th, width=tw,
                               flip_horizontal=lay.spread(flip), brightness_factor=1.0, contrast_factor=1.0,
                               saturation_factor=1.0, grayscale=False, mean=None, std=None,
@@ -183,7 +183,7 @@ class TritonRandomAffine(T._BatchAware):
     def forward(self, img: torch.Tensor) -> torch.Tensor:
         lay = self._layout(img)
         h, w = lay.image.shape[2:]
-        angle, translate, scale, shear = self._get_params(lay.count, lay.image.device, (h, w))
+        angle, translate, scale, shear = self._get_params(lay.count, lay.param_device, (h, w))
         out = F.affine(lay.image, angle=lay.spread(angle), translate=lay.spread2(translate), scale=lay.spread(scale),
                        shear=lay.spread2(shear), interpolation=self.interpolation, fill=self.fill, center=self.center)
         return lay.restore(out)

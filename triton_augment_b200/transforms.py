@@ -137,9 +137,12 @@ def _size_pair(size):
 class _Layout:
     """Shape bookkeeping of one forward call."""
 
-    def __init__(self, image: torch.Tensor, same_on_batch: bool, same_on_frame: bool, upload: bool = True):
+    def __init__(self, image: torch.Tensor, same_on_batch: bool, same_on_frame: bool, upload: bool = True,
+                 param_device=None):
         flat, self.batch, self.frames, self.shape, self.was_3d = _normalize_video_shape(image)
         self.image = _ensure_cuda(flat) if upload else flat
+        # where the random parameters are drawn: the image's device, like the reference
+        self.param_device = self.image.device if param_device is None else torch.device(param_device)
         self.sob, self.sof = same_on_batch, same_on_frame
         self.total = self.image.shape[0]
         self.count = _compute_param_count(self.batch, self.frames, same_on_batch, same_on_frame)
@@ -155,13 +158,17 @@ class _Layout:
 
 
 class _BatchAware(nn.Module):
+    # Set to torch.device("cpu") to draw parameters from the CPU generator instead of the
+    # image's device (reproducible across machines; the tests use it).  None = reference behaviour.
+    _param_device = None
+
     def __init__(self, same_on_batch: bool = False, same_on_frame: bool = True):
         super().__init__()
         self.same_on_batch = same_on_batch
         self.same_on_frame = same_on_frame
 
     def _layout(self, image, upload=True) -> _Layout:
-        return _Layout(image, self.same_on_batch, self.same_on_frame, upload)
+        return _Layout(image, self.same_on_batch, self.same_on_frame, upload, self._param_device)
 
     def _tail(self):
         return f"same_on_batch={self.same_on_batch}, same_on_frame={self.same_on_frame})"
