@@ -125,6 +125,34 @@ int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out,
 size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p);
 
 /*
+ * ta_b200_gray_mean() for callers that cannot allocate device memory.  (No counterpart in
+ * the reference, which allocates freely through torch.)
+ *
+ * Some users of this library are handed their device memory once and may not ask for more:
+ * a plugin inside a host application that owns the CUDA allocator, a data-loading service
+ * whose memory budget is frozen after start-up, code that runs where a cudaMalloc would
+ * stall or is forbidden.  For them the scratch lives inside the library, in a fixed 1 MiB
+ * array of device memory that every GPU using the library holds from load to process exit.
+ * The call itself allocates nothing and frees nothing, on the host's CUDA heap or through
+ * any library; the caller still supplies the input image, the parameter vectors and
+ * mean_out[n], exactly as for ta_b200_gray_mean().
+ *
+ * Limit: counters plus partial sums must fit the array, i.e.
+ *     round_up(4 n, 256) + 4 n min(128, ceil(oh ow / 4096))  <=  1 048 576 bytes
+ * (for example about 18 700 images of 224x224, or 2032 images of 1024x1024).  A larger call is
+ * refused with TA_B200_ERR_TOO_LARGE and a message saying how much was needed; split the
+ * batch or use ta_b200_gray_mean() with your own scratch.
+ *
+ * The first call on each device looks up the array's device address (one runtime query,
+ * made with that device current).  Make that first call before starting any stream capture.
+ * All calls on a device share the one array and it keeps what the last call left in it: the
+ * part that must start at zero is cleared on `stream` at the start of every call, and two
+ * calls whose kernels can overlap on the GPU (different streams, no ordering between them)
+ * race on it and produce garbage - order them yourself.
+ */
+int ta_b200_gray_mean_static(const ta_b200_fused_params *p, float *mean_out, void *stream);
+
+/*
  * Host-buffer variant of ta_b200_fused_augment(): p->in and p->out are HOST
  * pointers (pinned memory gives full PCIe speed); every per-image vector and the
  * matrix are host pointers too.  The batch is cut into slices that flow through

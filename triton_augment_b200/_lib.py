@@ -23,7 +23,7 @@ APPLY_BRIGHTNESS, APPLY_CONTRAST, APPLY_SATURATION, APPLY_GRAYSCALE, APPLY_NORMA
 # Every symbol include/ta_b200.h declares.
 SYMBOLS = (
     "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
-    "ta_b200_gray_mean_scratch_bytes", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
+    "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
     "ta_b200_debug_tile_shape",
 )
@@ -70,6 +70,8 @@ def load():
     lib.ta_b200_gray_mean.restype = C.c_int
     lib.ta_b200_gray_mean_scratch_bytes.argtypes = [C.POINTER(FusedParams)]
     lib.ta_b200_gray_mean_scratch_bytes.restype = C.c_size_t
+    lib.ta_b200_gray_mean_static.argtypes = [C.POINTER(FusedParams), C.c_void_p, C.c_void_p]
+    lib.ta_b200_gray_mean_static.restype = C.c_int
     lib.ta_b200_fused_augment_host.argtypes = [C.POINTER(FusedParams)]
     lib.ta_b200_fused_augment_host.restype = C.c_int
     lib.ta_b200_inverse_affine_matrix.argtypes = [C.c_int32] + [C.c_void_p] * 7

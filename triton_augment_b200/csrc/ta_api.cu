@@ -278,3 +278,80 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
 }  // namespace ta
 
 #include "ta_api_helpers.cuh"
+
+// ----------------------------------------------------------------------------- allocation-free pre-pass
+// ta_b200_gray_mean_static(): the grayscale-mean pre-pass for callers that may not allocate.
+// Its scratch is this fixed array in device memory.  Every GPU that loads the library carries
+// the array until the process exits, and every call on a device uses the same bytes.
+namespace ta {
+
+constexpr size_t kStaticScratchBytes = 1u << 20;                       // 1 MiB per device
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address;
+// the address a kernel can use is looked up once per device, with that device current.
+static std::mutex g_static_mu;
+static void *g_static_ptr[kMaxDevices] = {};
+
+static int static_scratch_for_current_device(void **out)
+{
+    int d = -1;
+    cudaError_t e = cudaGetDevice(&d);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (d < 0 || d >= kMaxDevices) return fail(TA_B200_ERR_DEVICE, "device index %d not supported", d);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[d]) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, d);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+        if (major != 10) return fail(TA_B200_ERR_DEVICE, "device %d is not compute capability 10.x", d);
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (!ptr) return fail(TA_B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_ptr[d] = ptr;
+    }
+    *out = g_static_ptr[d];
+    return TA_B200_OK;
+}
+
+static int gray_mean_static(const ta_b200_fused_params *p, float *mean_out, cudaStream_t stream)
+{
+    int rc = validate_geometry_only(p);
+    if (rc != TA_B200_OK) return rc;
+    if (!mean_out) return fail(TA_B200_ERR_NULL, "mean_out is NULL");
+    if (p->n == 0) return TA_B200_OK;
+    if (p->n > 65535) return fail(TA_B200_ERR_TOO_LARGE, "at most 65535 images per call");
+    const int bpi = mean_blocks_per_image(p->oh, p->ow);
+    const size_t need = mean_partials_offset(p->n) + (size_t)p->n * bpi * sizeof(float);
+    if (need > kStaticScratchBytes)
+        return fail(TA_B200_ERR_TOO_LARGE,
+                    "this call needs %zu bytes of scratch but the built-in buffer holds %zu: pass fewer images per call "
+                    "(%d images of %dx%d need %d partial sums each) or use ta_b200_gray_mean with your own scratch",
+                    need, kStaticScratchBytes, p->n, p->oh, p->ow, bpi);
+    void *scratch = nullptr;
+    rc = static_scratch_for_current_device(&scratch);
+    if (rc != TA_B200_OK) return rc;
+    static DeviceState no_counters;                                    // only its null `counters` is read
+    KArgs k;
+    fill_kargs(k, p, no_counters);
+    unsigned *counters = (unsigned *)scratch;
+    float *partials = (float *)((char *)scratch + mean_partials_offset(p->n));
+    // The tickets must start at zero; the previous call (possibly with another n) left its own there.
+    cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)p->n * sizeof(unsigned), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static scratch)");
+    const int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    const bool bright = (p->apply & TA_B200_APPLY_BRIGHTNESS) != 0;
+    e = p->dtype == TA_B200_F32
+            ? launch_gray_mean<float>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream)
+            : launch_gray_mean<__half>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "launch(gray_mean, static scratch)");
+    return TA_B200_OK;
+}
+
+}  // namespace ta
+
+extern "C" int ta_b200_gray_mean_static(const ta_b200_fused_params *p, float *mean_out, void *stream)
+{
+    return ta::gray_mean_static(p, mean_out, (cudaStream_t)stream);
+}
