@@ -97,7 +97,8 @@ def test_benchmark_geometry_is_always_staged():
     for _ in range(12):
         m = _matrix(rng, 15, 0.1, (0.9, 1.1), 5, 1280, 1280)
         top, left = float(rng.integers(0, 257)), float(rng.integers(0, 257))
-        for tx, ty in [(0, 0), (15, 31), (7, 16), (15, 0), (0, 31)]:
+        nx, ny = (1024 + tw - 1) // tw, (1024 + th - 1) // th
+        for tx, ty in [(0, 0), (nx - 1, ny - 1), (nx // 2, ny // 2), (nx - 1, 0), (0, ny - 1)]:
             rows, *_ = _lib.tile_footprint(True, 4, 1280, 1280, 1024, 1024, top, left, False, m, tx, ty)
             assert rows > 0
 

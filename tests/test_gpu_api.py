@@ -221,3 +221,23 @@ def test_sharded_wrapper_equals_single_device():
         outs.append(ta.ShardedAugment.for_rank(aug, rank, 3, device=DEV)((x[a:b], tuple(x.shape))))
     torch.manual_seed(79)
     assert torch.cat(outs).equal(aug(x))
+
+
+def test_matrix_kernel_is_bit_identical_to_torch_ops():
+    """The affine matrix is an INPUT of the fused kernel; the single-launch matrix kernel may
+    replace the reference's ~30 elementwise torch operations only because it returns the same
+    bits.  Checked over benchmark-like, extreme and near-identity parameter ranges."""
+    from triton_augment_b200 import _lib, functional as F
+    g = torch.Generator(device=DEV).manual_seed(0)
+    u = lambda lo, hi, *s: torch.empty(*s, device=DEV).uniform_(lo, hi, generator=g)
+    for n, a, t, s0, s1, sh, c in ((200_000, 15, 128, 0.9, 1.1, 5, 0), (200_000, 180, 500, 0.3, 3.0, 45, 100),
+                                   (200_000, 1e-3, 0.1, 0.999, 1.001, 1e-3, 0), (7, 90, 10, 1.0, 1.0, 0, 0)):
+        angle, tr, sc, shr, ce = u(-a, a, n), u(-t, t, n, 2), u(s0, s1, n), u(-sh, sh, n, 2), u(-c, c, n, 2)
+        got = _lib.inverse_affine_matrix(ce, angle, tr, sc, shr)
+        old = F._MATRIX_KERNEL
+        F._MATRIX_KERNEL = False
+        try:
+            want = F._get_inverse_affine_matrix(ce, angle, tr, sc, shr)
+        finally:
+            F._MATRIX_KERNEL = old
+        assert torch.equal(got.view(torch.int32), want.contiguous().view(torch.int32))

@@ -12,7 +12,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libta_b200.so")
+LIB_PATH = os.environ.get("TA_B200_LIB") or os.path.join(_HERE, "lib", "libta_b200.so")
 
 ABI_VERSION = 1
 F32, F16 = 0, 1
@@ -149,6 +149,19 @@ def launch_gray_mean(params: FusedParams, device: torch.device) -> torch.Tensor:
         stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         check(lib.ta_b200_gray_mean(C.byref(params), _ptr(means), _ptr(scratch), need, stream), "ta_b200_gray_mean")
     return means
+
+
+def inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.Tensor:
+    """``[n, 6]`` inverse affine matrices from device fp32 parameter tensors in one launch."""
+    dev = angle.device
+    n = angle.shape[0]
+    args = [t.contiguous() for t in (center, angle, translate, scale, shear)]
+    out = torch.empty(n, 6, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        check(load().ta_b200_inverse_affine_matrix(n, *[_ptr(t) for t in args], _ptr(out), stream),
+              "ta_b200_inverse_affine_matrix")
+    return out
 
 
 def debug_counters(reset: bool = False):

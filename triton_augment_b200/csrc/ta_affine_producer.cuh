@@ -12,7 +12,8 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
     using Info = TileInfo<T, C, F>;
     constexpr int CH = 16 / (int)sizeof(T);
     constexpr size_t STAGE = AffineSmem<T, C, F>::stage;
-    constexpr int NGROUPS = kMaxRows / kGroupRows;          // 8: lanes 0..7 each own one row group
+    constexpr int NGROUPS = kMaxRows / kGroupRows;          // lanes 0 .. NGROUPS-1 each own one row group
+    static_assert(NGROUPS <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
     const int lane = threadIdx.x & 31;
     const int tiles_per_img = k.tiles_x * k.tiles_y;
     T *stage = reinterpret_cast<T *>(smem + p * STAGE);
@@ -44,8 +45,8 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         int gxs = 0, bw = kPitch, bi = kNumBoxWidths - 1;
         const int ngroups = (fp.rows + kGroupRows - 1) / kGroupRows;
         if (staged) {
-            // lanes 0..7: columns of row group `lane`; the other lanes mirror lane & 7
-            const int grp = lane & (NGROUPS - 1);
+            // lanes 0 .. NGROUPS-1: columns of row group `lane`; the other lanes hold a neutral entry
+            const int grp = lane;
             int xs = 0, xe = CH;
             const int r_first = grp * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
             if (grp >= ngroups || !tile_rows_range(fp, MODE - 1, CH, r_first, r_last, xs, xe)) { xs = 0; xe = CH; }
@@ -53,7 +54,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             int wmax = xe - xs;
             bool inside = grp >= ngroups || (xs >= 0 && xe <= k.w);
 #pragma unroll
-            for (int o = 1; o < NGROUPS; o <<= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
+            for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
             inside = __all_sync(0xffffffffu, inside) && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
             bi = wmax <= box_width(0) ? 0 : wmax <= box_width(1) ? 1 : 2;
             bw = box_width(bi);
@@ -65,11 +66,13 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         if (use > 0 && !mbar_wait_or_abort(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
 
         if (staged) {
-            // rowoff[r] = r * bw - (first column of r's group); rows lane and lane + 32
-            const int x_lo = __shfl_sync(0xffffffffu, gxs, lane >> 3);
-            const int x_hi = __shfl_sync(0xffffffffu, gxs, 4 + (lane >> 3));
-            ti->rowoff[lane] = lane * bw - x_lo;
-            ti->rowoff[lane + 32] = (lane + 32) * bw - x_hi;
+            // rowoff[r] = r * bw - (first column of r's group); rows lane, lane + 32, ...
+#pragma unroll
+            for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
+                const int r = base + lane;
+                const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, NGROUPS - 1));
+                if (r < kMaxRows) ti->rowoff[r] = r * bw - x_first;
+            }
             if (lane == 0) {
                 ti->rowoff[kMaxRows] = 0;
                 mbar_expect_tx(&full[p], (uint32_t)(ngroups * C * bw * kGroupRows * (int)sizeof(T)));

@@ -33,15 +33,21 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
     unsigned long long n_viol = 0;
+    int cur_n = -1;
+    Geom g;
+    Colour<T, C, F> col;
     int it = 0;
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
         const int s = it % kStages, use = it / kStages;
         if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
         const T *stage = reinterpret_cast<const T *>(smem + s * STAGE);
         const Info *ti = reinterpret_cast<const Info *>(smem + s * STAGE + (size_t)C * kPlane * sizeof(T));
-        const Geom g = ti->g;
-        const Colour<T, C, F> col = ti->col;
         const int n = ti->n, rows = ti->rows, row0 = ti->row0;
+        if (n != cur_n) {            // per-image parameters change only every few tiles (warp-uniform branch)
+            g = ti->g;
+            col = ti->col;
+            cur_n = n;
+        }
         const int x = ti->x0 + wx * 32 + lane;
         const int y_first = ti->y0 + wy * ROWS_PER_WARP;
 
@@ -52,10 +58,12 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
             const float xc = centred(img_x(g, k.ow, x), g.half_w);
 #pragma unroll
             for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
-                const int ya = y_first + 2 * pr;
-                if (ya >= k.oh) break;
-                const bool b_ok = ya + 1 < k.oh;
-                const int yb = b_ok ? ya + 1 : ya;           // keep the second lane on valid geometry
+                // No early exit: rows past the image's last row are computed on the last row's
+                // geometry (always staged) and only their stores are dropped, so the pairs stay
+                // independent and their instructions can interleave.
+                const int y_raw = y_first + 2 * pr;
+                const bool a_ok = y_raw < k.oh, b_ok = y_raw + 1 < k.oh;
+                const int ya = min(y_raw, k.oh - 1), yb = min(y_raw + 1, k.oh - 1);
                 const float2 yc = f2(centred(img_y(g, ya), g.half_h), centred(img_y(g, yb), g.half_h));
                 const float2 sx = src_coord2(xc, g.a, g.b, yc, g.c, g.half_w);
                 const float2 sy = src_coord2(xc, g.d, g.e, yc, g.f, g.half_h);
@@ -104,14 +112,26 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                         smp[1][c] = Elem<T>::from_f(acc.y);
                     }
                 }
+                const unsigned o = (unsigned)(y_raw * k.ow + x);
+                if constexpr (sizeof(T) == 4) {
+                    float2 v2[C];
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    float v[C];
-                    col.apply(k, smp[j], v);
-                    if (j == 0 || b_ok) {
-                        const unsigned o = (unsigned)((ya + j) * k.ow + x);
+                    for (int c = 0; c < C; ++c) v2[c] = f2(smp[0][c], smp[1][c]);
+                    col.apply2(k, v2);
 #pragma unroll
-                        for (int c = 0; c < C; ++c) Elem<T>::store(out + (size_t)c * oplane + o, v[c]);
+                    for (int c = 0; c < C; ++c) {
+                        if (a_ok) Elem<T>::store(out + (size_t)c * oplane + o, v2[c].x);
+                        if (b_ok) Elem<T>::store(out + (size_t)c * oplane + o + k.ow, v2[c].y);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float v[C];
+                        col.apply(k, smp[j], v);
+                        if (j == 0 ? a_ok : b_ok) {
+#pragma unroll
+                            for (int c = 0; c < C; ++c) Elem<T>::store(out + (size_t)c * oplane + o + j * k.ow, v[c]);
+                        }
                     }
                 }
             }

@@ -107,7 +107,14 @@ template <typename T> struct Elem;
 template <> struct Elem<float> {
     static __device__ __forceinline__ float to_f(float v) { return v; }
     static __device__ __forceinline__ float from_f(float v) { return v; }
-    static __device__ __forceinline__ void store(float *p, float v) { __stcs(p, v); }
+    static __device__ __forceinline__ void store(float *p, float v)
+    {
+#ifdef TA_STREAMING_STORES       // st.global.cs measured no better than plain stores (0-2 % worse)
+        __stcs(p, v);
+#else
+        *p = v;
+#endif
+    }
 };
 template <> struct Elem<__half> {
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
@@ -215,6 +222,50 @@ template <int C, unsigned F> struct Colour<float, C, F> {
         if (F & kN) {
 #pragma unroll
             for (int i = 0; i < C; ++i) v[i] = __fmaf_rn(v[i], k.inv_std[i], k.nbias[i]);
+        }
+    }
+    // Two pixels at once (.x and .y of each channel): everything that does not clamp goes
+    // through the packed fp32 pipe, the clamping steps stay scalar because only scalar
+    // multiplies / FMAs carry the saturate modifier.  Same arithmetic per pixel as apply().
+    __device__ __forceinline__ void apply2(const KArgs &k, float2 (&v)[C]) const
+    {
+        if (F & kB) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = make_float2(__saturatef(v[i].x * bf), __saturatef(v[i].y * bf));
+        }
+        if (F & kC) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                if (F & kMean) {
+                    v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, cf, gmt)), __saturatef(__fmaf_rn(v[i].y, cf, gmt)));
+                } else {
+                    const float2 d = __fadd2_rn(v[i], make_float2(-0.5f, -0.5f));
+                    v[i] = make_float2(__saturatef(__fmaf_rn(d.x, cf, 0.5f)), __saturatef(__fmaf_rn(d.y, cf, 0.5f)));
+                }
+            }
+        }
+        if (C == 3 && (F & kS)) {
+            float2 g = __fmul2_rn(make_float2(0.2989f, 0.2989f), v[0]);
+            g = __ffma2_rn(make_float2(0.587f, 0.587f), v[1], g);
+            g = __ffma2_rn(make_float2(0.114f, 0.114f), v[C - 1], g);
+            g = __fmul2_rn(g, make_float2(oms, oms));
+#pragma unroll
+            for (int i = 0; i < C; ++i)
+                v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, sf, g.x)), __saturatef(__fmaf_rn(v[i].y, sf, g.y)));
+        }
+        if (C == 3 && (F & kG)) {
+            if (gray) {
+                float2 g = __fmul2_rn(make_float2(0.2989f, 0.2989f), v[0]);
+                g = __ffma2_rn(make_float2(0.587f, 0.587f), v[1], g);
+                g = __ffma2_rn(make_float2(0.114f, 0.114f), v[C - 1], g);
+#pragma unroll
+                for (int i = 0; i < C; ++i) v[i] = g;
+            }
+        }
+        if (F & kN) {
+#pragma unroll
+            for (int i = 0; i < C; ++i)
+                v[i] = __ffma2_rn(v[i], make_float2(k.inv_std[i], k.inv_std[i]), make_float2(k.nbias[i], k.nbias[i]));
         }
     }
 };

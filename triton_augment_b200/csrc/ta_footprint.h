@@ -31,7 +31,9 @@ constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 grou
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
 constexpr int kPitch = 96;       // widest staged row, in elements
 constexpr int kNumBoxWidths = 3; // tensor-copy box widths to choose from per tile
-TA_HD int box_width(int i) { return i == 0 ? 72 : i == 1 ? 80 : kPitch; }
+// A row pitch that is a multiple of 32 words keeps lanes of one warp that sit in different
+// source rows on different banks; narrower boxes save L2 traffic but cost 2-way conflicts.
+TA_HD int box_width(int i) { return i == 0 ? kPitch : i == 1 ? kPitch : kPitch; }
 constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
 constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
 

@@ -7,6 +7,7 @@ stand-alone functionals are the fused kernel with no-op arguments.
 """
 from __future__ import annotations
 
+import os
 from typing import Sequence
 
 import torch
@@ -20,6 +21,9 @@ __all__ = [
 ]
 
 _DEG2RAD = 3.141592653589793 / 180.0
+# TA_B200_TORCH_MATRIX=1 builds the affine matrices with the reference's torch expressions
+# instead of the library's single kernel (same bits either way; kept for cross-checking).
+_MATRIX_KERNEL = os.environ.get("TA_B200_TORCH_MATRIX", "0") != "1"
 
 
 class InterpolationMode:
@@ -98,6 +102,12 @@ def _get_inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.
     reference's (functional.py:853-890) on purpose: the matrix is an input of the kernel,
     and both kernels must see bit-identical inputs for their outputs to be comparable.
     """
+    if _MATRIX_KERNEL and angle.is_cuda and all(t.dtype == torch.float32 and t.device == angle.device
+                                               for t in (center, angle, translate, scale, shear)):
+        # One launch instead of ~30 elementwise ones.  The kernel rounds every operation
+        # individually in the order below and returns the same bits as the torch expressions
+        # (tests/test_gpu_api.py::test_matrix_kernel_is_bit_identical_to_torch_ops).
+        return _lib.inverse_affine_matrix(center, angle, translate, scale, shear)
     rot = angle * _DEG2RAD
     sx = shear[:, 0] * _DEG2RAD
     sy = shear[:, 1] * _DEG2RAD
@@ -130,9 +140,18 @@ def _check_interpolation(interpolation) -> None:
         raise ValueError(f"Only 'nearest' and 'bilinear' interpolation are supported, got {interpolation}")
 
 
+_TRIPLE_CACHE = {}
+
+
 def _rounded_triple(values, dtype):
     """mean/std as Python floats holding image-dtype-rounded values (functional.py:1350-1351)."""
-    return [float(v) for v in torch.tensor(values, dtype=dtype).to(torch.float32)]
+    key = (tuple(float(v) for v in values), dtype)
+    hit = _TRIPLE_CACHE.get(key)
+    if hit is None:
+        hit = [float(v) for v in torch.tensor(key[0], dtype=dtype).to(torch.float32)]
+        if len(_TRIPLE_CACHE) < 64:
+            _TRIPLE_CACHE[key] = hit
+    return hit
 
 
 def _contrast_mode(mode) -> int:
