@@ -31,9 +31,9 @@ sys.path.insert(0, ROOT)
 MEAN, STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
 N_IMG, SRC, CROP = 64, 1280, 1024
 METRIC, UNIT = "fused-augment throughput, 1280x1280 -> 1024x1024 affine config", "images/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one affine-kernel launch, from the ncu capture
-# summarised in profiles/ (8-image case, scaled by images: traffic is proportional to them).
-NCU_TRAFFIC_PER_IMAGE = {"bilinear": None, "nearest": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of one full 64-image affine-kernel launch (single-pass
+# ncu capture, profiles/affine_kernel_c3_fp32.md), divided by 64.
+NCU_TRAFFIC_PER_IMAGE = {"bilinear": (832574208 + 762701568) / 64, "nearest": (831968512 + 762443264) / 64}
 
 
 def measured_peak_gbs():
@@ -208,6 +208,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--interp", default="bilinear", choices=["bilinear", "nearest"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--profile-case", type=int, default=0, metavar="IMAGES",
+                    help="only launch the fused kernel 3 times on IMAGES images (for ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -215,6 +217,17 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.profile_case:
+        # For profilers: the workload's tensors for a few images, three launches of the fused
+        # kernel through the C ABI, nothing else.  Prints no benchmark line.
+        global N_IMG
+        N_IMG = args.profile_case
+        torch.cuda.set_device(0)
+        torch.manual_seed(1234)
+        img = torch.rand(N_IMG, 3, SRC, SRC, device="cuda:0")
+        ms = kernel_only(make_transform(args.interp), img, 2, 1, None)
+        print(f"profile case: {N_IMG} images, {args.interp}, {ms:.4f} ms per launch")
         return
 
     import torch.distributed as dist
