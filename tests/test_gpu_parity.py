@@ -170,6 +170,39 @@ def test_every_flag_combination(dtype, interp):
         assert err <= tol, (bits, err)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_vectorised_crop_flip_kernel_every_shift(dtype):
+    """Crop/flip with whole-vector output rows runs on the 128-bit kernel, which shifts each
+    lane's run out of two aligned vectors.  Every left offset 0..16, with and without flip,
+    input widths that are and are not multiples of the vector (so the shift changes from row
+    to row), odd heights, and windows that leave the image (read as 0): bit-exact vs the oracle."""
+    ta = _ta()
+    dev = _dev()
+    rng = np.random.default_rng(8)
+    for (h, w, oh, ow) in [(40, 200, 33, 136), (37, 203, 30, 144), (50, 178, 50, 160), (48, 172, 40, 152)]:
+        n = 17
+        img = rng.random((n, 3, h, w), dtype=np.float32).astype(dtype)
+        left = np.arange(n, dtype=np.float32)
+        top = (np.arange(n) % max(1, h - oh + 1)).astype(np.float32)
+        for flip_all in (False, True):
+            flip = np.full(n, flip_all)
+            flip[3] = not flip_all
+            t = lambda a: torch.from_numpy(a).to(dev)
+            got = ta.fused_augment(t(img), t(top), t(left), oh, ow, t(flip)).cpu().numpy()
+            want = O.fused_augment(img, top, left, oh, ow, flip)
+            assert np.array_equal(got, want), (dtype, h, w, flip_all)
+    # windows partly outside the image: left beyond w - ow, negative top
+    img = rng.random((4, 3, 32, 64), dtype=np.float32).astype(dtype)
+    top = np.array([-3.0, 0.0, 5.0, 30.0], np.float32)
+    left = np.array([-8.0, 40.0, 0.0, 60.0], np.float32)
+    flip = np.array([False, True, False, True])
+    t = lambda a: torch.from_numpy(a).to(dev)
+    got = ta.fused_augment(t(img), t(top), t(left), 16, 32, t(flip), brightness_factor=1.1, mean=MEAN, std=STD)
+    want = O.fused_augment(img, top, left, 16, 32, flip, brightness=np.float32(1.1).astype(dtype), mean=MEAN, std=STD)
+    tol = FP16_TOL if dtype == np.float16 else FP32_TOL
+    assert float(np.abs(got.cpu().numpy().astype(np.float32) - want.astype(np.float32)).max()) <= tol
+
+
 def test_staging_assertions_hold_on_random_geometry():
     """The checked build of the staged kernel counts every shared-memory tap that falls outside
     what was staged; over random matrices, sizes, offsets and flips there must be none, no

@@ -9,10 +9,10 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 // src_coord(): ((fma(xc, a, b*yc) + c) + half) + (-0.5), each step rounded to nearest.
 __device__ __forceinline__ float2 src_coord2(float xc, float a, float b, float2 yc, float c, float half)
 {
-    float2 u = __ffma2_rn(f2(xc, xc), f2(a, a), __fmul2_rn(f2(b, b), yc));
-    u = __fadd2_rn(u, f2(c, c));
-    u = __fadd2_rn(f2(half, half), u);
-    return __fadd2_rn(u, f2(-0.5f, -0.5f));
+    float2 u = pk_fma(f2(xc, xc), f2(a, a), pk_mul(f2(b, b), yc));
+    u = pk_add(u, f2(c, c));
+    u = pk_add(f2(half, half), u);
+    return pk_add(u, f2(-0.5f, -0.5f));
 }
 
 }  // namespace ta
@@ -98,16 +98,16 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                         }
                     }
                     const float2 one = f2(1.0f, 1.0f), neg = f2(-1.0f, -1.0f);
-                    const float2 omx = __ffma2_rn(dx, neg, one), omy = __ffma2_rn(dy, neg, one);   // 1 - d, one rounding
-                    const float2 w00 = __fmul2_rn(omx, omy), w10 = __fmul2_rn(dx, omy);
-                    const float2 w01 = __fmul2_rn(omx, dy), w11 = __fmul2_rn(dx, dy);
+                    const float2 omx = pk_fma(dx, neg, one), omy = pk_fma(dy, neg, one);   // 1 - d, one rounding
+                    const float2 w00 = pk_mul(omx, omy), w10 = pk_mul(dx, omy);
+                    const float2 w01 = pk_mul(omx, dy), w11 = pk_mul(dx, dy);
 #pragma unroll
                     for (int c = 0; c < C; ++c) {
                         const T *pl = stage + c * kPlane;
-                        float2 acc = __fmul2_rn(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
-                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
-                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
-                        acc = __ffma2_rn(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
+                        float2 acc = pk_mul(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
+                        acc = pk_fma(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
+                        acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
+                        acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
                         smp[0][c] = Elem<T>::from_f(acc.x);
                         smp[1][c] = Elem<T>::from_f(acc.y);
                     }

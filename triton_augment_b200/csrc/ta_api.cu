@@ -6,6 +6,7 @@
 #include <limits.h>
 #include <math.h>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <stdio.h>
 #include <string.h>
 
@@ -35,7 +36,9 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 3, kNumDtypes = 2;
+constexpr int kNumKinds = 4, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit
+// TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
+static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 
 struct DeviceState {
     std::mutex mu;
@@ -229,15 +232,25 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     } else {
         ke = p->c == 3 ? &tab.c3[f] : &tab.c1[f];
     }
+    // Crop/flip only: the 128-bit kernel needs whole-vector output rows and vector-aligned tensors.
+    const size_t es_bytes = p->dtype == TA_B200_F32 ? 4 : 2;
+    const int epv = (int)(16 / es_bytes);
+    const bool vec = kind == 0 && !g_force_scalar_direct && p->ow % epv == 0 && ((uintptr_t)p->in % 16) == 0 &&
+                     ((uintptr_t)p->out % 16) == 0 && ((size_t)p->n * p->c * p->h * p->w * es_bytes) % 16 == 0;
+    if (vec) ke = p->c == 3 ? &tab.c3_vec[f] : &tab.c1_vec[f];
     if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;
-    rc = prepare_kernel(*s, *ke, kind, p->dtype, p->c, slot, &blocks);
+    rc = prepare_kernel(*s, *ke, vec ? 3 : kind, p->dtype, p->c, slot, &blocks);
     if (rc != TA_B200_OK) return rc;
 
     KArgs k;
     fill_kargs(k, p, *s);
     long long work;
-    if (kind == 0) {
+    if (vec) {
+        k.tiles_x = (p->ow + 32 * epv - 1) / (32 * epv);
+        k.tiles_y = (p->oh + kVecRows - 1) / kVecRows;
+        work = ((long long)p->n * k.tiles_x * k.tiles_y + kWarps - 1) / kWarps;
+    } else if (kind == 0) {
         k.tiles_x = (p->ow + 31) / 32;
         k.tiles_y = (p->oh + kDirectRows - 1) / kDirectRows;
         work = ((long long)p->n * k.tiles_x * k.tiles_y + kWarps - 1) / kWarps;      // CTAs needed at one strip per warp

@@ -102,6 +102,34 @@ __device__ __forceinline__ void fence_proxy_async()
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ----------------------------------------------------------------------------- packed fp32
+// Two independent IEEE round-to-nearest operations per instruction on sm_100 (fma.rn.f32x2 and
+// friends).  -DTA_NO_PACKED builds the same arithmetic from scalar instructions.
+__device__ __forceinline__ float2 pk_fma(float2 a, float2 b, float2 c)
+{
+#ifdef TA_NO_PACKED
+    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
+#else
+    return __ffma2_rn(a, b, c);
+#endif
+}
+__device__ __forceinline__ float2 pk_mul(float2 a, float2 b)
+{
+#ifdef TA_NO_PACKED
+    return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y));
+#else
+    return __fmul2_rn(a, b);
+#endif
+}
+__device__ __forceinline__ float2 pk_add(float2 a, float2 b)
+{
+#ifdef TA_NO_PACKED
+    return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+#else
+    return __fadd2_rn(a, b);
+#endif
+}
+
 // ----------------------------------------------------------------------------- element access
 template <typename T> struct Elem;
 template <> struct Elem<float> {
@@ -239,25 +267,25 @@ template <int C, unsigned F> struct Colour<float, C, F> {
                 if (F & kMean) {
                     v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, cf, gmt)), __saturatef(__fmaf_rn(v[i].y, cf, gmt)));
                 } else {
-                    const float2 d = __fadd2_rn(v[i], make_float2(-0.5f, -0.5f));
+                    const float2 d = pk_add(v[i], make_float2(-0.5f, -0.5f));
                     v[i] = make_float2(__saturatef(__fmaf_rn(d.x, cf, 0.5f)), __saturatef(__fmaf_rn(d.y, cf, 0.5f)));
                 }
             }
         }
         if (C == 3 && (F & kS)) {
-            float2 g = __fmul2_rn(make_float2(0.2989f, 0.2989f), v[0]);
-            g = __ffma2_rn(make_float2(0.587f, 0.587f), v[1], g);
-            g = __ffma2_rn(make_float2(0.114f, 0.114f), v[C - 1], g);
-            g = __fmul2_rn(g, make_float2(oms, oms));
+            float2 g = pk_mul(make_float2(0.2989f, 0.2989f), v[0]);
+            g = pk_fma(make_float2(0.587f, 0.587f), v[1], g);
+            g = pk_fma(make_float2(0.114f, 0.114f), v[C - 1], g);
+            g = pk_mul(g, make_float2(oms, oms));
 #pragma unroll
             for (int i = 0; i < C; ++i)
                 v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, sf, g.x)), __saturatef(__fmaf_rn(v[i].y, sf, g.y)));
         }
         if (C == 3 && (F & kG)) {
             if (gray) {
-                float2 g = __fmul2_rn(make_float2(0.2989f, 0.2989f), v[0]);
-                g = __ffma2_rn(make_float2(0.587f, 0.587f), v[1], g);
-                g = __ffma2_rn(make_float2(0.114f, 0.114f), v[C - 1], g);
+                float2 g = pk_mul(make_float2(0.2989f, 0.2989f), v[0]);
+                g = pk_fma(make_float2(0.587f, 0.587f), v[1], g);
+                g = pk_fma(make_float2(0.114f, 0.114f), v[C - 1], g);
 #pragma unroll
                 for (int i = 0; i < C; ++i) v[i] = g;
             }
@@ -265,7 +293,7 @@ template <int C, unsigned F> struct Colour<float, C, F> {
         if (F & kN) {
 #pragma unroll
             for (int i = 0; i < C; ++i)
-                v[i] = __ffma2_rn(v[i], make_float2(k.inv_std[i], k.inv_std[i]), make_float2(k.nbias[i], k.nbias[i]));
+                v[i] = pk_fma(v[i], make_float2(k.inv_std[i], k.inv_std[i]), make_float2(k.nbias[i], k.nbias[i]));
         }
     }
 };

@@ -8,6 +8,7 @@
 
 #include "ta_affine.cuh"
 #include "ta_direct.cuh"
+#include "ta_direct_vec.cuh"
 
 namespace ta {
 
@@ -22,6 +23,8 @@ struct KernelEntry {
 struct KernelTable {
     KernelEntry c3[kNumFlagCombos];
     KernelEntry c1[kNumFlagCombos];
+    KernelEntry c3_vec[kNumFlagCombos];   // crop/flip only: the 128-bit variant (direct_vec_kernel)
+    KernelEntry c1_vec[kNumFlagCombos];
     KernelEntry c3_checked;          // affine only, flags 0, staging assertions on
     KernelEntry c1_checked;
 };
@@ -42,6 +45,12 @@ template <typename T, int C, int KIND, unsigned F, bool CHECK = false> KernelEnt
                             kAffineThreads};
 }
 
+template <typename T, int C, unsigned F> KernelEntry vec_entry()
+{
+    if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
+    else return KernelEntry{(const void *)&direct_vec_kernel<T, C, F>, 0, kThreads};
+}
+
 template <typename T, int KIND, unsigned... Fs>
 void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
 {
@@ -52,6 +61,8 @@ void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
         t.c1_checked = kernel_entry<T, 1, KIND, 0u, true>();
     } else {
         t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
+        ((t.c3_vec[Fs] = vec_entry<T, 3, Fs>()), ...);
+        ((t.c1_vec[Fs] = vec_entry<T, 1, Fs>()), ...);
     }
 }
 
