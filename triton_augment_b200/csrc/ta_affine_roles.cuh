@@ -64,15 +64,16 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 const int y_raw = y_first + 2 * pr;
                 const bool a_ok = y_raw < k.oh, b_ok = y_raw + 1 < k.oh;
                 const int ya = min(y_raw, k.oh - 1), yb = min(y_raw + 1, k.oh - 1);
-                const float2 yc = f2(centred(img_y(g, ya), g.half_h), centred(img_y(g, yb), g.half_h));
+                const float2 yc = f2(centred(__fadd_rn(float_of_small_uint(ya), g.top), g.half_h),
+                                     centred(__fadd_rn(float_of_small_uint(yb), g.top), g.half_h));
                 const float2 sx = src_coord2(xc, g.a, g.b, yc, g.c, g.half_w);
                 const float2 sy = src_coord2(xc, g.d, g.e, yc, g.f, g.half_h);
                 T smp[2][C];
                 if (MODE == 1) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
-                        const int xn = __float2int_rn(j ? sx.y : sx.x);
-                        int r = __float2int_rn(j ? sy.y : sy.x) - row0;
+                        const int xn = rint_magic(j ? sx.y : sx.x);
+                        int r = rint_magic(j ? sy.y : sy.x) - row0;
                         if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
                         int idx = ti->rowoff[r] + xn;
                         if (CHECK && (unsigned)(idx - r * ti->bw) >= (unsigned)ti->bw) { ++n_viol; idx = 0; }
@@ -85,9 +86,10 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const float fx = j ? sx.y : sx.x, fy = j ? sy.y : sy.x;
-                        const int x0 = __float2int_rd(fx), y0 = __float2int_rd(fy);
-                        (j ? dx.y : dx.x) = fx - (float)x0;
-                        (j ? dy.y : dy.x) = fy - (float)y0;
+                        float frac_x, frac_y;
+                        const int x0 = floor_magic(fx, frac_x), y0 = floor_magic(fy, frac_y);
+                        (j ? dx.y : dx.x) = frac_x;
+                        (j ? dy.y : dy.x) = frac_y;
                         int r = y0 - row0;
                         if (CHECK && (unsigned)r >= (unsigned)(rows - 1)) { ++n_viol; r = 0; }
                         i0[j] = ti->rowoff[r] + x0;

@@ -163,7 +163,9 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
     }
     const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
     k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
-                  ((size_t)p->h * p->w * es) % 16 == 0;
+                  ((size_t)p->h * p->w * es) % 16 == 0 &&
+                  // the staged path converts coordinates with a 2^22-range shortcut
+                  p->h < (1 << 22) && p->w < (1 << 22) && p->oh < (1 << 22) && p->ow < (1 << 22);
 }
 
 static unsigned template_flags(const ta_b200_fused_params *p)

@@ -130,6 +130,29 @@ __device__ __forceinline__ float2 pk_add(float2 a, float2 b)
 #endif
 }
 
+// ----------------------------------------------------------------------------- conversions without the XU pipe
+// float <-> int conversions issue at a quarter of the FMA rate.  For |v| < 2^22 the same
+// integers fall out of one addition of 1.5 * 2^23, whose unit in the last place is 1: the sum
+// is rounded to an integer by the adder itself, to nearest-even (= rint) or downwards (= floor)
+// depending on the instruction's rounding mode, and the integer sits in the low mantissa bits.
+// The staged path only sees coordinates below kCoordLimit, so the results equal
+// cvt.rni / cvt.rmi bit for bit there.
+constexpr float kMagic = 12582912.0f;            // 1.5 * 2^23, bit pattern 0x4B400000
+constexpr int kMagicBits = 0x4B400000;
+
+__device__ __forceinline__ int rint_magic(float v) { return __float_as_int(__fadd_rn(v, kMagic)) - kMagicBits; }
+
+// floor(v) as int, and v - floor(v) (exact, the same value as v - (float)floor)
+__device__ __forceinline__ int floor_magic(float v, float &frac)
+{
+    const float t = __fadd_rd(v, kMagic);
+    frac = __fsub_rn(v, __fsub_rn(t, kMagic));
+    return __float_as_int(t) - kMagicBits;
+}
+
+// (float)i for 0 <= i < 2^23
+__device__ __forceinline__ float float_of_small_uint(int i) { return __fsub_rn(__int_as_float(0x4B000000 | i), 8388608.0f); }
+
 // ----------------------------------------------------------------------------- element access
 template <typename T> struct Elem;
 template <> struct Elem<float> {
