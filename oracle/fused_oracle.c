@@ -94,14 +94,11 @@ static inline void map_coords(const ta_oracle_params *p, int n, int xo, int yo, 
     float half_w = (float)p->w * 0.5f, half_h = (float)p->h * 0.5f;  /* :408-409 */
     float xc = (x_img - half_w) + 0.5f;                              /* :410 */
     float yc = (y_img - half_h) + 0.5f;                              /* :411 */
-    float ux, uy;
-    if (p->fma_coords) {
-        ux = fmaf(xc, m[0], m[1] * yc);
-        uy = fmaf(xc, m[3], m[4] * yc);
-    } else {
-        ux = m[0] * xc + m[1] * yc;                                  /* :414 */
-        uy = m[3] * xc + m[4] * yc;                                  /* :415 */
-    }
+    /* a*xc + b*yc (:414-415): which product, if any, the compiler fused into the addition.
+     * Bits 0-1 choose for x, bits 2-3 for y: 0 none, 1 fma(xc, a, b*yc), 2 fma(yc, b, a*xc). */
+    const int rx = p->fma_coords & 3, ry = (p->fma_coords >> 2) & 3;
+    float ux = rx == 1 ? fmaf(xc, m[0], m[1] * yc) : rx == 2 ? fmaf(yc, m[1], m[0] * xc) : m[0] * xc + m[1] * yc;
+    float uy = ry == 1 ? fmaf(xc, m[3], m[4] * yc) : ry == 2 ? fmaf(yc, m[4], m[3] * xc) : m[3] * xc + m[4] * yc;
     ux = ux + m[2];
     uy = uy + m[5];
     ux = ux + half_w;

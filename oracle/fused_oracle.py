@@ -71,6 +71,42 @@ def max_threads() -> int:
     return int(lib().ta_oracle_max_threads())
 
 
+def coord_recipe(fma_coords) -> int:
+    """How ``a*xc + b*yc`` of the coordinate map is contracted, per axis.
+
+    ``False`` / ``0``: not at all (the CPU interpreter).  ``True``: ``fma(xc, a, b*yc)`` for both
+    axes, what the reference's GPU build does in its nearest-sampling kernels.  ``"nearest"`` /
+    ``"bilinear"``: the recipe measured for that variant of the reference's GPU kernel (see
+    tests/golden/make_gpu_golden.py).  ``(rx, ry)``: explicit, 0 none / 1 ``fma(xc,a,b*yc)`` /
+    2 ``fma(yc,b,a*xc)``.
+    """
+    if isinstance(fma_coords, str):
+        raise ValueError("resolve 'gpu' with gpu_recipe(interpolation, flags) first")
+    if isinstance(fma_coords, (tuple, list)):
+        return int(fma_coords[0]) | (int(fma_coords[1]) << 2)
+    if isinstance(fma_coords, (bool, np.bool_)):
+        return 5 if fma_coords else 0
+    return int(fma_coords)
+
+
+def gpu_recipe(interpolation, flags) -> tuple:
+    """Contraction the reference's kernel shows when Triton 3.6 compiles it for sm_100.
+
+    Measured on a B200 by comparing the reference's output with every recipe, for all 32
+    combinations of the colour flags, fp32, sizes divisible by 16 (the sweep is described in
+    tests/golden/make_gpu_golden.py):
+      * nearest sampling: x and y are fma(xc, a, b*yc) in every variant;
+      * bilinear sampling: x = fma(xc, a, b*yc), y = fma(yc, e, d*xc), except in the variants
+        that take the RGB-triplet path (saturation or grayscale on) AND have brightness or
+        contrast on, where it is the other way round: x = fma(yc, b, a*xc), y = fma(xc, d, e*yc).
+    Each compiled variant is a different LLVM module, hence the different choices.
+    """
+    if str(interpolation).lower() != "bilinear":
+        return (1, 1)
+    spatial = flags["saturation"] or flags["grayscale"]
+    return (2, 1) if spatial and (flags["brightness"] or flags["contrast"]) else (1, 2)
+
+
 def _vec(x, n, dtype):
     a = np.asarray(x)
     if a.ndim == 0:
@@ -128,7 +164,9 @@ def _prepare(image, top, left, height, width, flip, matrix, interpolation, fill,
     p.apply_normalize = int(apply_norm)
     p.brightness, p.contrast, p.saturation = _ptr(keep["b"]), _ptr(keep["c"]), _ptr(keep["s"])
     p.gray, p.mean, p.std = _ptr(keep["g"]), _ptr(keep["mean"]), _ptr(keep["std"])
-    p.fma_coords = int(fma_coords)
+    if isinstance(fma_coords, str) and fma_coords == "gpu":
+        fma_coords = gpu_recipe(interpolation, flags)
+    p.fma_coords = coord_recipe(fma_coords)
     p.contrast_mode = int(contrast_mode)
     p.gray_mean = _ptr(keep["gm"])
     p.src_index = _ptr(keep["idx"])
@@ -138,7 +176,7 @@ def _prepare(image, top, left, height, width, flip, matrix, interpolation, fill,
 
 def fused_augment(image, top, left, height, width, flip=0, matrix=None, interpolation="nearest",
                   fill=0.0, brightness=1.0, contrast=1.0, saturation=1.0, grayscale=0,
-                  mean=None, std=None, *, flags=None, fma_coords=True,
+                  mean=None, std=None, *, flags=None, fma_coords="gpu",
                   contrast_mode=CONTRAST_FAST, gray_mean=None, want_index=False, threads=0):
     """The reference's fused pass on the CPU.
 
@@ -165,7 +203,7 @@ def fused_augment(image, top, left, height, width, flip=0, matrix=None, interpol
 
 
 def gray_mean(image, top, left, height, width, flip=0, matrix=None, interpolation="nearest",
-              fill=0.0, brightness=1.0, *, apply_brightness=None, fma_coords=True):
+              fill=0.0, brightness=1.0, *, apply_brightness=None, fma_coords="gpu"):
     """Per-image grayscale mean of the geometry+brightness result (exact contrast)."""
     n = np.asarray(image).shape[0]
     b = _vec(brightness, n, np.asarray(image).dtype)

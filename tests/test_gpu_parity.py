@@ -52,7 +52,7 @@ def _run_cuda(case, **over):
     return out.cpu().numpy()
 
 
-def _run_oracle(case, fma=True):
+def _run_oracle(case, fma="gpu"):
     kw = {}
     if "matrix" in case:
         kw = dict(matrix=case["matrix"], interpolation=str(case["interp"]), fill=float(case["fill"]))
@@ -72,7 +72,7 @@ def test_golden_cases_vs_oracle(fused_golden):
     for name in _names(fused_golden):
         case = fused_case(fused_golden, name)
         got = _run_cuda(case).astype(np.float32)
-        want = _run_oracle(case, fma=True).astype(np.float32)
+        want = _run_oracle(case).astype(np.float32)
         tol = FP16_TOL if case["image"].dtype == np.float16 else FP32_TOL
         err = float(np.abs(got - want).max())
         assert err <= tol, (name, err)
@@ -93,7 +93,7 @@ def test_golden_cases_vs_reference_outputs(fused_golden):
         if "matrix" not in case:
             assert float(np.abs(got - want).max()) <= tol, name
             continue
-        a = _run_oracle(case, fma=True).astype(np.float32)
+        a = _run_oracle(case).astype(np.float32)
         b = _run_oracle(case, fma=False).astype(np.float32)
         same = np.abs(a - b) <= 1e-7
         # nearest: a flipped rounding moves a few texels; bilinear: any coordinate ulp shows
@@ -165,7 +165,7 @@ def test_every_flag_combination(dtype, interp):
                                interpolation=interp if interp != "none" else "nearest",
                                brightness=b.astype(dtype), contrast=c.astype(dtype), saturation=s.astype(dtype),
                                grayscale=g, mean=MEAN if norm else None, std=STD if norm else None,
-                               fma_coords=True).astype(np.float32)
+                               ).astype(np.float32)
         err = float(np.abs(got - want).max())
         assert err <= tol, (bits, err)
 

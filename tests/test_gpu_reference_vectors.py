@@ -1,0 +1,77 @@
+"""CUDA kernels against vectors produced by the reference's own Triton kernels ON A B200
+(tests/golden/gpu_reference_cases.npz, written by tests/golden/make_gpu_golden.py).
+
+This is the comparison the task names: same inputs and parameters through the reference's GPU
+kernels and through ours; fp32 within 1e-5, fp16 within 1e-2, nearest-mode geometry bit-exact
+(checked through a SHA-256 of the sampled-index image, 3 million pixels at 1280x1280)."""
+import hashlib
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, MEAN, STD
+
+pytestmark = pytest.mark.gpu
+sys.path.insert(0, GOLDEN)
+
+
+@pytest.fixture(scope="module")
+def vectors():
+    return np.load(os.path.join(GOLDEN, "gpu_reference_cases.npz"))
+
+
+def _inputs(z, name):
+    import make_gpu_golden as G            # procedural inputs only; does not import the reference
+    n, h, w, oh, ow = (int(v) for v in z[f"{name}|shape"])
+    p = {k: z[f"{name}|{k}"] for k in ("angle", "translate", "scale", "shear", "top", "left", "flip",
+                                        "brightness", "contrast", "saturation", "gray")}
+    return G, (n, h, w, oh, ow), p, getattr(torch, str(z[f"{name}|dtype"]))
+
+
+def test_parameters_regenerate(vectors):
+    """The fixture's parameters come from a seeded generator in the script; make sure the
+    script still produces them (otherwise the stored outputs would not belong to them)."""
+    for name in vectors["names"]:
+        G, (n, h, w, oh, ow), p, _ = _inputs(vectors, str(name))
+        again = G.case_params(str(name), n, h, w, oh, ow)
+        for k, v in p.items():
+            assert np.array_equal(np.asarray(again[k]), v), (name, k)
+
+
+def test_matrix_equals_the_reference_matrix(vectors):
+    import triton_augment_b200 as ta
+    for name in vectors["names"]:
+        name = str(name)
+        G, (n, h, w, oh, ow), p, _ = _inputs(vectors, name)
+        t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(G.DEV)
+        m = ta.functional._prepare_affine_matrix_only(n, G.DEV, h, w, t(p["angle"]), t(p["translate"]), t(p["scale"]),
+                                                      t(p["shear"]), None)
+        assert np.array_equal(m.cpu().numpy().view(np.int32), vectors[f"{name}|matrix"].view(np.int32)), name
+
+
+def test_nearest_geometry_hash(vectors):
+    import triton_augment_b200 as ta
+    for name in vectors["names"]:
+        name = str(name)
+        G, (n, h, w, oh, ow), p, _ = _inputs(vectors, name)
+        got = G.run(ta.functional, G.index_image(n, h, w), p, oh, ow, "nearest", colour=False)
+        idx = got[:, 0].cpu().numpy().astype(np.int32)
+        assert hashlib.sha256(idx.tobytes()).hexdigest() == str(vectors[f"{name}|nearest_index_sha256"]), name
+
+
+@pytest.mark.parametrize("interp", ["nearest", "bilinear"])
+def test_full_pipeline_against_reference_output(vectors, interp):
+    import triton_augment_b200 as ta
+    stride = int(vectors["stride"])
+    for name in vectors["names"]:
+        name = str(name)
+        G, (n, h, w, oh, ow), p, dtype = _inputs(vectors, name)
+        got = G.run(ta.functional, G.procedural_image(n, 3, h, w, dtype), p, oh, ow, interp, colour=True)
+        sub = got[:, :, ::stride, ::stride].cpu().numpy().astype(np.float32)
+        want = vectors[f"{name}|{interp}_sub"].astype(np.float32)
+        tol = 1e-2 if dtype == torch.float16 else 1e-5
+        err = float(np.abs(sub - want).max())
+        assert err <= tol, (name, interp, err)

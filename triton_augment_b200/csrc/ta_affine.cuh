@@ -103,8 +103,8 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
         const int y = y_first + i;
         if (y >= k.oh) break;
         const float yc = centred(img_y(g, y), g.half_h);
-        const float sx = src_coord(xc, g.a, __fmul_rn(g.b, yc), g.c, g.half_w);
-        const float sy = src_coord(xc, g.d, __fmul_rn(g.e, yc), g.f, g.half_h);
+        const float sx = src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+        const float sy = src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
         T s[C];
         if (MODE == 1) {
             const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);

@@ -7,9 +7,12 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 
 // Two source coordinates at once with the packed fp32 pipe; per lane the operation order of
 // src_coord(): ((fma(xc, a, b*yc) + c) + half) + (-0.5), each step rounded to nearest.
+// R picks which product is fused into the addition (see CoordRecipe).
+template <int R>
 __device__ __forceinline__ float2 src_coord2(float xc, float a, float b, float2 yc, float c, float half)
 {
-    float2 u = pk_fma(f2(xc, xc), f2(a, a), pk_mul(f2(b, b), yc));
+    float2 u = R == 1 ? pk_fma(f2(xc, xc), f2(a, a), pk_mul(f2(b, b), yc))
+                      : pk_fma(yc, f2(b, b), pk_mul(f2(a, a), f2(xc, xc)));
     u = pk_add(u, f2(c, c));
     u = pk_add(f2(half, half), u);
     return pk_add(u, f2(-0.5f, -0.5f));
@@ -66,8 +69,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 const int ya = min(y_raw, k.oh - 1), yb = min(y_raw + 1, k.oh - 1);
                 const float2 yc = f2(centred(__fadd_rn(float_of_small_uint(ya), g.top), g.half_h),
                                      centred(__fadd_rn(float_of_small_uint(yb), g.top), g.half_h));
-                const float2 sx = src_coord2(xc, g.a, g.b, yc, g.c, g.half_w);
-                const float2 sy = src_coord2(xc, g.d, g.e, yc, g.f, g.half_h);
+                const float2 sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g.a, g.b, yc, g.c, g.half_w);
+                const float2 sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g.d, g.e, yc, g.f, g.half_h);
                 T smp[2][C];
                 if (MODE == 1) {
 #pragma unroll

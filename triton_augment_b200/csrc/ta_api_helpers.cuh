@@ -52,8 +52,10 @@ __global__ void __launch_bounds__(kThreads) gray_mean_kernel(const __grid_consta
             for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xin, yin, fillv));
         } else {
             const float xc = centred(img_x(g, k.ow, x), g.half_w), yc = centred(img_y(g, y), g.half_h);
-            const float sx = src_coord(xc, g.a, __fmul_rn(g.b, yc), g.c, g.half_w);
-            const float sy = src_coord(xc, g.d, __fmul_rn(g.e, yc), g.f, g.half_h);
+            // the common recipe of the sampling mode; the rarer swapped one moves a coordinate by
+            // one ulp at most, which is invisible in a mean over the whole window
+            const float sx = src_coord_r<CoordRecipe<KIND, 0u>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+            const float sy = src_coord_r<CoordRecipe<KIND, 0u>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
             if (KIND == 1) {
                 const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
 #pragma unroll

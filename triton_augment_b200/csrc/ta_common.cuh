@@ -220,6 +220,28 @@ __device__ __forceinline__ float src_coord(float xc, float a, float b_yc, float 
     return __fadd_rn(u, -0.5f);
 }
 
+// Which of the two products of a*xc + b*yc the reference's GPU build fuses into the addition
+// is a choice its compiler makes per compiled variant (every flag combination is a separate
+// LLVM module).  Measured on a B200 with Triton 3.6 against all 32 colour-flag combinations:
+//   nearest  : x and y use fma(xc, a, b*yc)                                   -> recipe 1, 1
+//   bilinear : x = fma(xc, a, b*yc), y = fma(yc, e, d*xc)                     -> recipe 1, 2
+//              except with (saturation or grayscale) and (brightness or contrast) on,
+//              where x = fma(yc, b, a*xc), y = fma(xc, d, e*yc)               -> recipe 2, 1
+// MODE 1 nearest, 2 bilinear; F the colour flags.
+template <int MODE, unsigned F> struct CoordRecipe {
+    static constexpr bool swapped = MODE == 2 && (F & (kS | kG)) != 0 && (F & (kB | kC)) != 0;
+    static constexpr int x = MODE == 2 ? (swapped ? 2 : 1) : 1;
+    static constexpr int y = MODE == 2 ? (swapped ? 1 : 2) : 1;
+};
+
+template <int R> __device__ __forceinline__ float src_coord_r(float xc, float yc, float a, float b, float c, float half)
+{
+    float u = R == 1 ? __fmaf_rn(xc, a, __fmul_rn(b, yc)) : __fmaf_rn(yc, b, __fmul_rn(a, xc));
+    u = __fadd_rn(u, c);
+    u = __fadd_rn(half, u);
+    return __fadd_rn(u, -0.5f);
+}
+
 // ----------------------------------------------------------------------------- colour tier
 // Restates triton_augment/kernels/fused_kernel.py:234-283.  F holds the compiled-in operations.
 template <typename T, int C, unsigned F> struct Colour;
