@@ -187,7 +187,7 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
 def fused_augment(image, top, left, height: int, width: int, flip_horizontal=False, angle=0.0,
                   translate=[0.0, 0.0], scale=1.0, shear=[0.0, 0.0], interpolation="nearest", fill: float = 0.0,
                   center=None, brightness_factor=1.0, contrast_factor=1.0, saturation_factor=1.0,
-                  grayscale=False, mean=None, std=None, *, contrast_mode="fast", _flags=None) -> torch.Tensor:
+                  grayscale=False, mean=None, std=None, *, contrast_mode="fast", _flags=None, _matrix=None) -> torch.Tensor:
     """Affine + crop + flip + brightness + contrast + saturation + grayscale + normalize, one pass.
 
     Drop-in for the reference's ``fused_augment`` (functional.py:1218-1433): per-image
@@ -225,7 +225,9 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     left_t = _convert_to_tensor(left, n, torch.float32, dev, "left")
     flip_t = _convert_to_tensor(flip_horizontal, n, torch.bool, dev, "flip_horizontal")
     matrix = None
-    if _flags["affine"]:
+    if _flags["affine"] and _matrix is not None:
+        matrix = _matrix                 # built by the caller from these same parameters
+    elif _flags["affine"]:
         matrix = _prepare_affine_matrix_only(n, dev, img_h, img_w, angle, translate, scale, shear, center).contiguous()
     return _run_fused(image, height, width, top_t, left_t, flip_t, matrix, _flags["affine"] and _is_bilinear(interpolation),
                       float(fill), brightness, contrast, saturation, gray,
