@@ -1,7 +1,7 @@
 // Fused inverse-affine + crop + flip + colour + normalize kernel (nearest / bilinear).
 //
 // Persistent, warp-specialised, one CTA per SM.  The CTA walks output tiles of
-// kTileW x kTileH pixels (grid-stride).  PRODUCER warps (one per stage) work ahead of sixteen
+// kTileW x kTileH pixels (grid-stride).  PRODUCER warps (one per stage) work ahead of the
 // CONSUMER warps through a ring of kStages shared-memory stages:
 //
 //   producer  for each tile: work out which source rows the tile reads and, per group of 8
@@ -37,9 +37,23 @@ constexpr int kConsumerWarps = 16;
 constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 constexpr int kPlane = kMaxRows * kPitch;          // elements per channel per stage
+#ifndef TA_PRODUCER_SLEEP_NS
+#define TA_PRODUCER_SLEEP_NS 256
+#endif
+#ifndef TA_CONSUMER_SLEEP_NS
+#define TA_CONSUMER_SLEEP_NS 0
+#endif
+constexpr unsigned kProducerSleepNs = TA_PRODUCER_SLEEP_NS;   // between polls of a stage's "empty" barrier
+constexpr unsigned kConsumerSleepNs = TA_CONSUMER_SLEEP_NS;   // between polls of a stage's "full" barrier
 
+constexpr int kNumGroups = kMaxRows / kGroupRows;
+constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
+
+// The input seen as [N*C, H, W].  rows[g] copies a box of kPitch columns x (g + 1) * kGroupRows
+// rows of one plane: a window tile is one copy per channel.  rows[0] doubles as the per-group
+// box of tiles whose groups start at different columns.
 struct alignas(64) TMaps {
-    CUtensorMap m[kNumBoxWidths];                  // [N*C, H, W] with boxes {box_width(i), 8, 1}
+    CUtensorMap rows[kNumGroups];
 };
 
 template <typename T, int C, unsigned F> struct TileInfo {
@@ -47,13 +61,19 @@ template <typename T, int C, unsigned F> struct TileInfo {
     Colour<T, C, F> col;
     int n, x0, y0;        // image, first output column / row of the tile
     int rows, row0;       // staged source rows (rows == 0: gather this tile from global memory)
-    int bw;               // row pitch of this tile's stage (the box width chosen for it)
-    int rowoff[kMaxRows + 1];   // rowoff[r] + x = element index of texel (row0 + r, x) in a channel plane
+    int window;           // every row starts at column xs0: texel (y, x) sits at element
+    int xs0;              //   (y - row0) * kPitch + (x - xs0) of a channel plane
+    int rowoff[kMaxRows + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
 };
 
+// Shared memory: kStages pixel stages, then kInfoSlots tile descriptors.  Tile number i of a CTA
+// uses stage i % kStages and descriptor i % kInfoSlots, so the producer can write the descriptor
+// of the stage's next tile while the consumers still read the current one, and only the copy
+// itself has to wait for the stage to be released.
 template <typename T, int C, unsigned F> struct AffineSmem {
-    static constexpr size_t stage = ((size_t)C * kPlane * sizeof(T) + sizeof(TileInfo<T, C, F>) + 1023) / 1024 * 1024;
-    static constexpr size_t total = kStages * stage + 1024;   // + slack to align the base to 1 KiB
+    static constexpr size_t stage = ((size_t)C * kPlane * sizeof(T) + 1023) / 1024 * 1024;
+    static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
+    static constexpr size_t total = kStages * stage + kInfoSlots * info + 1024;   // + slack to align the base to 1 KiB
 };
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar)
@@ -72,12 +92,16 @@ __device__ __forceinline__ unsigned long long global_ns()
 }
 
 // Wait for a phase of an mbarrier for at most ~2 s, giving up early when another thread
-// of the CTA has already given up.
+// of the CTA has already given up.  A failed poll comes back after ~60 cycles and the loop
+// around it costs ~8 instructions, so a warp that polls flat out (a producer waits nearly all
+// the time) takes issue slots from the consumers: SLEEP_NS > 0 sleeps between polls.
+template <unsigned SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (int i = 0; i < (1 << 24); ++i) {
+        if (SLEEP_NS) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (*abort_flag) return false;

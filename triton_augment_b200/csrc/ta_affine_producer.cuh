@@ -1,6 +1,10 @@
 // Producer role of the staged affine kernel.  There is one producer warp per stage of the
-// ring: warp p fills stage p for the CTA's tiles p, p + kStages, p + 2 kStages, ... so each
-// producer has kStages tile-times for the arithmetic of one tile.
+// ring: warp p fills stage p for the CTA's tiles p, p + kStages, p + 2 kStages, ...
+//
+// Per tile the warp (1) works out the source footprint and writes the tile's descriptor, (2)
+// waits until the consumers have released the stage, (3) issues the copies.  Only (3) sits
+// between "stage free" and "data on its way", so it is kept to one tensor copy per channel in
+// the common case; everything else is done ahead of the wait.
 #pragma once
 
 namespace ta {
@@ -10,83 +14,77 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                                                 uint64_t *full, uint64_t *empty, volatile int *abort_flag, int p)
 {
     using Info = TileInfo<T, C, F>;
+    using Smem = AffineSmem<T, C, F>;
     constexpr int CH = 16 / (int)sizeof(T);
-    constexpr size_t STAGE = AffineSmem<T, C, F>::stage;
-    constexpr int NGROUPS = kMaxRows / kGroupRows;          // lanes 0 .. NGROUPS-1 each own one row group
-    static_assert(NGROUPS <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
+    static_assert(kNumGroups <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
     const int lane = threadIdx.x & 31;
     const int tiles_per_img = k.tiles_x * k.tiles_y;
-    T *stage = reinterpret_cast<T *>(smem + p * STAGE);
-    Info *ti = reinterpret_cast<Info *>(smem + p * STAGE + (size_t)C * kPlane * sizeof(T));
+    T *stage = reinterpret_cast<T *>(smem + p * Smem::stage);
     unsigned long long n_staged = 0, n_direct = 0;
+#ifdef TA_WAIT_STATS
+    unsigned long long n_issue = 0;
+    long long w_end = clock64();
+#endif
     int cur_n = -1;
     Geom g;
     Colour<T, C, F> col;
 
+    // Tile number -> (image, tile row, tile column), then stepped by kStages * gridDim.x tiles per
+    // round with carries instead of divisions.
+    const int first = (int)blockIdx.x + p * (int)gridDim.x, step = kStages * (int)gridDim.x;
+    int n = first / tiles_per_img, ty = (first % tiles_per_img) / k.tiles_x, tx = (first % tiles_per_img) % k.tiles_x;
+    const int step_n = step / tiles_per_img, step_ty = (step % tiles_per_img) / k.tiles_x,
+              step_tx = (step % tiles_per_img) % k.tiles_x;
+
     int use = 0;
-    for (long long tile = (long long)blockIdx.x + (long long)p * gridDim.x; tile < k.num_tiles;
-         tile += (long long)kStages * gridDim.x, ++use) {
-        const int n = (int)(tile / tiles_per_img);
-        const int t_in = (int)(tile - (long long)n * tiles_per_img);
-        const int ty = t_in / k.tiles_x, tx = t_in - ty * k.tiles_x;
+    for (int tile = first; tile < k.num_tiles; tile += step, ++use) {
         if (n != cur_n) {                                   // per-image parameters: reload on change only
             load_geom(g, k, n, true);
             col.init(k, n);
             cur_n = n;
         }
+        Info *ti = reinterpret_cast<Info *>(smem + kStages * Smem::stage + (size_t)(p + kStages * (use & 1)) * Smem::info);
+
+        // ---- (1) footprint and descriptor
         TileFootprint fp;
         fp.rows = 0;
         fp.row0 = 0;
-        if (k.staged_ok) {
-            const float m[6] = {g.a, g.b, g.c, g.d, g.e, g.f};
-            tile_footprint(fp, MODE - 1, CH, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
-        }
-        bool staged = fp.rows > 0;
-        int gxs = 0, bw = kPitch, bi = kNumBoxWidths - 1;
+        const float m[6] = {g.a, g.b, g.c, g.d, g.e, g.f};
+        if (k.staged_ok) tile_footprint(fp, MODE - 1, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
+        bool staged = fp.rows > 0, window = false;
+        int gxs = 0;
         const int ngroups = (fp.rows + kGroupRows - 1) / kGroupRows;
         if (staged) {
-            // lanes 0 .. NGROUPS-1: columns of row group `lane`; the other lanes hold a neutral entry
-            const int grp = lane;
-            int xs = 0, xe = CH;
-            const int r_first = grp * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
-            if (grp >= ngroups || !tile_rows_range(fp, MODE - 1, CH, r_first, r_last, xs, xe)) { xs = 0; xe = CH; }
-            gxs = xs;
-            int wmax = xe - xs;
-            bool inside = grp >= ngroups || (xs >= 0 && xe <= k.w);
+            window = tile_window(fp, MODE - 1, CH, gxs);
+            bool inside;
+            if (window) {
+                int c0, c1;
+                column_range(MODE - 1, fp.xmin, fp.xmax, c0, c1);
+                inside = c0 >= 0 && c1 < k.w;
+            } else {
+                // lanes 0 .. kNumGroups-1: columns of row group `lane`; the other lanes hold a neutral entry
+                staged = tile_edges(fp, MODE - 1, CH, m);
+                int xs = 0, xe = CH;
+                const int r_first = lane * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
+                const bool have = staged && lane < ngroups && tile_rows_range(fp, MODE - 1, CH, r_first, r_last, xs, xe);
+                if (!have) { xs = 0; xe = CH; }
+                gxs = xs;
+                staged = staged && __all_sync(0xffffffffu, xe - xs <= kPitch);
+                inside = __all_sync(0xffffffffu, !have || (xs >= 0 && xe <= k.w));
+                if (staged) {
+                    // rowoff[r] = r * kPitch - (first column of r's group); rows lane, lane + 32, ...
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) wmax = max(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
-            inside = __all_sync(0xffffffffu, inside) && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
-            bi = wmax <= box_width(0) ? 0 : wmax <= box_width(1) ? 1 : 2;
-            bw = box_width(bi);
-            // fill != 0 cannot rely on TMA's zero fill: stage only tiles that stay inside the image
-            staged = wmax <= kPitch && (k.fill == 0.0f || inside);
-        }
-
-        // The stage must have been released by every consumer warp before it is overwritten.
-        if (use > 0 && !mbar_wait_or_abort(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
-
-        if (staged) {
-            // rowoff[r] = r * bw - (first column of r's group); rows lane, lane + 32, ...
-#pragma unroll
-            for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
-                const int r = base + lane;
-                const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, NGROUPS - 1));
-                if (r < kMaxRows) ti->rowoff[r] = r * bw - x_first;
+                    for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
+                        const int r = base + lane;
+                        const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, kNumGroups - 1));
+                        if (r < kMaxRows) ti->rowoff[r] = r * kPitch - x_first;
+                    }
+                    if (lane == 0) ti->rowoff[kMaxRows] = 0;
+                }
             }
-            if (lane == 0) {
-                ti->rowoff[kMaxRows] = 0;
-                mbar_expect_tx(&full[p], (uint32_t)(ngroups * C * bw * kGroupRows * (int)sizeof(T)));
-            }
-            __syncwarp();
-            if (lane < ngroups) {
-#pragma unroll
-                for (int c = 0; c < C; ++c)
-                    tma_load_3d(stage + c * kPlane + lane * kGroupRows * bw, &maps.m[bi], gxs,
-                                fp.row0 + lane * kGroupRows, n * C + c, &full[p]);
-            }
-            ++n_staged;
-        } else {
-            ++n_direct;
+            // fill != 0 cannot rely on the copy's zero fill: stage only tiles that stay inside the image
+            inside = inside && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
+            staged = staged && (k.fill == 0.0f || inside);
         }
         if (lane == 0) {
             ti->g = g;
@@ -96,11 +94,58 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             ti->y0 = ty * kTileH;
             ti->rows = staged ? fp.rows : 0;
             ti->row0 = fp.row0;
-            ti->bw = bw;
+            ti->window = window ? 1 : 0;
+            ti->xs0 = gxs;
         }
         __syncwarp();
+
+        // ---- (2) the stage must have been released by every consumer warp before it is overwritten
+#ifdef TA_WAIT_STATS
+        const long long w0 = clock64();
+        if (use > 0) n_staged += (unsigned long long)(w0 - w_end);      // compute part
+#endif
+        if (use > 0 && !mbar_wait_or_abort<kProducerSleepNs>(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
+#ifdef TA_WAIT_STATS
+        const long long w1 = clock64();
+        n_direct += (unsigned long long)(w1 - w0);
+#endif
+
+        // ---- (3) copies; the warp's own arrival publishes the descriptor
+        if (staged) {
+            if (lane == 0)
+                mbar_expect_tx(&full[p], (uint32_t)(ngroups * C * kPitch * kGroupRows * (int)sizeof(T)));
+            __syncwarp();
+            if (window) {
+                if (lane < C)         // one box of ngroups * kGroupRows rows per channel
+                    tma_load_3d(stage + lane * kPlane, &maps.rows[ngroups - 1], gxs, fp.row0, n * C + lane, &full[p]);
+            } else if (lane < ngroups) {
+#pragma unroll
+                for (int c = 0; c < C; ++c)
+                    tma_load_3d(stage + c * kPlane + lane * kGroupRows * kPitch, &maps.rows[0], gxs,
+                                fp.row0 + lane * kGroupRows, n * C + c, &full[p]);
+            }
+#ifndef TA_WAIT_STATS
+            ++n_staged;
+        } else {
+            ++n_direct;
+#endif
+        }
         if (lane == 0) mbar_arrive(&full[p]);
+#ifdef TA_WAIT_STATS
+        w_end = clock64();
+        n_issue += (unsigned long long)(w_end - w1);
+#endif
+
+        // next tile of this warp
+        tx += step_tx;
+        if (tx >= k.tiles_x) { tx -= k.tiles_x; ++ty; }
+        ty += step_ty;
+        if (ty >= k.tiles_y) { ty -= k.tiles_y; ++n; }
+        n += step_n;
     }
+#ifdef TA_WAIT_STATS
+    if (lane == 0 && k.counters) atomicAdd(k.counters + kCntViolation, n_issue);
+#endif
     if (lane == 0 && k.counters) {
         if (n_staged) atomicAdd(k.counters + kCntStaged, n_staged);
         if (n_direct) atomicAdd(k.counters + kCntDirect, n_direct);

@@ -5,17 +5,50 @@ namespace ta {
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
+// A packed operand whose halves hold the same value.  Packed instructions read an aligned
+// register pair, so a broadcast scalar costs two register copies wherever it is used unless it
+// lives in a pair of its own; hiding the halves from the optimiser (it would otherwise merge
+// two copies of one value and re-create the pair at every use) keeps it there.
+__device__ __forceinline__ float2 bcast(float v)
+{
+    float2 p = make_float2(v, v);
+#ifndef TA_NO_PINNED_PAIRS
+    asm volatile("" : "+f"(p.x), "+f"(p.y));
+#endif
+    return p;
+}
+
+// Per-image geometry as packed operands.
+struct Geom2 {
+    float2 a, b, c, d, e, f, half_w, half_h, top, neg_half_h;
+    __device__ __forceinline__ void set(const Geom &g)
+    {
+        a = bcast(g.a); b = bcast(g.b); c = bcast(g.c); d = bcast(g.d); e = bcast(g.e); f = bcast(g.f);
+        half_w = bcast(g.half_w); half_h = bcast(g.half_h); top = bcast(g.top); neg_half_h = bcast(-g.half_h);
+    }
+};
+
+// Literal constants as packed operands, set up once per thread.
+struct Const2 {
+    float2 half, neg_half, one, neg_one, magic, neg_magic, neg_two23;
+    __device__ __forceinline__ void set()
+    {
+        half = bcast(0.5f); neg_half = bcast(-0.5f); one = bcast(1.0f); neg_one = bcast(-1.0f);
+        magic = bcast(kMagic); neg_magic = bcast(-kMagic); neg_two23 = bcast(-8388608.0f);
+    }
+};
+
 // Two source coordinates at once with the packed fp32 pipe; per lane the operation order of
 // src_coord(): ((fma(xc, a, b*yc) + c) + half) + (-0.5), each step rounded to nearest.
 // R picks which product is fused into the addition (see CoordRecipe).
 template <int R>
-__device__ __forceinline__ float2 src_coord2(float xc, float a, float b, float2 yc, float c, float half)
+__device__ __forceinline__ float2 src_coord2(float2 xc, float2 a, float2 b, float2 yc, float2 c, float2 half,
+                                             float2 neg_half)
 {
-    float2 u = R == 1 ? pk_fma(f2(xc, xc), f2(a, a), pk_mul(f2(b, b), yc))
-                      : pk_fma(yc, f2(b, b), pk_mul(f2(a, a), f2(xc, xc)));
-    u = pk_add(u, f2(c, c));
-    u = pk_add(f2(half, half), u);
-    return pk_add(u, f2(-0.5f, -0.5f));
+    float2 u = R == 1 ? pk_fma(xc, a, pk_mul(b, yc)) : pk_fma(yc, b, pk_mul(a, xc));
+    u = pk_add(u, c);
+    u = pk_add(half, u);
+    return pk_add(u, neg_half);
 }
 
 }  // namespace ta
@@ -25,29 +58,196 @@ __device__ __forceinline__ float2 src_coord2(float xc, float a, float b, float2 
 namespace ta {
 
 // ----------------------------------------------------------------------------- consumer
+// Texels of one pixel pair (two output rows, same column) from a stage, two ways.
+//
+// Window path (TileInfo::window): all staged rows start at column xs0, so texel (y, x) lives at
+// byte  stage + ES * ((y - row0) * kPitch + (x - xs0)).  The integers y and x never exist as
+// such: adding 1.5 * 2^23 to a coordinate leaves rint / floor of it in the low bits of the
+// float, and address = kb + ES * kPitch * bits(y) + ES * bits(x) with every constant (stage
+// base, row0, xs0, the two magic offsets) folded into kb once per tile, modulo 2^32.
+//
+// Table path: each row group has its own first column; rowoff[] translates.
+template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
+    static constexpr uint32_t ES = sizeof(T), ROWB = ES * kPitch, PLANEB = ES * kPlane;
+
+    // -> smp[j][c], j = 0 / 1 for the pair's first / second row
+    static __device__ __forceinline__ void window(const Const2 &k2, uint32_t stage_addr, uint32_t kb, int rows, int row0,
+                                                  int xs0, float2 sx, float2 sy, T (&smp)[2][C],
+                                                  unsigned long long &n_viol)
+    {
+        const float2 magic = k2.magic, unmagic = k2.neg_magic;
+        if (MODE == 1) {
+            const float2 tx = pk_add(sx, magic), ty = pk_add(sy, magic);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t bx = __float_as_uint(j ? tx.y : tx.x), by = __float_as_uint(j ? ty.y : ty.x);
+                uint32_t addr = kb + by * ROWB + bx * ES;
+                if (CHECK) {
+                    const int r = (int)(by - (uint32_t)kMagicBits) - row0, x = (int)(bx - (uint32_t)kMagicBits) - xs0;
+                    if ((unsigned)r >= (unsigned)rows || (unsigned)x >= (unsigned)kPitch) { ++n_viol; addr = stage_addr; }
+                }
+#pragma unroll
+                for (int c = 0; c < C; ++c) smp[j][c] = Elem<T>::lds(addr + c * PLANEB);
+            }
+        } else {
+            const float2 tx = pk_add_rd(sx, magic), ty = pk_add_rd(sy, magic);
+            const float2 neg = k2.neg_one, one = k2.one;
+            const float2 dx = pk_fma(pk_add(tx, unmagic), neg, sx);      // s - floor(s), exact
+            const float2 dy = pk_fma(pk_add(ty, unmagic), neg, sy);
+            uint32_t addr[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t bx = __float_as_uint(j ? tx.y : tx.x), by = __float_as_uint(j ? ty.y : ty.x);
+                addr[j] = kb + by * ROWB + bx * ES;
+                if (CHECK) {
+                    const int r = (int)(by - (uint32_t)kMagicBits) - row0, x = (int)(bx - (uint32_t)kMagicBits) - xs0;
+                    if ((unsigned)r >= (unsigned)(rows - 1) || (unsigned)x >= (unsigned)(kPitch - 1)) {
+                        ++n_viol; addr[j] = stage_addr;
+                    }
+                }
+            }
+            const float2 omx = pk_fma(dx, neg, one), omy = pk_fma(dy, neg, one);   // 1 - d, one rounding
+            const float2 w00 = pk_mul(omx, omy), w10 = pk_mul(dx, omy);
+            const float2 w01 = pk_mul(omx, dy), w11 = pk_mul(dx, dy);
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const uint32_t a0 = addr[0] + c * PLANEB, a1 = addr[1] + c * PLANEB;
+                float2 acc = pk_mul(f2(Elem<T>::to_f(Elem<T>::lds(a0)), Elem<T>::to_f(Elem<T>::lds(a1))), w00);
+                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ES)), Elem<T>::to_f(Elem<T>::lds(a1 + ES))), w10, acc);
+                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ROWB)), Elem<T>::to_f(Elem<T>::lds(a1 + ROWB))), w01, acc);
+                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ROWB + ES)), Elem<T>::to_f(Elem<T>::lds(a1 + ROWB + ES))), w11, acc);
+                smp[0][c] = Elem<T>::from_f(acc.x);
+                smp[1][c] = Elem<T>::from_f(acc.y);
+            }
+        }
+    }
+
+    static __device__ __forceinline__ void table(const Const2 &k2, const T *stage, const int *rowoff, int rows,
+                                                 int row0, float2 sx, float2 sy, T (&smp)[2][C],
+                                                 unsigned long long &n_viol)
+    {
+        if (MODE == 1) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int xn = rint_magic(j ? sx.y : sx.x);
+                int r = rint_magic(j ? sy.y : sy.x) - row0;
+                if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
+                int idx = rowoff[r] + xn;
+                if (CHECK && (unsigned)(idx - r * kPitch) >= (unsigned)kPitch) { ++n_viol; idx = 0; }
+#pragma unroll
+                for (int c = 0; c < C; ++c) smp[j][c] = stage[c * kPlane + idx];
+            }
+        } else {
+            int i0[2], i1[2];
+            float2 dx, dy;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float frac_x, frac_y;
+                const int x0 = floor_magic(j ? sx.y : sx.x, frac_x), y0 = floor_magic(j ? sy.y : sy.x, frac_y);
+                (j ? dx.y : dx.x) = frac_x;
+                (j ? dy.y : dy.x) = frac_y;
+                int r = y0 - row0;
+                if (CHECK && (unsigned)r >= (unsigned)(rows - 1)) { ++n_viol; r = 0; }
+                i0[j] = rowoff[r] + x0;
+                i1[j] = rowoff[r + 1] + x0;
+                if (CHECK && ((unsigned)(i0[j] - r * kPitch) >= (unsigned)(kPitch - 1) ||
+                              (unsigned)(i1[j] - (r + 1) * kPitch) >= (unsigned)(kPitch - 1))) {
+                    ++n_viol; i0[j] = i1[j] = 0;
+                }
+            }
+            const float2 one = k2.one, neg = k2.neg_one;
+            const float2 omx = pk_fma(dx, neg, one), omy = pk_fma(dy, neg, one);
+            const float2 w00 = pk_mul(omx, omy), w10 = pk_mul(dx, omy);
+            const float2 w01 = pk_mul(omx, dy), w11 = pk_mul(dx, dy);
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+                const T *pl = stage + c * kPlane;
+                float2 acc = pk_mul(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
+                acc = pk_fma(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
+                acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
+                acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
+                smp[0][c] = Elem<T>::from_f(acc.x);
+                smp[1][c] = Elem<T>::from_f(acc.y);
+            }
+        }
+    }
+};
+
+// Colour tier and stores of one pixel pair.  `row_a` points at the pair's first output
+// pixel in channel 0; channels are `oplane` elements apart, the second row `ow` elements on.
+template <typename T, int C, unsigned F>
+__device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F> &col, T (&smp)[2][C], T *row_a,
+                                            unsigned oplane, bool a_ok, bool b_ok)
+{
+#ifdef TA_COLOUR_PACKED
+    constexpr bool packed_colour = sizeof(T) == 4;
+#else
+    // The colour tier's packed form needs eleven broadcast operand pairs for thirteen packed
+    // instructions; there are no registers to keep those pairs in, and re-creating them costs
+    // more than the packing saves.
+    constexpr bool packed_colour = false;
+#endif
+    if constexpr (packed_colour) {
+        float2 v2[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) v2[c] = f2(smp[0][c], smp[1][c]);
+        col.apply2(k, v2);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            if (a_ok) Elem<T>::store(row_a + (size_t)c * oplane, v2[c].x);
+            if (b_ok) Elem<T>::store(row_a + (size_t)c * oplane + k.ow, v2[c].y);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float v[C];
+            col.apply(k, smp[j], v);
+            if (j == 0 ? a_ok : b_ok) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) Elem<T>::store(row_a + (size_t)c * oplane + j * k.ow, v[c]);
+            }
+        }
+    }
+}
+
 template <typename T, int C, int MODE, unsigned F, bool CHECK>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
                                                 volatile int *abort_flag)
 {
     using Info = TileInfo<T, C, F>;
-    constexpr size_t STAGE = AffineSmem<T, C, F>::stage;
+    using Sampler = PairSampler<T, C, MODE, CHECK>;
+    using Smem = AffineSmem<T, C, F>;
     constexpr int ROWS_PER_WARP = kTileH / (kConsumerWarps / 2);     // 4
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
     unsigned long long n_viol = 0;
+#ifdef TA_WAIT_STATS
+    long long wait_cycles = 0;
+    const long long t_begin = clock64();
+#endif
     int cur_n = -1;
     Geom g;
+    Geom2 g2;
+    Const2 k2;
+    k2.set();
     Colour<T, C, F> col;
     int it = 0;
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
         const int s = it % kStages, use = it / kStages;
-        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
-        const T *stage = reinterpret_cast<const T *>(smem + s * STAGE);
-        const Info *ti = reinterpret_cast<const Info *>(smem + s * STAGE + (size_t)C * kPlane * sizeof(T));
+#ifdef TA_WAIT_STATS
+        const long long w0 = clock64();
+#endif
+        if (!mbar_wait_or_abort<kConsumerSleepNs>(&full[s], (uint32_t)use & 1u, abort_flag)) return;
+#ifdef TA_WAIT_STATS
+        wait_cycles += clock64() - w0;
+#endif
+        const T *stage = reinterpret_cast<const T *>(smem + s * Smem::stage);
+        const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
         const int n = ti->n, rows = ti->rows, row0 = ti->row0;
         if (n != cur_n) {            // per-image parameters change only every few tiles (warp-uniform branch)
             g = ti->g;
+            g2.set(g);
             col = ti->col;
             cur_n = n;
         }
@@ -57,8 +257,13 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         if (rows == 0) {
             affine_rows_direct<T, C, MODE, F>(k, g, col, n, x, y_first, ROWS_PER_WARP);
         } else if (x < k.ow) {
-            T *out = (T *)k.out + (size_t)n * C * oplane;
-            const float xc = centred(img_x(g, k.ow, x), g.half_w);
+            T *out = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
+            const float2 xc = bcast(centred(img_x(g, k.ow, x), g.half_w));
+            const bool window = ti->window != 0;
+            const int xs0 = ti->xs0;
+            const uint32_t stage_addr = smem_u32(stage);
+            const uint32_t kb = stage_addr - Sampler::ES * (uint32_t)(row0 * kPitch + xs0)
+                                - Sampler::ES * (uint32_t)(kPitch + 1) * (uint32_t)kMagicBits;
 #pragma unroll
             for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
                 // No early exit: rows past the image's last row are computed on the last row's
@@ -67,84 +272,28 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 const int y_raw = y_first + 2 * pr;
                 const bool a_ok = y_raw < k.oh, b_ok = y_raw + 1 < k.oh;
                 const int ya = min(y_raw, k.oh - 1), yb = min(y_raw + 1, k.oh - 1);
-                const float2 yc = f2(centred(__fadd_rn(float_of_small_uint(ya), g.top), g.half_h),
-                                     centred(__fadd_rn(float_of_small_uint(yb), g.top), g.half_h));
-                const float2 sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g.a, g.b, yc, g.c, g.half_w);
-                const float2 sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g.d, g.e, yc, g.f, g.half_h);
+                // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred()
+                float2 yc = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
+                yc = pk_add(yc, g2.top);
+                yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
+                const float2 sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                const float2 sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
                 T smp[2][C];
-                if (MODE == 1) {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int xn = rint_magic(j ? sx.y : sx.x);
-                        int r = rint_magic(j ? sy.y : sy.x) - row0;
-                        if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
-                        int idx = ti->rowoff[r] + xn;
-                        if (CHECK && (unsigned)(idx - r * ti->bw) >= (unsigned)ti->bw) { ++n_viol; idx = 0; }
-#pragma unroll
-                        for (int c = 0; c < C; ++c) smp[j][c] = stage[c * kPlane + idx];
-                    }
-                } else {
-                    int i0[2], i1[2];
-                    float2 dx, dy;
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const float fx = j ? sx.y : sx.x, fy = j ? sy.y : sy.x;
-                        float frac_x, frac_y;
-                        const int x0 = floor_magic(fx, frac_x), y0 = floor_magic(fy, frac_y);
-                        (j ? dx.y : dx.x) = frac_x;
-                        (j ? dy.y : dy.x) = frac_y;
-                        int r = y0 - row0;
-                        if (CHECK && (unsigned)r >= (unsigned)(rows - 1)) { ++n_viol; r = 0; }
-                        i0[j] = ti->rowoff[r] + x0;
-                        i1[j] = ti->rowoff[r + 1] + x0;
-                        if (CHECK && ((unsigned)(i0[j] - r * ti->bw) >= (unsigned)(ti->bw - 1) ||
-                                      (unsigned)(i1[j] - (r + 1) * ti->bw) >= (unsigned)(ti->bw - 1))) {
-                            ++n_viol; i0[j] = i1[j] = 0;
-                        }
-                    }
-                    const float2 one = f2(1.0f, 1.0f), neg = f2(-1.0f, -1.0f);
-                    const float2 omx = pk_fma(dx, neg, one), omy = pk_fma(dy, neg, one);   // 1 - d, one rounding
-                    const float2 w00 = pk_mul(omx, omy), w10 = pk_mul(dx, omy);
-                    const float2 w01 = pk_mul(omx, dy), w11 = pk_mul(dx, dy);
-#pragma unroll
-                    for (int c = 0; c < C; ++c) {
-                        const T *pl = stage + c * kPlane;
-                        float2 acc = pk_mul(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
-                        acc = pk_fma(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
-                        acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
-                        acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
-                        smp[0][c] = Elem<T>::from_f(acc.x);
-                        smp[1][c] = Elem<T>::from_f(acc.y);
-                    }
-                }
-                const unsigned o = (unsigned)(y_raw * k.ow + x);
-                if constexpr (sizeof(T) == 4) {
-                    float2 v2[C];
-#pragma unroll
-                    for (int c = 0; c < C; ++c) v2[c] = f2(smp[0][c], smp[1][c]);
-                    col.apply2(k, v2);
-#pragma unroll
-                    for (int c = 0; c < C; ++c) {
-                        if (a_ok) Elem<T>::store(out + (size_t)c * oplane + o, v2[c].x);
-                        if (b_ok) Elem<T>::store(out + (size_t)c * oplane + o + k.ow, v2[c].y);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        float v[C];
-                        col.apply(k, smp[j], v);
-                        if (j == 0 ? a_ok : b_ok) {
-#pragma unroll
-                            for (int c = 0; c < C; ++c) Elem<T>::store(out + (size_t)c * oplane + o + j * k.ow, v[c]);
-                        }
-                    }
-                }
+                if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
+                else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
+                finish_pair<T, C, F>(k, col, smp, out + (size_t)(2 * pr) * k.ow, oplane, a_ok, b_ok);
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
     }
     if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
+#ifdef TA_WAIT_STATS
+    if (lane == 0 && k.counters) {
+        (void)wait_cycles;
+        if (warp == 0) atomicAdd(k.counters + kCntTimeout, (unsigned long long)(clock64() - t_begin));  // one warp per CTA
+    }
+#endif
 }
 
 // ----------------------------------------------------------------------------- kernel

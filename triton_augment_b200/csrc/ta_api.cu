@@ -193,8 +193,8 @@ static EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
-// Tensor maps over the input seen as [n*c, h, w]: boxes of box_width(i) x 8 rows x 1 plane,
-// out-of-range elements read as zero.
+// Tensor maps over the input seen as [n*c, h, w]: boxes of kPitch columns x 8, 16, ... kMaxRows
+// rows x 1 plane, out-of-range elements read as zero.
 static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
 {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -203,9 +203,9 @@ static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
     const cuuint64_t dims[3] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->n * p->c};
     const cuuint64_t strides[2] = {(cuuint64_t)p->w * es, (cuuint64_t)p->w * p->h * es};
     const cuuint32_t estr[3] = {1, 1, 1};
-    for (int i = 0; i < kNumBoxWidths; ++i) {
-        const cuuint32_t box[3] = {(cuuint32_t)box_width(i), (cuuint32_t)kGroupRows, 1};
-        CUresult r = enc(&maps.m[i], p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+    for (int g = 0; g < kNumGroups; ++g) {
+        const cuuint32_t box[3] = {(cuuint32_t)kPitch, (cuuint32_t)((g + 1) * kGroupRows), 1};
+        CUresult r = enc(&maps.rows[g], p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                          3, const_cast<void *>(p->in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
@@ -262,7 +262,8 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         work = (long long)p->n * k.tiles_x * k.tiles_y;
     }
     const long long tiles = (long long)p->n * k.tiles_x * k.tiles_y;
-    if (tiles >= 2147483647LL) return fail(TA_B200_ERR_TOO_LARGE, "too many tiles (%lld)", tiles);
+    // 32-bit tile counters in the kernels are stepped past the end by up to a few grid strides
+    if (tiles >= 2147483647LL - (1 << 24)) return fail(TA_B200_ERR_TOO_LARGE, "too many tiles (%lld)", tiles);
     k.num_tiles = (int)tiles;
     // Persistent launch: one wave of resident CTAs, fewer when there is less work.
     long long grid = (long long)s->sm_count * blocks;

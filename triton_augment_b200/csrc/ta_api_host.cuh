@@ -223,16 +223,15 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
 {
     ta::TileFootprint fp;
     const int chunk = 16 / (elem_bytes == 2 ? 2 : 4);
-    ta::tile_footprint(fp, interp == TA_B200_BILINEAR ? 1 : 0, chunk, h, w, oh, ow, top, left, flip != 0, matrix,
-                       tile_x, tile_y);
+    const int mode = interp == TA_B200_BILINEAR ? 1 : 0;
+    ta::tile_footprint(fp, mode, h, w, oh, ow, top, left, flip != 0, matrix, tile_x, tile_y);
     if (row0) *row0 = fp.row0;
-    if (fp.rows == 0) return 0;
     int group_xs[ta::kMaxRows / ta::kGroupRows];
-    const int bw = ta::tile_group_plan(fp, interp == TA_B200_BILINEAR ? 1 : 0, chunk, group_xs);
-    if (bw == 0) return 0;
+    bool window = false;
+    if (!ta::tile_plan(fp, mode, chunk, matrix, group_xs, &window)) return 0;
     for (int r = 0; r < fp.rows && r < cap; ++r) {
         xs[r] = group_xs[r / ta::kGroupRows];
-        xe[r] = xs[r] + bw;
+        xe[r] = xs[r] + ta::kPitch;
     }
     return fp.rows;
 }

@@ -80,28 +80,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait: false when the phase did not complete within the poll budget.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity)
-{
-    for (int i = 0; i < (1 << 20); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
-
-// Bulk asynchronous copy global -> this CTA's shared memory, completion counted in
-// bytes on an mbarrier.  Addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void fence_proxy_async()
-{
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 // ----------------------------------------------------------------------------- packed fp32
 // Two independent IEEE round-to-nearest operations per instruction on sm_100 (fma.rn.f32x2 and
 // friends).  -DTA_NO_PACKED builds the same arithmetic from scalar instructions.
@@ -127,6 +105,15 @@ __device__ __forceinline__ float2 pk_add(float2 a, float2 b)
     return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
 #else
     return __fadd2_rn(a, b);
+#endif
+}
+// Packed addition rounded towards minus infinity (the floor step of floor_magic, two at once).
+__device__ __forceinline__ float2 pk_add_rd(float2 a, float2 b)
+{
+#ifdef TA_NO_PACKED
+    return make_float2(__fadd_rd(a.x, b.x), __fadd_rd(a.y, b.y));
+#else
+    return __fadd2_rd(a, b);
 #endif
 }
 
@@ -158,6 +145,13 @@ template <typename T> struct Elem;
 template <> struct Elem<float> {
     static __device__ __forceinline__ float to_f(float v) { return v; }
     static __device__ __forceinline__ float from_f(float v) { return v; }
+    // load from a 32-bit shared-memory address (constant offsets fold into the instruction)
+    static __device__ __forceinline__ float lds(uint32_t addr)
+    {
+        float v;
+        asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+        return v;
+    }
     static __device__ __forceinline__ void store(float *p, float v)
     {
 #ifdef TA_STREAMING_STORES       // st.global.cs measured no better than plain stores (0-2 % worse)
@@ -170,6 +164,12 @@ template <> struct Elem<float> {
 template <> struct Elem<__half> {
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+    static __device__ __forceinline__ __half lds(uint32_t addr)
+    {
+        unsigned short v;
+        asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+        return __ushort_as_half(v);
+    }
     static __device__ __forceinline__ void store(__half *p, float v)
     {
         __stcs(reinterpret_cast<unsigned short *>(p), __half_as_ushort(__float2half_rn(v)));

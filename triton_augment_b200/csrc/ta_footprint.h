@@ -29,23 +29,25 @@ constexpr int kTileW = 64;       // output tile, pixels
 constexpr int kTileH = 32;
 constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 groups of 8 rows)
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
-constexpr int kPitch = 96;       // widest staged row, in elements
-constexpr int kNumBoxWidths = 3; // tensor-copy box widths to choose from per tile
-// A row pitch that is a multiple of 32 words keeps lanes of one warp that sit in different
-// source rows on different banks; narrower boxes save L2 traffic but cost 2-way conflicts.
-TA_HD int box_width(int i) { return i == 0 ? kPitch : i == 1 ? kPitch : kPitch; }
+constexpr int kPitch = 96;       // staged row pitch = width of every tensor-copy box, in elements.
+// A pitch that is a multiple of 32 words keeps lanes of one warp that sit in different source
+// rows on different banks (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but
+// 2-way bank conflicts cost more than they saved).
 constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
 constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
 
 struct TileFootprint {
     float sx[4], sy[4];   // source coordinates of the tile's corners (x0y0, x1y0, x1y1, x0y1)
-    float inv[4];         // 1 / (sy[j] - sy[i]) per edge, 0 when the edge is level
+    float inv[4];         // 1 / (sy[j] - sy[i]) per edge, 0 when the edge is level (tile_edges())
+    float xmin, xmax;     // extreme source x of the corners
+    float dx, dy;         // extent of the tile in centred output coordinates
     int row0;             // first source row
     int rows;             // number of source rows (0 = do not stage)
 };
 
-// mode: 0 nearest (reads row rint(sy)), 1 bilinear (reads rows floor(sy), floor(sy)+1)
-TA_HD void tile_footprint(TileFootprint &t, int mode, int chunk, int h, int w, int oh, int ow,
+// Corners, rows and bounding box.  mode: 0 nearest (reads row rint(sy)), 1 bilinear (reads rows
+// floor(sy), floor(sy)+1).  rows == 0 on return: the tile is not staged.
+TA_HD void tile_footprint(TileFootprint &t, int mode, int h, int w, int oh, int ow,
                           float top, float left, bool flip, const float *m, int tile_x, int tile_y)
 {
     const int x_first = tile_x * kTileW, y_first = tile_y * kTileH;
@@ -58,43 +60,68 @@ TA_HD void tile_footprint(TileFootprint &t, int mode, int chunk, int h, int w, i
     const float yc0 = (float)y_first + top - half_h + 0.5f, yc1 = (float)y_last + top - half_h + 0.5f;
     const float cx[4] = {xc0, xc1, xc1, xc0}, cy[4] = {yc0, yc0, yc1, yc1};
     float ymin = INFINITY, ymax = -INFINITY, xmin = INFINITY, xmax = -INFINITY;
+    // Per corner and written so that a NaN fails (fminf/fmaxf drop NaNs).
+    bool sane = true;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         t.sx[i] = (m[0] * cx[i] + m[1] * cy[i] + m[2]) + half_w - 0.5f;
         t.sy[i] = (m[3] * cx[i] + m[4] * cy[i] + m[5]) + half_h - 0.5f;
         ymin = fminf(ymin, t.sy[i]); ymax = fmaxf(ymax, t.sy[i]);
         xmin = fminf(xmin, t.sx[i]); xmax = fmaxf(xmax, t.sx[i]);
+        sane = sane && fabsf(t.sx[i]) < kCoordLimit && fabsf(t.sy[i]) < kCoordLimit;
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float d = t.sy[(i + 1) & 3] - t.sy[i];
-        t.inv[i] = d != 0.0f ? 1.0f / d : 0.0f;
-    }
+    t.xmin = xmin; t.xmax = xmax;
+    t.dx = xc1 - xc0; t.dy = yc1 - yc0;
     t.rows = 0;
     t.row0 = 0;
-    // Per corner and written so that a NaN fails (fminf/fmaxf above drop NaNs).
-    bool sane = true;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sane = sane && fabsf(t.sx[i]) < kCoordLimit && fabsf(t.sy[i]) < kCoordLimit;
     if (!sane) return;
     int r0, r1;
     if (mode == 0) { r0 = (int)ceilf(ymin - kEps - 0.5f); r1 = (int)floorf(ymax + kEps + 0.5f); }
     else           { r0 = (int)floorf(ymin - kEps);       r1 = (int)floorf(ymax + kEps) + 1; }
     const int rows = r1 - r0 + 1;
     if (rows < 1 || rows > kMaxRows) return;
-    // Upper bound of any row's column span.  Inside a slab of height s in source y,
-    // eliminating yc gives sx = (a - b d / e) xc + (b / e) sy + const and eliminating xc
-    // gives sx = (b - a e / d) yc + (a / d) sy + const; either bounds the span.
-    const float s = (mode == 0 ? 1.0f : 2.0f) + 2.0f * kEps;
-    const float dx = xc1 - xc0, dy = yc1 - yc0;
-    float span = INFINITY;
-    if (m[4] != 0.0f) span = fminf(span, fabsf(m[0] - m[1] * m[3] / m[4]) * dx + fabsf(m[1] / m[4]) * s);
-    if (m[3] != 0.0f) span = fminf(span, fabsf(m[1] - m[0] * m[4] / m[3]) * dy + fabsf(m[0] / m[3]) * s);
-    span = fminf(span, xmax - xmin);
-    // + 2 eps, + the second tap / rounding to nearest, + rounding both ends to whole chunks
-    if (!(span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)kPitch)) return;
     t.row0 = r0;
     t.rows = rows;
+}
+
+// floor / ceil of a column to a multiple of `chunk`, valid for negative columns
+TA_HD int chunk_floor(int c, int chunk) { return (c >= 0 ? c / chunk : -((-c + chunk - 1) / chunk)) * chunk; }
+TA_HD int chunk_ceil(int c, int chunk) { return (c >= 0 ? (c + chunk - 1) / chunk : -((-c) / chunk)) * chunk; }
+
+// Inclusive column range read around source x in [lo, hi].
+TA_HD void column_range(int mode, float lo, float hi, int &c0, int &c1)
+{
+    if (mode == 0) { c0 = (int)ceilf(lo - kEps - 0.5f); c1 = (int)floorf(hi + kEps + 0.5f); }
+    else           { c0 = (int)floorf(lo - kEps);       c1 = (int)floorf(hi + kEps) + 1; }
+}
+
+// The common case: one window of kPitch columns starting at xs (a multiple of `chunk`) covers
+// every row the tile reads, i.e. the bounding box of the corners fits.
+TA_HD bool tile_window(const TileFootprint &t, int mode, int chunk, int &xs)
+{
+    int c0, c1;
+    column_range(mode, t.xmin, t.xmax, c0, c1);
+    xs = chunk_floor(c0, chunk);
+    return c1 + 1 - xs <= kPitch;
+}
+
+// Otherwise rows are fetched in groups with a window each; this prepares the per-edge terms
+// tile_rows_range() needs and checks that no group can be wider than a window.  Inside a slab
+// of height s in source y, eliminating yc gives sx = (a - b d / e) xc + (b / e) sy + const and
+// eliminating xc gives sx = (b - a e / d) yc + (a / d) sy + const; either bounds a row's span.
+TA_HD bool tile_edges(TileFootprint &t, int mode, int chunk, const float *m)
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float d = t.sy[(i + 1) & 3] - t.sy[i];
+        t.inv[i] = d != 0.0f ? 1.0f / d : 0.0f;
+    }
+    const float s = (mode == 0 ? 1.0f : 2.0f) + 2.0f * kEps;
+    float span = t.xmax - t.xmin;
+    if (m[4] != 0.0f) span = fminf(span, fabsf(m[0] - m[1] * m[3] / m[4]) * t.dx + fabsf(m[1] / m[4]) * s);
+    if (m[3] != 0.0f) span = fminf(span, fabsf(m[1] - m[0] * m[4] / m[3]) * t.dy + fabsf(m[0] / m[3]) * s);
+    // + 2 eps, + the second tap / rounding to nearest, + rounding both ends to whole chunks
+    return span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)kPitch;
 }
 
 // Columns [xs, xe) of source row row0 + r that the tile reads, rounded outward to
@@ -133,34 +160,35 @@ TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_fi
     }
     if (!(lo <= hi)) { xs = 0; xe = 0; return false; }
     int c0, c1;   // inclusive column range
-    if (mode == 0) { c0 = (int)ceilf(lo - kEps - 0.5f); c1 = (int)floorf(hi + kEps + 0.5f); }
-    else           { c0 = (int)floorf(lo - kEps);       c1 = (int)floorf(hi + kEps) + 1; }
-    // floor / ceil to chunk multiples, valid for negative columns
-    int q0 = c0 >= 0 ? c0 / chunk : -((-c0 + chunk - 1) / chunk);
-    int q1 = c1 + 1 >= 0 ? (c1 + 1 + chunk - 1) / chunk : -((-(c1 + 1)) / chunk);
-    xs = q0 * chunk;
-    xe = q1 * chunk;
+    column_range(mode, lo, hi, c0, c1);
+    xs = chunk_floor(c0, chunk);
+    xe = chunk_ceil(c1 + 1, chunk);
     return true;
 }
 
-// What is actually fetched: rows in groups of kGroupRows, every group one box whose first
-// column is the smallest xs of its rows and whose width is the narrowest box_width() that
-// covers the widest group.  Scalar restatement of what the producer warp computes with
-// shuffles; returns the box width, or 0 when some group is wider than the widest box
-// (then the tile is not staged).  group_xs has kMaxRows / kGroupRows entries.
-TA_HD int tile_group_plan(const TileFootprint &t, int mode, int chunk, int *group_xs)
+// What is actually fetched.  Window case: all rows, kPitch columns from *group_xs.  Otherwise
+// rows in groups of kGroupRows, every group kPitch columns from the smallest xs of its rows
+// (group_xs has kMaxRows / kGroupRows entries).  Scalar restatement of the producer warp's
+// decisions; returns false when the tile is not staged.
+TA_HD bool tile_plan(TileFootprint &t, int mode, int chunk, const float *m, int *group_xs, bool *window)
 {
-    int wmax = 0;
+    if (t.rows == 0) return false;
+    int xs;
+    *window = tile_window(t, mode, chunk, xs);
+    if (*window) {
+        for (int g = 0; g < kMaxRows / kGroupRows; ++g) group_xs[g] = xs;
+        return true;
+    }
+    if (!tile_edges(t, mode, chunk, m)) return false;
     for (int g = 0; g < kMaxRows / kGroupRows; ++g) {
         int lo = 0, hi = chunk;
         const int r_first = g * kGroupRows;
         const int r_last = r_first + kGroupRows - 1 < t.rows - 1 ? r_first + kGroupRows - 1 : t.rows - 1;
         if (r_first >= t.rows || !tile_rows_range(t, mode, chunk, r_first, r_last, lo, hi)) { lo = 0; hi = chunk; }
+        if (hi - lo > kPitch) return false;
         group_xs[g] = lo;
-        wmax = hi - lo > wmax ? hi - lo : wmax;
     }
-    if (wmax > kPitch) return 0;
-    return wmax <= box_width(0) ? box_width(0) : wmax <= box_width(1) ? box_width(1) : box_width(2);
+    return true;
 }
 
 }  // namespace ta
