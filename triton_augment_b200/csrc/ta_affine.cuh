@@ -56,13 +56,14 @@ struct alignas(64) TMaps {
     CUtensorMap rows[kNumGroups];
 };
 
-template <typename T, int C, unsigned F> struct TileInfo {
-    Geom g;
-    Colour<T, C, F> col;
+template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int n, x0, y0;        // image, first output column / row of the tile
     int rows, row0;       // staged source rows (rows == 0: gather this tile from global memory)
     int window;           // every row starts at column xs0: texel (y, x) sits at element
     int xs0;              //   (y - row0) * kPitch + (x - xs0) of a channel plane
+    int pad;
+    Geom g;
+    Colour<T, C, F> col;
     int rowoff[kMaxRows + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
 };
 
@@ -73,7 +74,7 @@ template <typename T, int C, unsigned F> struct TileInfo {
 template <typename T, int C, unsigned F> struct AffineSmem {
     static constexpr size_t stage = ((size_t)C * kPlane * sizeof(T) + 1023) / 1024 * 1024;
     static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
-    static constexpr size_t total = kStages * stage + kInfoSlots * info + 1024;   // + slack to align the base to 1 KiB
+    static constexpr size_t total = kStages * stage + kInfoSlots * info;
 };
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar)

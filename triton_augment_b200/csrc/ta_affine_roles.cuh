@@ -173,19 +173,24 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
     }
 };
 
-// Colour tier and stores of one pixel pair.  `row_a` points at the pair's first output
-// pixel in channel 0; channels are `oplane` elements apart, the second row `ow` elements on.
+// Colour tier and stores of one pixel pair.  plane[c] points at the thread's pixel in the first
+// row of its tile strip, channel c; `row` (a compile-time constant after unrolling) is the
+// pair's first row within the strip and row_bytes the byte pitch of an output row, so every
+// store address is one multiply-add on a per-tile pointer.
 template <typename T, int C, unsigned F>
-__device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F> &col, T (&smp)[2][C], T *row_a,
-                                            unsigned oplane, bool a_ok, bool b_ok)
+__device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F> &col, T (&smp)[2][C],
+                                            T *const (&plane)[C], int row, unsigned row_bytes, bool a_ok, bool b_ok)
 {
-#ifdef TA_COLOUR_PACKED
-    constexpr bool packed_colour = sizeof(T) == 4;
-#else
-    // The colour tier's packed form needs eleven broadcast operand pairs for thirteen packed
-    // instructions; there are no registers to keep those pairs in, and re-creating them costs
-    // more than the packing saves.
+    auto at = [&](int c, int r) {
+        return reinterpret_cast<T *>(reinterpret_cast<char *>(plane[c]) + (size_t)row_bytes * (unsigned)r);
+    };
+    // fp32: packed colour arithmetic (measured 3 % faster than per-pixel scalar code, although
+    // most of its operands are broadcast pairs); fp16 follows the reference's mixed-precision
+    // steps per pixel.
+#ifdef TA_COLOUR_SCALAR
     constexpr bool packed_colour = false;
+#else
+    constexpr bool packed_colour = sizeof(T) == 4;
 #endif
     if constexpr (packed_colour) {
         float2 v2[C];
@@ -194,8 +199,8 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
         col.apply2(k, v2);
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            if (a_ok) Elem<T>::store(row_a + (size_t)c * oplane, v2[c].x);
-            if (b_ok) Elem<T>::store(row_a + (size_t)c * oplane + k.ow, v2[c].y);
+            if (a_ok) Elem<T>::store(at(c, row), v2[c].x);
+            if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
         }
     } else {
 #pragma unroll
@@ -204,7 +209,7 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
             col.apply(k, smp[j], v);
             if (j == 0 ? a_ok : b_ok) {
 #pragma unroll
-                for (int c = 0; c < C; ++c) Elem<T>::store(row_a + (size_t)c * oplane + j * k.ow, v[c]);
+                for (int c = 0; c < C; ++c) Elem<T>::store(at(c, row + j), v[c]);
             }
         }
     }
@@ -244,23 +249,29 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 #endif
         const T *stage = reinterpret_cast<const T *>(smem + s * Smem::stage);
         const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
-        const int n = ti->n, rows = ti->rows, row0 = ti->row0;
+        const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
+        const int4 h1 = *reinterpret_cast<const int4 *>(&ti->row0);    // row0, window, xs0, -
+        const int n = h0.x, rows = h0.w, row0 = h1.x;
         if (n != cur_n) {            // per-image parameters change only every few tiles (warp-uniform branch)
             g = ti->g;
             g2.set(g);
             col = ti->col;
             cur_n = n;
         }
-        const int x = ti->x0 + wx * 32 + lane;
-        const int y_first = ti->y0 + wy * ROWS_PER_WARP;
+        const int x = h0.y + wx * 32 + lane;
+        const int y_first = h0.z + wy * ROWS_PER_WARP;
 
         if (rows == 0) {
             affine_rows_direct<T, C, MODE, F>(k, g, col, n, x, y_first, ROWS_PER_WARP);
         } else if (x < k.ow) {
-            T *out = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
+            T *plane[C];
+            plane[0] = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
+#pragma unroll
+            for (int c = 1; c < C; ++c) plane[c] = plane[c - 1] + oplane;
+            const unsigned row_bytes = (unsigned)k.ow * (unsigned)sizeof(T);
             const float2 xc = bcast(centred(img_x(g, k.ow, x), g.half_w));
-            const bool window = ti->window != 0;
-            const int xs0 = ti->xs0;
+            const bool window = h1.y != 0;
+            const int xs0 = h1.z;
             const uint32_t stage_addr = smem_u32(stage);
             const uint32_t kb = stage_addr - Sampler::ES * (uint32_t)(row0 * kPitch + xs0)
                                 - Sampler::ES * (uint32_t)(kPitch + 1) * (uint32_t)kMagicBits;
@@ -281,7 +292,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 T smp[2][C];
                 if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                 else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                finish_pair<T, C, F>(k, col, smp, out + (size_t)(2 * pr) * k.ow, oplane, a_ok, b_ok);
+                finish_pair<T, C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
             }
         }
         __syncwarp();
@@ -301,11 +312,12 @@ template <typename T, int C, int MODE, unsigned F, bool CHECK>
 __global__ void __launch_bounds__(kAffineThreads, 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
-    extern __shared__ unsigned char smem_dyn[];
+    // Used as declared (no pointer arithmetic through integers), so the compiler keeps every
+    // access in the shared address space.  Tensor copies without swizzle need 16-byte alignment.
+    extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(8) uint64_t full[kStages];
     __shared__ __align__(8) uint64_t empty[kStages];
     __shared__ int abort_flag;
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
