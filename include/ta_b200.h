@@ -196,6 +196,11 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
                                  int32_t oh, int32_t ow, float top, float left, int32_t flip,
                                  const float matrix[6], int32_t tile_x, int32_t tile_y,
                                  int32_t *row0, int32_t *xs, int32_t *xe, int32_t cap);
+/* Which kernel runs calls without a matrix (crop / flip / colour), process-wide: 0 = chosen
+ * by size (default: large fp32 batches go through the staged kernel, everything else through
+ * the crop kernels), 1 = always the crop kernels, 2 = the staged kernel whenever the tensors
+ * allow it.  Both produce identical output; the switch exists so that tests can compare them. */
+int ta_b200_debug_crop_path(int32_t path);
 /* Tile shape of the staged affine kernel: out[0] = width, out[1] = height,
  * out[2] = row capacity, out[3] = row pitch in elements. */
 void ta_b200_debug_tile_shape(int32_t out[4]);

@@ -25,6 +25,7 @@ SYMBOLS = (
     "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
     "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
+    "ta_b200_debug_crop_path",
     "ta_b200_debug_tile_shape",
 )
 
@@ -76,6 +77,8 @@ def load():
     lib.ta_b200_fused_augment_host.restype = C.c_int
     lib.ta_b200_inverse_affine_matrix.argtypes = [C.c_int32] + [C.c_void_p] * 7
     lib.ta_b200_inverse_affine_matrix.restype = C.c_int
+    lib.ta_b200_debug_crop_path.argtypes = [C.c_int32]
+    lib.ta_b200_debug_crop_path.restype = C.c_int
     lib.ta_b200_debug_counters.argtypes = [C.POINTER(C.c_uint64), C.c_int]
     lib.ta_b200_debug_counters.restype = C.c_int
     lib.ta_b200_debug_tile_footprint.argtypes = (
@@ -162,6 +165,11 @@ def inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.Tenso
         check(load().ta_b200_inverse_affine_matrix(n, *[_ptr(t) for t in args], _ptr(out), stream),
               "ta_b200_inverse_affine_matrix")
     return out
+
+
+def crop_path(path: int) -> None:
+    """0: pick the kernel for matrix-free calls by size, 1: crop kernels only, 2: staged kernel (tests)."""
+    check(load().ta_b200_debug_crop_path(int(path)), "ta_b200_debug_crop_path")
 
 
 def debug_counters(reset: bool = False):

@@ -20,7 +20,8 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "lib", "obj")
 LIB = os.path.join(HERE, "lib", "libta_b200.so")
 
-UNITS = ["ta_api.cu"] + [f"ta_inst_{t}_{k}.cu" for t in ("f32", "f16") for k in ("direct", "nearest", "bilinear")]
+UNITS = (["ta_api.cu", "ta_inst_f32_crop_staged.cu"]
+         + [f"ta_inst_{t}_{k}.cu" for t in ("f32", "f16") for k in ("direct", "nearest", "bilinear")])
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -122,16 +122,18 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
     const T *img = (const T *)k.in + (size_t)n * C * k.h * k.w;
     T *out = (T *)k.out + (size_t)n * C * k.oh * k.ow;
     const size_t plane = (size_t)k.h * k.w, oplane = (size_t)k.oh * k.ow;
-    const T fillv = Elem<T>::from_f(k.fill);
-    const float xc = centred(img_x(g, k.ow, x), g.half_w);
+    const T fillv = Elem<T>::from_f(MODE == 0 ? 0.0f : k.fill);
+    const float xi = img_x(g, k.ow, x);
+    const float xc = centred(xi, g.half_w);
     for (int i = 0; i < y_count; ++i) {
         const int y = y_first + i;
         if (y >= k.oh) break;
-        const float yc = centred(img_y(g, y), g.half_h);
-        const float sx = src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
-        const float sy = src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
+        const float yi = img_y(g, y);
+        const float yc = centred(yi, g.half_h);
+        const float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+        const float sy = MODE == 0 ? truncf(yi) : src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
         T s[C];
-        if (MODE == 1) {
+        if (MODE != 2) {
             const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
 #pragma unroll
             for (int c = 0; c < C; ++c) s[c] = tap_global(img + c * plane, k.w, k.h, xn, yn, fillv);

@@ -39,7 +39,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
     int use = 0;
     for (int tile = first; tile < k.num_tiles; tile += step, ++use) {
         if (n != cur_n) {                                   // per-image parameters: reload on change only
-            load_geom(g, k, n, true);
+            load_geom(g, k, n, MODE != 0);
             col.init(k, n);
             cur_n = n;
         }
@@ -50,23 +50,30 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         fp.rows = 0;
         fp.row0 = 0;
         const float m[6] = {g.a, g.b, g.c, g.d, g.e, g.f};
-        if (k.staged_ok) tile_footprint(fp, MODE - 1, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
+        constexpr int FMODE = MODE == 2 ? 1 : 0;            // footprint rule: nearest or bilinear
+        if (k.staged_ok) {
+            if (MODE == 0) tile_footprint_crop(fp, k.oh, k.ow, g.top, g.left, g.flip, tx, ty);
+            else tile_footprint(fp, FMODE, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
+        }
         bool staged = fp.rows > 0, window = false;
         int gxs = 0;
         const int ngroups = (fp.rows + kGroupRows - 1) / kGroupRows;
         if (staged) {
-            window = tile_window(fp, MODE - 1, CH, gxs);
+            window = MODE == 0 ? tile_window_crop(fp, CH, gxs) : tile_window(fp, FMODE, CH, gxs);
             bool inside;
-            if (window) {
+            if (MODE == 0) {
+                staged = window;              // zero outside the image is the crop kernels' rule too
+                inside = true;
+            } else if (window) {
                 int c0, c1;
-                column_range(MODE - 1, fp.xmin, fp.xmax, c0, c1);
+                column_range(FMODE, fp.xmin, fp.xmax, c0, c1);
                 inside = c0 >= 0 && c1 < k.w;
             } else {
                 // lanes 0 .. kNumGroups-1: columns of row group `lane`; the other lanes hold a neutral entry
-                staged = tile_edges(fp, MODE - 1, CH, m);
+                staged = tile_edges(fp, FMODE, CH, m);
                 int xs = 0, xe = CH;
                 const int r_first = lane * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
-                const bool have = staged && lane < ngroups && tile_rows_range(fp, MODE - 1, CH, r_first, r_last, xs, xe);
+                const bool have = staged && lane < ngroups && tile_rows_range(fp, FMODE, CH, r_first, r_last, xs, xe);
                 if (!have) { xs = 0; xe = CH; }
                 gxs = xs;
                 staged = staged && __all_sync(0xffffffffu, xe - xs <= kPitch);
@@ -84,7 +91,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             }
             // fill != 0 cannot rely on the copy's zero fill: stage only tiles that stay inside the image
             inside = inside && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
-            staged = staged && (k.fill == 0.0f || inside);
+            staged = staged && (MODE == 0 || k.fill == 0.0f || inside);
         }
         if (lane == 0) {
             ti->g = g;

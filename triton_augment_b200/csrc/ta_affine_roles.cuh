@@ -76,7 +76,7 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                                                   unsigned long long &n_viol)
     {
         const float2 magic = k2.magic, unmagic = k2.neg_magic;
-        if (MODE == 1) {
+        if (MODE != 2) {
             const float2 tx = pk_add(sx, magic), ty = pk_add(sy, magic);
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -126,7 +126,7 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                                                  int row0, float2 sx, float2 sy, T (&smp)[2][C],
                                                  unsigned long long &n_viol)
     {
-        if (MODE == 1) {
+        if (MODE != 2) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int xn = rint_magic(j ? sx.y : sx.x);
@@ -269,7 +269,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 #pragma unroll
             for (int c = 1; c < C; ++c) plane[c] = plane[c - 1] + oplane;
             const unsigned row_bytes = (unsigned)k.ow * (unsigned)sizeof(T);
-            const float2 xc = bcast(centred(img_x(g, k.ow, x), g.half_w));
+            // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
+            const float2 xc = bcast(MODE == 0 ? truncf(img_x(g, k.ow, x)) : centred(img_x(g, k.ow, x), g.half_w));
             const bool window = h1.y != 0;
             const int xs0 = h1.z;
             const uint32_t stage_addr = smem_u32(stage);
@@ -286,9 +287,15 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred()
                 float2 yc = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
                 yc = pk_add(yc, g2.top);
-                yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
-                const float2 sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                const float2 sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                float2 sx, sy;
+                if (MODE == 0) {
+                    sx = xc;
+                    sy = f2(truncf(yc.x), truncf(yc.y));
+                } else {
+                    yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
+                    sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                    sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                }
                 T smp[2][C];
                 if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                 else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);

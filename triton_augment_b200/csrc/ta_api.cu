@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../../include/ta_b200.h"
@@ -36,9 +37,12 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 4, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit
+constexpr int kNumKinds = 5, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
+// Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
+// 2 = the staged kernel whenever the tensors allow it (ta_b200_debug_crop_path).
+static std::atomic<int> g_crop_path{0};
 
 struct DeviceState {
     std::mutex mu;
@@ -82,7 +86,8 @@ static int current_device(DeviceState **out, int *index)
 static const KernelTable &table_for(int kind, int dtype)
 {
     if (dtype == TA_B200_F32)
-        return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : table_f32_bilinear();
+        return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : kind == 2 ? table_f32_bilinear()
+                                                                                : table_f32_crop_staged();
     return kind == 0 ? table_f16_direct() : kind == 1 ? table_f16_nearest() : table_f16_bilinear();
 }
 
@@ -222,7 +227,20 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     rc = current_device(&s, nullptr);
     if (rc != TA_B200_OK) return rc;
 
-    const int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    KArgs k;
+    fill_kargs(k, p, *s);
+    int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    if (kind == 0 && p->dtype == TA_B200_F32 && k.staged_ok) {
+        // Large fp32 batches run faster through the staged kernel (tensor copies cost no
+        // instructions): measured 264 us instead of 288 us on 64 x 3 x 1280^2 -> 1024^2 with all
+        // colour operations, bit-identical output.  Small or narrow outputs and fp16 do not gain.
+        const int path = g_crop_path.load(std::memory_order_relaxed);
+        const bool large = p->ow >= 160 && (double)p->n * p->c * p->oh * p->ow * 4.0 >= 32.0 * 1024 * 1024;
+        if (path == 2 || (path == 0 && large)) {
+            kind = 3;
+            k.fill = 0.0f;
+        }
+    }
     unsigned f = template_flags(p);
     const KernelTable &tab = table_for(kind, p->dtype);
     unsigned slot = f;
@@ -242,11 +260,9 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     if (vec) ke = p->c == 3 ? &tab.c3_vec[f] : &tab.c1_vec[f];
     if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;
-    rc = prepare_kernel(*s, *ke, vec ? 3 : kind, p->dtype, p->c, slot, &blocks);
+    rc = prepare_kernel(*s, *ke, vec ? 3 : kind == 3 ? 4 : kind, p->dtype, p->c, slot, &blocks);
     if (rc != TA_B200_OK) return rc;
 
-    KArgs k;
-    fill_kargs(k, p, *s);
     long long work;
     if (vec) {
         k.tiles_x = (p->ow + 32 * epv - 1) / (32 * epv);

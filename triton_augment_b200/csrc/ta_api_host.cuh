@@ -236,6 +236,13 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
     return fp.rows;
 }
 
+int ta_b200_debug_crop_path(int32_t path)
+{
+    if (path < 0 || path > 2) return ta::fail(TA_B200_ERR_UNSUPPORTED, "crop path %d", path);
+    ta::g_crop_path.store(path, std::memory_order_relaxed);
+    return TA_B200_OK;
+}
+
 void ta_b200_debug_tile_shape(int32_t out[4])
 {
     out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows; out[3] = ta::kPitch;

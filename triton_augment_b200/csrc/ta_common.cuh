@@ -196,6 +196,9 @@ __device__ __forceinline__ void load_geom(Geom &g, const KArgs &k, int n, bool a
         const float *m = k.matrix + (size_t)n * 6;
         g.a = __ldg(m + 0); g.b = __ldg(m + 1); g.c = __ldg(m + 2);
         g.d = __ldg(m + 3); g.e = __ldg(m + 4); g.f = __ldg(m + 5);
+    } else {
+        g.a = g.e = 1.0f;
+        g.b = g.c = g.d = g.f = 0.0f;
     }
 }
 
@@ -227,7 +230,7 @@ __device__ __forceinline__ float src_coord(float xc, float a, float b_yc, float 
 //   bilinear : x = fma(xc, a, b*yc), y = fma(yc, e, d*xc)                     -> recipe 1, 2
 //              except with (saturation or grayscale) and (brightness or contrast) on,
 //              where x = fma(yc, b, a*xc), y = fma(xc, d, e*yc)               -> recipe 2, 1
-// MODE 1 nearest, 2 bilinear; F the colour flags.
+// MODE 1 nearest, 2 bilinear (0, crop/flip without a matrix, has no coordinate arithmetic); F the colour flags.
 template <int MODE, unsigned F> struct CoordRecipe {
     static constexpr bool swapped = MODE == 2 && (F & (kS | kG)) != 0 && (F & (kB | kC)) != 0;
     static constexpr int x = MODE == 2 ? (swapped ? 2 : 1) : 1;

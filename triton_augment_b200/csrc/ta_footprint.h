@@ -105,6 +105,35 @@ TA_HD bool tile_window(const TileFootprint &t, int mode, int chunk, int &xs)
     return c1 + 1 - xs <= kPitch;
 }
 
+// Crop / flip without a matrix: source pixel = (int)(x_img), (int)(y_img) (truncation, as the
+// crop kernels do), monotone in x and y, so the tile's first and last pixel give the exact
+// range.  Fills xmin / xmax / row0 / rows only; the window always exists (a tile is kTileW wide).
+TA_HD void tile_footprint_crop(TileFootprint &t, int oh, int ow, float top, float left, bool flip, int tile_x, int tile_y)
+{
+    const int x_first = tile_x * kTileW, y_first = tile_y * kTileH;
+    const int x_last = (x_first + kTileW < ow ? x_first + kTileW : ow) - 1;
+    const int y_last = (y_first + kTileH < oh ? y_first + kTileH : oh) - 1;
+    const float xa = (float)(flip ? ow - 1 - x_last : x_first) + left;
+    const float xb = (float)(flip ? ow - 1 - x_first : x_last) + left;
+    const float ya = (float)y_first + top, yb = (float)y_last + top;
+    t.rows = 0;
+    t.row0 = 0;
+    t.xmin = t.xmax = 0.0f;
+    if (!(fabsf(xa) < kCoordLimit && fabsf(xb) < kCoordLimit && fabsf(ya) < kCoordLimit && fabsf(yb) < kCoordLimit)) return;
+    t.xmin = (float)(int)xa;
+    t.xmax = (float)(int)xb;
+    const int r0 = (int)ya, r1 = (int)yb;
+    if (r1 - r0 + 1 > kMaxRows) return;
+    t.row0 = r0;
+    t.rows = r1 - r0 + 1;
+}
+
+TA_HD bool tile_window_crop(const TileFootprint &t, int chunk, int &xs)
+{
+    xs = chunk_floor((int)t.xmin, chunk);
+    return (int)t.xmax + 1 - xs <= kPitch;
+}
+
 // Otherwise rows are fetched in groups with a window each; this prepares the per-edge terms
 // tile_rows_range() needs and checks that no group can be wider than a window.  Inside a slab
 // of height s in source y, eliminating yc gives sx = (a - b d / e) xc + (b / e) sy + const and

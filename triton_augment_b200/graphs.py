@@ -1,0 +1,65 @@
+"""Replay one transform call as a CUDA graph (extra; the reference has no counterpart).
+
+A `TritonFusedAugment.forward` on a device-resident batch is ~19 small launches (one per random
+draw, as in the reference, so that a seed gives the reference's parameters) followed by the
+fused kernel.  For large batches the GPU work hides the launches; once the fused kernel runs
+in a quarter of a millisecond the host cannot issue them fast enough.  `GraphedTransform`
+captures the whole call once and replays it with a single launch.  Every replay draws fresh
+parameters: PyTorch's CUDA generator advances its Philox offset per replay exactly as the
+eager calls would, so graphed and eager runs started from the same seed produce the same
+outputs (tests/test_gpu_api.py checks this).
+
+The price is the usual one of CUDA graphs: input and output live at fixed addresses.
+
+    aug = ta.TritonFusedAugment(...)
+    g = ta.GraphedTransform(aug, batch)      # `batch` is the staging tensor the loader refills
+    for _ in loader_steps:
+        batch.copy_(next_batch, non_blocking=True)   # or fill it in place some other way
+        out = g()                            # same tensor every time; consume before the next call
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+__all__ = ["GraphedTransform"]
+
+
+class GraphedTransform:
+    """``transform(example)`` captured as a CUDA graph.
+
+    ``example`` becomes the static input: later calls either pass nothing (the caller has
+    refilled ``example`` in place), the same tensor, or another tensor of the same shape and
+    dtype, which is copied into it first.  The returned tensor is the graph's static output
+    and is overwritten by the next call.  ``warmup`` eager calls run before the capture (lazy
+    initialisation must not happen inside it); they consume random draws like any other call.
+    """
+
+    def __init__(self, transform, example: torch.Tensor, warmup: int = 3):
+        if not isinstance(example, torch.Tensor) or not example.is_cuda:
+            raise ValueError("GraphedTransform needs a CUDA tensor as the static input")
+        self.transform = transform
+        self.static_input = example
+        device = example.device
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            for _ in range(max(int(warmup), 1)):
+                transform(example)
+        torch.cuda.current_stream(device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.device(device), torch.cuda.graph(self.graph):
+            self.static_output = transform(example)
+
+    def __call__(self, image: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if image is not None and image is not self.static_input:
+            if image.shape != self.static_input.shape or image.dtype != self.static_input.dtype:
+                raise ValueError(f"expected {tuple(self.static_input.shape)} {self.static_input.dtype}, "
+                                 f"got {tuple(image.shape)} {image.dtype}")
+            if not image.is_cuda or image.data_ptr() != self.static_input.data_ptr():
+                self.static_input.copy_(image, non_blocking=True)
+        self.graph.replay()
+        return self.static_output
+
+    forward = __call__
