@@ -38,7 +38,7 @@ constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 constexpr int kPlane = kMaxRows * kPitch;          // elements per channel per stage
 #ifndef TA_PRODUCER_SLEEP_NS
-#define TA_PRODUCER_SLEEP_NS 256
+#define TA_PRODUCER_SLEEP_NS 0
 #endif
 #ifndef TA_CONSUMER_SLEEP_NS
 #define TA_CONSUMER_SLEEP_NS 0
@@ -93,9 +93,10 @@ __device__ __forceinline__ unsigned long long global_ns()
 }
 
 // Wait for a phase of an mbarrier for at most ~2 s, giving up early when another thread
-// of the CTA has already given up.  A failed poll comes back after ~60 cycles and the loop
-// around it costs ~8 instructions, so a warp that polls flat out (a producer waits nearly all
-// the time) takes issue slots from the consumers: SLEEP_NS > 0 sleeps between polls.
+// of the CTA has already given up.  SLEEP_NS > 0 sleeps between polls; measured, it buys
+// nothing (a failed poll already parks the warp for a while) and a producer that sleeps reacts
+// late to a released stage, which costs 5-8 % when the consumers are light, so both roles
+// poll without sleeping.
 template <unsigned SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {

@@ -39,7 +39,7 @@ struct Const2 {
 };
 
 // Two source coordinates at once with the packed fp32 pipe; per lane the operation order of
-// src_coord(): ((fma(xc, a, b*yc) + c) + half) + (-0.5), each step rounded to nearest.
+// src_coord_r(): ((fma + c) + half) + (-0.5), each step rounded to nearest.
 // R picks which product is fused into the addition (see CoordRecipe).
 template <int R>
 __device__ __forceinline__ float2 src_coord2(float2 xc, float2 a, float2 b, float2 yc, float2 c, float2 half,

@@ -137,9 +137,6 @@ __device__ __forceinline__ int floor_magic(float v, float &frac)
     return __float_as_int(t) - kMagicBits;
 }
 
-// (float)i for 0 <= i < 2^23
-__device__ __forceinline__ float float_of_small_uint(int i) { return __fsub_rn(__int_as_float(0x4B000000 | i), 8388608.0f); }
-
 // ----------------------------------------------------------------------------- element access
 template <typename T> struct Elem;
 template <> struct Elem<float> {
@@ -212,17 +209,6 @@ __device__ __forceinline__ float img_y(const Geom &g, int y) { return __fadd_rn(
 // Centred coordinate, geometric_kernel.py:410-411: (v - half) + 0.5.
 __device__ __forceinline__ float centred(float v, float half) { return __fadd_rn(__fsub_rn(v, half), 0.5f); }
 
-// Source coordinate, geometric_kernel.py:414-415, in the operation order and with the one
-// contraction the reference's GPU build performs: ((fma(xc, a, b*yc) + c) + half) + (-0.5).
-// Every step is an explicitly rounded intrinsic so the compiler cannot re-associate or fuse.
-__device__ __forceinline__ float src_coord(float xc, float a, float b_yc, float c, float half)
-{
-    float u = __fmaf_rn(xc, a, b_yc);
-    u = __fadd_rn(u, c);
-    u = __fadd_rn(half, u);
-    return __fadd_rn(u, -0.5f);
-}
-
 // Which of the two products of a*xc + b*yc the reference's GPU build fuses into the addition
 // is a choice its compiler makes per compiled variant (every flag combination is a separate
 // LLVM module).  Measured on a B200 with Triton 3.6 against all 32 colour-flag combinations:
@@ -237,6 +223,9 @@ template <int MODE, unsigned F> struct CoordRecipe {
     static constexpr int y = MODE == 2 ? (swapped ? 1 : 2) : 1;
 };
 
+// Source coordinate, geometric_kernel.py:414-415, in the reference's operation order:
+// ((fma + c) + half) + (-0.5).  Every step is an explicitly rounded intrinsic so the compiler
+// cannot re-associate or fuse; R picks the contraction (see CoordRecipe).
 template <int R> __device__ __forceinline__ float src_coord_r(float xc, float yc, float a, float b, float c, float half)
 {
     float u = R == 1 ? __fmaf_rn(xc, a, __fmul_rn(b, yc)) : __fmaf_rn(yc, b, __fmul_rn(a, xc));

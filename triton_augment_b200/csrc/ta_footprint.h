@@ -153,18 +153,11 @@ TA_HD bool tile_edges(TileFootprint &t, int mode, int chunk, const float *m)
     return span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)kPitch;
 }
 
-// Columns [xs, xe) of source row row0 + r that the tile reads, rounded outward to
-// whole chunks.  xs is a multiple of `chunk` (floor division, so also for negative
-// columns).  Returns false (and xe == xs == 0) for a row no pixel reads.
-TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_first, int r_last, int &xs, int &xe);
-
-TA_HD bool tile_row_range(const TileFootprint &t, int mode, int chunk, int r, int &xs, int &xe)
-{
-    return tile_rows_range(t, mode, chunk, r, r, xs, xe);
-}
-
-// Same for the union of rows row0 + r_first .. row0 + r_last: the pixels that read any of
-// them lie in one (thicker) slab, so it is the same clip.
+// Columns [xs, xe) of source rows row0 + r_first .. row0 + r_last that the tile reads, rounded
+// outward to whole chunks: the pixels that read any of these rows lie in one slab of the
+// parallelogram, which is clipped against its edges.  xs is a multiple of `chunk` (floor
+// division, so also for negative columns).  Returns false (and xe == xs == 0) when no pixel
+// reads the rows.  Needs tile_edges() first.
 TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_first, int r_last, int &xs, int &xe)
 {
     const float ya = (float)(t.row0 + r_first) - (mode == 0 ? 0.5f : 1.0f) - kEps;
