@@ -191,14 +191,46 @@ def kernel_only(aug, img, steps, warmup, barrier):
     from triton_augment_b200 import _lib, functional as F
     from triton_augment_b200.transforms import _Layout
     dev = img.device
+    n, _, src_h, src_w = img.shape
+    crop = aug.crop_height
     lay = _Layout(img, False, True)
     angle, translate, scale, shear, top, left, flip, b, c, s, g = aug._spread_all(
-        lay, aug._get_params(lay.count, dev, (SRC, SRC)))
-    matrix = F._prepare_affine_matrix_only(N_IMG, dev, SRC, SRC, angle, translate, scale, shear, None).contiguous()
-    out = torch.empty(N_IMG, 3, CROP, CROP, device=dev)
-    p = _lib.make_params(img, out, top, left, flip, matrix, 0.0, F._is_bilinear(aug.interpolation), 31, b, c, s, g,
+        lay, aug._get_params(lay.count, dev, (src_h, src_w)))
+    matrix = None
+    if aug.has_affine:
+        matrix = F._prepare_affine_matrix_only(n, dev, src_h, src_w, angle, translate, scale, shear, None).contiguous()
+    out = torch.empty(n, 3, crop, crop, device=dev, dtype=img.dtype)
+    p = _lib.make_params(img, out, top, left, flip, matrix, 0.0, aug.has_affine and F._is_bilinear(aug.interpolation), 31,
+                         b.to(img.dtype), c.to(img.dtype), s.to(img.dtype), g,
                          F._rounded_triple(MEAN, img.dtype), F._rounded_triple(STD, img.dtype))
     return timed(lambda: _lib.launch_fused(p, dev), steps, warmup, barrier)
+
+
+# Other configurations of the reference's benchmark list, for profiler captures (--profile-config):
+# images, source size, crop, dtype, affine
+PROFILE_CONFIGS = {
+    "c3": (N_IMG, SRC, CROP, torch.float32, True),
+    "c4": (512, 512, 448, torch.float16, True),          # fp16 affine + crop 448 + flip + colour + normalize
+    "c5b": (4096, 224, 112, torch.float32, False),       # crop 112 + flip + colour + normalize, image batch
+}
+
+
+def profile_case(config, images, interp):
+    """For profilers: the configuration's tensors for `images` images, three launches of the fused
+    kernel through the C ABI, nothing else.  Prints no benchmark line."""
+    import triton_augment_b200 as ta
+    n, src, crop, dtype, affine = PROFILE_CONFIGS[config]
+    n = images or n
+    torch.cuda.set_device(0)
+    torch.manual_seed(1234)
+    img = torch.rand(n, 3, src, src, device="cuda:0").to(dtype)
+    kw = dict(degrees=15, translate=(0.1, 0.1), scale=(0.9, 1.1), shear=5, interpolation=interp) if affine else {}
+    aug = ta.TritonFusedAugment(crop_size=crop, horizontal_flip_p=0.5, brightness=0.2, contrast=0.2, saturation=0.2,
+                                grayscale_p=0.1, mean=MEAN, std=STD, **kw)
+    ms = kernel_only(aug, img, 2, 1, None)
+    gbs = 2 * n * 3 * crop * crop * img.element_size() / (ms * 1e-3) / 1e9
+    print(f"profile case {config}: {n} images, {interp if affine else 'no affine'}, {ms:.4f} ms per launch, "
+          f"{gbs:.0f} GB/s algorithmic")
 
 
 def main():
@@ -208,8 +240,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--interp", default="bilinear", choices=["bilinear", "nearest"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--profile-case", type=int, default=0, metavar="IMAGES",
-                    help="only launch the fused kernel 3 times on IMAGES images (for ncu)")
+    ap.add_argument("--profile-case", type=int, default=None, metavar="IMAGES",
+                    help="only launch the fused kernel 3 times on IMAGES images (0 = the configuration's own batch); for ncu")
+    ap.add_argument("--profile-config", default="c3", choices=sorted(PROFILE_CONFIGS),
+                    help="which configuration --profile-case builds")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -218,16 +252,8 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
-    if args.profile_case:
-        # For profilers: the workload's tensors for a few images, three launches of the fused
-        # kernel through the C ABI, nothing else.  Prints no benchmark line.
-        global N_IMG
-        N_IMG = args.profile_case
-        torch.cuda.set_device(0)
-        torch.manual_seed(1234)
-        img = torch.rand(N_IMG, 3, SRC, SRC, device="cuda:0")
-        ms = kernel_only(make_transform(args.interp), img, 2, 1, None)
-        print(f"profile case: {N_IMG} images, {args.interp}, {ms:.4f} ms per launch")
+    if args.profile_case is not None:
+        profile_case(args.profile_config, args.profile_case, args.interp)
         return
 
     import torch.distributed as dist
