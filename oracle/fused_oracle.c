@@ -22,7 +22,8 @@
  *   fma_coords = 0  a*xc + b*yc is two roundings (what the numpy-backed Triton
  *                   interpreter computes);
  *   fma_coords = 1  fma(xc, a, b*yc), the contraction Triton's GPU compiler
- *                   emits for triton_augment/kernels/geometric_kernel.py:414-415.
+ *                   emits for triton_augment/kernels/geometric_kernel.py:414-415
+ *                   (bit fields select other contractions per axis, see map_coords).
  * Compile with -ffp-contract=off so that nothing else is contracted.
  */
 #include <math.h>
@@ -95,8 +96,17 @@ static inline void map_coords(const ta_oracle_params *p, int n, int xo, int yo, 
     float xc = (x_img - half_w) + 0.5f;                              /* :410 */
     float yc = (y_img - half_h) + 0.5f;                              /* :411 */
     /* a*xc + b*yc (:414-415): which product, if any, the compiler fused into the addition.
-     * Bits 0-1 choose for x, bits 2-3 for y: 0 none, 1 fma(xc, a, b*yc), 2 fma(yc, b, a*xc). */
-    const int rx = p->fma_coords & 3, ry = (p->fma_coords >> 2) & 3;
+     * Bits 0-1 choose for x, bits 2-3 for y: 0 none, 1 fma(xc, a, b*yc), 2 fma(yc, b, a*xc).
+     * Bits 4-5 = k: the reference's kernel handles 1024 consecutive output pixels per program
+     * with 128 threads, so a thread's j-th pixel is 128 j further on; when its stores are not
+     * vectorised the compiler contracts the x expression of a thread's last k pixels the
+     * other way (recipe 1).  Those are the pixels whose linear index has bits 7-9 >= 8 - k. */
+    int rx = p->fma_coords & 3;
+    const int ry = (p->fma_coords >> 2) & 3, late = (p->fma_coords >> 4) & 3;
+    if (late) {
+        const uint32_t lin = (uint32_t)n * (uint32_t)(p->oh * p->ow) + (uint32_t)(yo * p->ow + xo);
+        if ((int)((lin >> 7) & 7u) >= 8 - late) rx = 1;
+    }
     float ux = rx == 1 ? fmaf(xc, m[0], m[1] * yc) : rx == 2 ? fmaf(yc, m[1], m[0] * xc) : m[0] * xc + m[1] * yc;
     float uy = ry == 1 ? fmaf(xc, m[3], m[4] * yc) : ry == 2 ? fmaf(yc, m[4], m[3] * xc) : m[3] * xc + m[4] * yc;
     ux = ux + m[2];

@@ -75,36 +75,54 @@ def coord_recipe(fma_coords) -> int:
     """How ``a*xc + b*yc`` of the coordinate map is contracted, per axis.
 
     ``False`` / ``0``: not at all (the CPU interpreter).  ``True``: ``fma(xc, a, b*yc)`` for both
-    axes, what the reference's GPU build does in its nearest-sampling kernels.  ``"nearest"`` /
-    ``"bilinear"``: the recipe measured for that variant of the reference's GPU kernel (see
-    tests/golden/make_gpu_golden.py).  ``(rx, ry)``: explicit, 0 none / 1 ``fma(xc,a,b*yc)`` /
-    2 ``fma(yc,b,a*xc)``.
+    axes, what the reference's GPU build does in its nearest-sampling kernels.
+    ``(rx, ry)`` or ``(rx, ry, k)``: explicit, 0 none / 1 ``fma(xc,a,b*yc)`` / 2 ``fma(yc,b,a*xc)``;
+    ``k``: the last k of a reference thread's 8 pixels use recipe 1 for x (see gpu_recipe).
     """
     if isinstance(fma_coords, str):
-        raise ValueError("resolve 'gpu' with gpu_recipe(interpolation, flags) first")
+        raise ValueError("resolve 'gpu' with gpu_recipe(...) first")
     if isinstance(fma_coords, (tuple, list)):
-        return int(fma_coords[0]) | (int(fma_coords[1]) << 2)
+        k = int(fma_coords[2]) if len(fma_coords) > 2 else 0
+        return int(fma_coords[0]) | (int(fma_coords[1]) << 2) | (k << 4)
     if isinstance(fma_coords, (bool, np.bool_)):
         return 5 if fma_coords else 0
     return int(fma_coords)
 
 
-def gpu_recipe(interpolation, flags) -> tuple:
+# gpu_recipe(): k per colour-flag combination (bit 0 brightness, 1 contrast, 2 saturation,
+# 3 grayscale, 4 normalize) of the variants whose x and y recipes are swapped.
+_LATE_X = {5: 1, 6: 1, 7: 3, 9: 2, 10: 1, 11: 3, 13: 2, 14: 2, 15: 3,
+           21: 1, 22: 2, 23: 3, 25: 2, 26: 1, 27: 3, 29: 2, 30: 2, 31: 3}
+
+
+def gpu_recipe(interpolation, flags, normalize=False, out_size=None, dtype=np.float32) -> tuple:
     """Contraction the reference's kernel shows when Triton 3.6 compiles it for sm_100.
 
     Measured on a B200 by comparing the reference's output with every recipe, for all 32
-    combinations of the colour flags, fp32, sizes divisible by 16 (the sweep is described in
+    combinations of the colour flags in fp32 (the sweep is described in
     tests/golden/make_gpu_golden.py):
       * nearest sampling: x and y are fma(xc, a, b*yc) in every variant;
       * bilinear sampling: x = fma(xc, a, b*yc), y = fma(yc, e, d*xc), except in the variants
         that take the RGB-triplet path (saturation or grayscale on) AND have brightness or
-        contrast on, where it is the other way round: x = fma(yc, b, a*xc), y = fma(xc, d, e*yc).
+        contrast on, where it is the other way round: x = fma(yc, b, a*xc), y = fma(xc, d, e*yc);
+      * in those swapped variants, when neither output dimension is divisible by 16 (Triton
+        then specialises the kernel without vectorised stores and a thread's 8 pixels lie 128
+        apart), the last k of a thread's 8 pixels use fma(xc, a, b*yc) for x after all; k is
+        1, 2 or 3 depending on the flag combination (``_LATE_X``).  ``out_size`` = (oh, ow)
+        enables this rule; it is known for fp32 only.
     Each compiled variant is a different LLVM module, hence the different choices.
     """
     if str(interpolation).lower() != "bilinear":
         return (1, 1)
     spatial = flags["saturation"] or flags["grayscale"]
-    return (2, 1) if spatial and (flags["brightness"] or flags["contrast"]) else (1, 2)
+    if not (spatial and (flags["brightness"] or flags["contrast"])):
+        return (1, 2)
+    k = 0
+    if out_size is not None and np.dtype(dtype) == np.float32 and out_size[0] % 16 and out_size[1] % 16:
+        bits = (int(bool(flags["brightness"])) | int(bool(flags["contrast"])) << 1 | int(bool(flags["saturation"])) << 2
+                | int(bool(flags["grayscale"])) << 3 | int(bool(normalize)) << 4)
+        k = _LATE_X[bits]
+    return (2, 1, k)
 
 
 def _vec(x, n, dtype):
@@ -165,7 +183,7 @@ def _prepare(image, top, left, height, width, flip, matrix, interpolation, fill,
     p.brightness, p.contrast, p.saturation = _ptr(keep["b"]), _ptr(keep["c"]), _ptr(keep["s"])
     p.gray, p.mean, p.std = _ptr(keep["g"]), _ptr(keep["mean"]), _ptr(keep["std"])
     if isinstance(fma_coords, str) and fma_coords == "gpu":
-        fma_coords = gpu_recipe(interpolation, flags)
+        fma_coords = gpu_recipe(interpolation, flags, apply_norm, (height, width), dt)
     p.fma_coords = coord_recipe(fma_coords)
     p.contrast_mode = int(contrast_mode)
     p.gray_mean = _ptr(keep["gm"])

@@ -64,14 +64,19 @@ def test_nearest_geometry_hash(vectors):
 
 @pytest.mark.parametrize("interp", ["nearest", "bilinear"])
 def test_full_pipeline_against_reference_output(vectors, interp):
+    """All colour operations on; for the case whose output dimensions are not divisible by 16
+    (the reference then mixes two coordinate contractions inside one launch) also three other
+    flag combinations."""
     import triton_augment_b200 as ta
-    stride = int(vectors["stride"])
     for name in vectors["names"]:
         name = str(name)
         G, (n, h, w, oh, ow), p, dtype = _inputs(vectors, name)
-        got = G.run(ta.functional, G.procedural_image(n, 3, h, w, dtype), p, oh, ow, interp, colour=True)
-        sub = got[:, :, ::stride, ::stride].cpu().numpy().astype(np.float32)
-        want = vectors[f"{name}|{interp}_sub"].astype(np.float32)
-        tol = 1e-2 if dtype == torch.float16 else 1e-5
-        err = float(np.abs(sub - want).max())
-        assert err <= tol, (name, interp, err)
+        stride = int(vectors[f"{name}|stride"])
+        img = G.procedural_image(n, 3, h, w, dtype)
+        for bits in (31,) + (G.EXTRA_FLAGS.get(name, ()) if interp == "bilinear" else ()):
+            got = G.run(ta.functional, img, p, oh, ow, interp, colour=True, bits=bits)
+            sub = got[:, :, ::stride, ::stride].cpu().numpy().astype(np.float32)
+            want = vectors[f"{name}|{interp}_sub" + ("" if bits == 31 else f"_flags{bits}")].astype(np.float32)
+            tol = 1e-2 if dtype == torch.float16 else 1e-5
+            err = float(np.abs(sub - want).max())
+            assert err <= tol, (name, interp, bits, err)

@@ -115,7 +115,7 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
 }
 
 // Gather rows [y_first, y_first + y_count) of one tile column from global memory (no staging).
-template <typename T, int C, int MODE, unsigned F>
+template <typename T, int C, int MODE, unsigned F, bool MIX>
 __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g, const Colour<T, C, F> &col,
                                                    int n, int x, int y_first, int y_count)
 {
@@ -131,7 +131,11 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
         if (y >= k.oh) break;
         const float yi = img_y(g, y);
         const float yc = centred(yi, g.half_h);
-        const float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+        float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+        if constexpr (MIX) {
+            if (late_x(k, (uint32_t)n * (uint32_t)oplane + (uint32_t)(y * k.ow + x)))
+                sx = src_coord_r<1>(xc, yc, g.a, g.b, g.c, g.half_w);
+        }
         const float sy = MODE == 0 ? truncf(yi) : src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
         T s[C];
         if (MODE != 2) {

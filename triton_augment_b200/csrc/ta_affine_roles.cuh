@@ -215,7 +215,7 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
     }
 }
 
-template <typename T, int C, int MODE, unsigned F, bool CHECK>
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
                                                 volatile int *abort_flag)
 {
@@ -262,7 +262,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         const int y_first = h0.z + wy * ROWS_PER_WARP;
 
         if (rows == 0) {
-            affine_rows_direct<T, C, MODE, F>(k, g, col, n, x, y_first, ROWS_PER_WARP);
+            affine_rows_direct<T, C, MODE, F, MIX>(k, g, col, n, x, y_first, ROWS_PER_WARP);
         } else if (x < k.ow) {
             T *plane[C];
             plane[0] = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
@@ -295,6 +295,12 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                     yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
                     sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
                     sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                    if constexpr (MIX) {                  // see late_x()
+                        const float2 alt = src_coord2<1>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                        const uint32_t base = (uint32_t)n * oplane + (uint32_t)x;
+                        if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
+                        if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
+                    }
                 }
                 T smp[2][C];
                 if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
@@ -315,7 +321,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 }
 
 // ----------------------------------------------------------------------------- kernel
-template <typename T, int C, int MODE, unsigned F, bool CHECK>
+// MIX: the variant of a swapped bilinear kernel (CoordRecipe) that applies late_x() per pixel.
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false>
 __global__ void __launch_bounds__(kAffineThreads, 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
@@ -339,7 +346,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     if ((threadIdx.x >> 5) >= kConsumerWarps)
         affine_producer<T, C, MODE, F>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
     else
-        affine_consumer<T, C, MODE, F, CHECK>(k, smem, full, empty, &abort_flag);
+        affine_consumer<T, C, MODE, F, CHECK, MIX>(k, smem, full, empty, &abort_flag);
 
     // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
     // memory: give each stage one more bounded chance to settle before the memory is released.

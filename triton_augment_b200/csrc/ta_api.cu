@@ -37,7 +37,7 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 5, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged
+constexpr int kNumKinds = 6, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
@@ -87,7 +87,7 @@ static const KernelTable &table_for(int kind, int dtype)
 {
     if (dtype == TA_B200_F32)
         return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : kind == 2 ? table_f32_bilinear()
-                                                                                : table_f32_crop_staged();
+               : kind == 3 ? table_f32_crop_staged() : table_f32_bilinear_mix();
     return kind == 0 ? table_f16_direct() : kind == 1 ? table_f16_nearest() : table_f16_bilinear();
 }
 
@@ -166,6 +166,14 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
         k.inv_std[i] = 1.0f / k.stdv[i];
         k.nbias[i] = -k.mean[i] * k.inv_std[i];
     }
+    // How many of a reference thread's 8 pixels get the other x contraction, per colour-flag
+    // combination (late_x() in ta_common.cuh; measured against the reference's kernels on a
+    // B200, fp32, bilinear, neither output dimension divisible by 16; 0 elsewhere).
+    static const unsigned char late_count[32] = {0, 0, 0, 0, 0, 1, 1, 3, 0, 2, 1, 3, 0, 2, 2, 3,
+                                                 0, 0, 0, 0, 0, 1, 2, 3, 0, 2, 1, 3, 0, 2, 2, 3};
+    k.late_x_slot = 8;
+    if (p->matrix && p->interp == TA_B200_BILINEAR && p->dtype == TA_B200_F32 && p->oh % 16 != 0 && p->ow % 16 != 0)
+        k.late_x_slot = 8 - late_count[p->apply & 31u];
     const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
     k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
                   ((size_t)p->h * p->w * es) % 16 == 0 &&
@@ -242,6 +250,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         }
     }
     unsigned f = template_flags(p);
+    if (kind == 2 && k.late_x_slot < 8 && !checked) kind = 4;     // only swapped fp32 variants get here (fill_kargs)
     const KernelTable &tab = table_for(kind, p->dtype);
     unsigned slot = f;
     const KernelEntry *ke;
@@ -260,7 +269,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     if (vec) ke = p->c == 3 ? &tab.c3_vec[f] : &tab.c1_vec[f];
     if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;
-    rc = prepare_kernel(*s, *ke, vec ? 3 : kind == 3 ? 4 : kind, p->dtype, p->c, slot, &blocks);
+    rc = prepare_kernel(*s, *ke, vec ? 3 : kind == 3 ? 4 : kind == 4 ? 5 : kind, p->dtype, p->c, slot, &blocks);
     if (rc != TA_B200_OK) return rc;
 
     long long work;

@@ -34,6 +34,7 @@ struct KArgs {
     int n, h, w, oh, ow;
     int tiles_x, tiles_y, num_tiles;
     int staged_ok;                     // source rows can be bulk-copied (16-byte aligned pitch and base)
+    int late_x_slot;                   // see late_x(): 8 = never
     float fill;
     float mean[3], stdv[3];            // image-dtype-rounded values
     float inv_std[3], nbias[3];        // 1/std and -mean/std (fp32 path)
@@ -226,6 +227,14 @@ template <int MODE, unsigned F> struct CoordRecipe {
 // Source coordinate, geometric_kernel.py:414-415, in the reference's operation order:
 // ((fma + c) + half) + (-0.5).  Every step is an explicitly rounded intrinsic so the compiler
 // cannot re-associate or fuse; R picks the contraction (see CoordRecipe).
+// In the swapped bilinear variants the reference's GPU build contracts x the other way
+// (recipe 1) for some pixels when its stores are not vectorised, i.e. when neither output
+// dimension is divisible by 16: it handles 1024 consecutive output pixels per program with 128
+// threads, a thread's j-th pixel lies 128 j further on, and the last 1-3 of a thread's 8 pixels
+// are the ones compiled differently.  `lin` is the pixel's index in the [N, oh, ow] output
+// (its low 10 bits are enough); the host sets late_x_slot = 8 - (that count), or 8 for never.
+__device__ __forceinline__ bool late_x(const KArgs &k, uint32_t lin) { return (int)((lin >> 7) & 7u) >= k.late_x_slot; }
+
 template <int R> __device__ __forceinline__ float src_coord_r(float xc, float yc, float a, float b, float c, float half)
 {
     float u = R == 1 ? __fmaf_rn(xc, a, __fmul_rn(b, yc)) : __fmaf_rn(yc, b, __fmul_rn(a, xc));

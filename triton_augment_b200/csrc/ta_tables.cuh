@@ -36,13 +36,19 @@ constexpr bool flags_valid(int channels, unsigned f)
     return true;
 }
 
-// KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear, 3 crop/flip through the staged kernel
+// KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear, 3 crop/flip through the staged kernel,
+// 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only)
 template <typename T, int C, int KIND, unsigned F, bool CHECK = false> KernelEntry kernel_entry()
 {
     if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
     else if constexpr (KIND == 0) return KernelEntry{(const void *)&direct_kernel<T, C, F>, 0, kThreads};
-    else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK>,
-                            AffineSmem<T, C, F>::total, kAffineThreads};
+    else if constexpr (KIND == 4) {
+        if constexpr (CoordRecipe<2, F>::swapped && !CHECK)
+            return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true>, AffineSmem<T, C, F>::total,
+                               kAffineThreads};
+        else return KernelEntry{nullptr, 0, 0};
+    } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK>,
+                              AffineSmem<T, C, F>::total, kAffineThreads};
 }
 
 template <typename T, int C, unsigned F> KernelEntry vec_entry()
@@ -79,6 +85,7 @@ template <typename T, int KIND> const KernelTable &make_table()
 // Defined one per translation unit (ta_inst_*.cu).
 const KernelTable &table_f32_direct();
 const KernelTable &table_f32_crop_staged();
+const KernelTable &table_f32_bilinear_mix();
 const KernelTable &table_f32_nearest();
 const KernelTable &table_f32_bilinear();
 const KernelTable &table_f16_direct();
