@@ -203,6 +203,7 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
             if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
         }
     } else {
+#if defined(TA_HALF_COLOUR_SCALAR) || defined(TA_COLOUR_SCALAR)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             float v[C];
@@ -212,6 +213,15 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
                 for (int c = 0; c < C; ++c) Elem<T>::store(at(c, row + j), v[c]);
             }
         }
+#else
+        float2 v2[C];
+        col.apply2(k, smp[0], smp[1], v2);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            if (a_ok) Elem<T>::store(at(c, row), v2[c].x);
+            if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
+        }
+#endif
     }
 }
 

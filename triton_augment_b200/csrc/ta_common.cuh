@@ -444,6 +444,90 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
             for (int i = 0; i < C; ++i) v[i] = __half2float(hv[i]);
         }
     }
+    // Two pixels at once: a[] and b[] are the texels of the pair, v[i] = (result for a, result
+    // for b).  Per pixel the same operations in the same precision as apply(): half2 arithmetic
+    // where apply() uses half, packed or saturating fp32 where it uses fp32.
+    static __device__ __forceinline__ __half2 gray_h2(__half2 r, __half2 g, __half2 b)
+    {
+        return __hadd2(__hadd2(__hmul2(__float2half2_rn(0.2989f), r), __hmul2(__float2half2_rn(0.587f), g)),
+                       __hmul2(__float2half2_rn(0.114f), b));
+    }
+    static __device__ __forceinline__ float2 sat2(float2 x) { return make_float2(__saturatef(x.x), __saturatef(x.y)); }
+    static __device__ __forceinline__ float2 gray_f2(const float2 (&v)[C])
+    {
+        float2 g = pk_mul(make_float2(0.2989f, 0.2989f), v[0]);
+        g = pk_fma(make_float2(0.587f, 0.587f), v[C > 1 ? 1 : 0], g);
+        return pk_fma(make_float2(0.114f, 0.114f), v[C - 1], g);
+    }
+    __device__ __forceinline__ void apply2(const KArgs &k, const __half (&a)[C], const __half (&b)[C], float2 (&v)[C]) const
+    {
+        __half2 hv[C];
+#pragma unroll
+        for (int i = 0; i < C; ++i) hv[i] = __halves2half2(a[i], b[i]);
+        constexpr bool wide_after_b = (F & kB) != 0;
+        constexpr bool wide_after_c = wide_after_b || (F & kC) != 0;
+        constexpr bool wide_after_s = wide_after_c || (C == 3 && (F & kS) != 0);
+        if (F & kB) {
+            const __half2 bh2 = __half2half2(bh);
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = sat2(__half22float2(__hmul2(hv[i], bh2)));
+        }
+        if (F & kC) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                if (wide_after_b) {
+                    if (F & kMean) {
+                        v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, cf, gmt)), __saturatef(__fmaf_rn(v[i].y, cf, gmt)));
+                    } else {
+                        const float2 d = pk_add(v[i], make_float2(-0.5f, -0.5f));
+                        v[i] = make_float2(__saturatef(__fmaf_rn(d.x, cf, 0.5f)), __saturatef(__fmaf_rn(d.y, cf, 0.5f)));
+                    }
+                } else if (F & kMean) {
+                    v[i] = sat2(__half22float2(__hadd2(__hmul2(hv[i], __half2half2(ch)), __half2half2(gmth))));
+                } else {
+                    const __half2 hh = __float2half2_rn(0.5f);
+                    v[i] = sat2(__half22float2(__hadd2(__hmul2(__hsub2(hv[i], hh), __half2half2(ch)), hh)));
+                }
+            }
+        }
+        if (C == 3 && (F & kS)) {
+            if (wide_after_c) {
+                const float2 gg = pk_mul(gray_f2(v), make_float2(oms, oms));
+#pragma unroll
+                for (int i = 0; i < C; ++i)
+                    v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, sf, gg.x)), __saturatef(__fmaf_rn(v[i].y, sf, gg.y)));
+            } else {
+                const __half2 gg = __hmul2(gray_h2(hv[0], hv[C > 1 ? 1 : 0], hv[C - 1]), __half2half2(omsh));
+#pragma unroll
+                for (int i = 0; i < C; ++i) v[i] = sat2(__half22float2(__hadd2(__hmul2(hv[i], __half2half2(sh)), gg)));
+            }
+        }
+        if (C == 3 && (F & kG)) {
+            if (gray) {
+                if (wide_after_s) {
+                    const float2 g = gray_f2(v);
+#pragma unroll
+                    for (int i = 0; i < C; ++i) v[i] = g;
+                } else {
+                    const __half2 g = gray_h2(hv[0], hv[C > 1 ? 1 : 0], hv[C - 1]);
+#pragma unroll
+                    for (int i = 0; i < C; ++i) hv[i] = g;
+                }
+            }
+        }
+        if (F & kN) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                if (wide_after_s)
+                    v[i] = pk_mul(pk_add(v[i], make_float2(-k.mean[i], -k.mean[i])), make_float2(k.inv_std[i], k.inv_std[i]));
+                else
+                    v[i] = __half22float2(__h2div(__hsub2(hv[i], __float2half2_rn(k.mean[i])), __float2half2_rn(k.stdv[i])));
+            }
+        } else if (!wide_after_s) {
+#pragma unroll
+            for (int i = 0; i < C; ++i) v[i] = __half22float2(hv[i]);
+        }
+    }
 };
 
 // ----------------------------------------------------------------------------- global-memory taps

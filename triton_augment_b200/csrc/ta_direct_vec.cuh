@@ -149,20 +149,19 @@ __global__ void __launch_bounds__(kThreads, VecTraits<T>::blocks) direct_vec_ker
                             res[c][e + 1] = __float_as_uint(v2[c].y);
                         }
                     }
-                } else
+                } else {
+                    // fp16: element pairs through the packed colour tier, results packed as half2 words
 #pragma unroll
-                for (int e = 0; e < EPV; ++e) {
-                    T s[C];
-                    float v[C];
+                    for (int e = 0; e < EPV; e += 2) {
+                        T sa[C], sb[C];
+                        float2 v2[C];
 #pragma unroll
-                    for (int c = 0; c < C; ++c) s[c] = elem_of<T>(o[c], e);
-                    col.apply(k, s, v);
+                        for (int c = 0; c < C; ++c) { sa[c] = elem_of<T>(o[c], e); sb[c] = elem_of<T>(o[c], e + 1); }
+                        col.apply2(k, sa, sb, v2);
 #pragma unroll
-                    for (int c = 0; c < C; ++c) {
-                        if (ES == 4) res[c][e] = __float_as_uint(v[c]);
-                        else {
-                            const uint32_t hbits = __half_as_ushort(__float2half_rn(v[c]));
-                            if (e & 1) res[c][e >> 1] |= hbits << 16; else res[c][e >> 1] = hbits;
+                        for (int c = 0; c < C; ++c) {
+                            const __half2 h = __floats2half2_rn(v2[c].x, v2[c].y);
+                            res[c][e >> 1] = *reinterpret_cast<const uint32_t *>(&h);
                         }
                     }
                 }
