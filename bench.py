@@ -209,6 +209,8 @@ def kernel_only(aug, img, steps, warmup, barrier):
 # Other configurations of the reference's benchmark list, for profiler captures (--profile-config):
 # images, source size, crop, dtype, affine
 PROFILE_CONFIGS = {
+    "c1": (32, 224, 224, torch.float32, False),          # colour + grayscale + normalize only
+    "c2": (256, 224, 112, torch.float32, False),         # crop 112 + flip + colour + normalize
     "c3": (N_IMG, SRC, CROP, torch.float32, True),
     "c4": (512, 512, 448, torch.float16, True),          # fp16 affine + crop 448 + flip + colour + normalize
     "c5b": (4096, 224, 112, torch.float32, False),       # crop 112 + flip + colour + normalize, image batch

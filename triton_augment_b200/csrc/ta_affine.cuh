@@ -37,15 +37,6 @@ constexpr int kConsumerWarps = 16;
 constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 constexpr int kPlane = kMaxRows * kPitch;          // elements per channel per stage
-#ifndef TA_PRODUCER_SLEEP_NS
-#define TA_PRODUCER_SLEEP_NS 0
-#endif
-#ifndef TA_CONSUMER_SLEEP_NS
-#define TA_CONSUMER_SLEEP_NS 0
-#endif
-constexpr unsigned kProducerSleepNs = TA_PRODUCER_SLEEP_NS;   // between polls of a stage's "empty" barrier
-constexpr unsigned kConsumerSleepNs = TA_CONSUMER_SLEEP_NS;   // between polls of a stage's "full" barrier
-
 constexpr int kNumGroups = kMaxRows / kGroupRows;
 constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
 
@@ -93,17 +84,14 @@ __device__ __forceinline__ unsigned long long global_ns()
 }
 
 // Wait for a phase of an mbarrier for at most ~2 s, giving up early when another thread
-// of the CTA has already given up.  SLEEP_NS > 0 sleeps between polls; measured, it buys
-// nothing (a failed poll already parks the warp for a while) and a producer that sleeps reacts
-// late to a released stage, which costs 5-8 % when the consumers are light, so both roles
-// poll without sleeping.
-template <unsigned SLEEP_NS>
+// of the CTA has already given up.  No sleep between polls: a failed poll already parks the
+// warp for a while (sleeping 256 ns on top of it changed nothing for heavy consumers and cost
+// 5-8 % with light ones, because the producer then reacts late to a released stage).
 __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (int i = 0; i < (1 << 24); ++i) {
-        if (SLEEP_NS) __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (*abort_flag) return false;

@@ -21,10 +21,6 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
     const int tiles_per_img = k.tiles_x * k.tiles_y;
     T *stage = reinterpret_cast<T *>(smem + p * Smem::stage);
     unsigned long long n_staged = 0, n_direct = 0;
-#ifdef TA_WAIT_STATS
-    unsigned long long n_issue = 0;
-    long long w_end = clock64();
-#endif
     int cur_n = -1;
     Geom g;
     Colour<T, C, F> col;
@@ -107,15 +103,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         __syncwarp();
 
         // ---- (2) the stage must have been released by every consumer warp before it is overwritten
-#ifdef TA_WAIT_STATS
-        const long long w0 = clock64();
-        if (use > 0) n_staged += (unsigned long long)(w0 - w_end);      // compute part
-#endif
-        if (use > 0 && !mbar_wait_or_abort<kProducerSleepNs>(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
-#ifdef TA_WAIT_STATS
-        const long long w1 = clock64();
-        n_direct += (unsigned long long)(w1 - w0);
-#endif
+        if (use > 0 && !mbar_wait_or_abort(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
 
         // ---- (3) copies; the warp's own arrival publishes the descriptor
         if (staged) {
@@ -131,17 +119,11 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                     tma_load_3d(stage + c * kPlane + lane * kGroupRows * kPitch, &maps.rows[0], gxs,
                                 fp.row0 + lane * kGroupRows, n * C + c, &full[p]);
             }
-#ifndef TA_WAIT_STATS
             ++n_staged;
         } else {
             ++n_direct;
-#endif
         }
         if (lane == 0) mbar_arrive(&full[p]);
-#ifdef TA_WAIT_STATS
-        w_end = clock64();
-        n_issue += (unsigned long long)(w_end - w1);
-#endif
 
         // next tile of this warp
         tx += step_tx;
@@ -150,9 +132,6 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         if (ty >= k.tiles_y) { ty -= k.tiles_y; ++n; }
         n += step_n;
     }
-#ifdef TA_WAIT_STATS
-    if (lane == 0 && k.counters) atomicAdd(k.counters + kCntViolation, n_issue);
-#endif
     if (lane == 0 && k.counters) {
         if (n_staged) atomicAdd(k.counters + kCntStaged, n_staged);
         if (n_direct) atomicAdd(k.counters + kCntDirect, n_direct);

@@ -237,10 +237,6 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
     unsigned long long n_viol = 0;
-#ifdef TA_WAIT_STATS
-    long long wait_cycles = 0;
-    const long long t_begin = clock64();
-#endif
     int cur_n = -1;
     Geom g;
     Geom2 g2;
@@ -250,13 +246,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     int it = 0;
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
         const int s = it % kStages, use = it / kStages;
-#ifdef TA_WAIT_STATS
-        const long long w0 = clock64();
-#endif
-        if (!mbar_wait_or_abort<kConsumerSleepNs>(&full[s], (uint32_t)use & 1u, abort_flag)) return;
-#ifdef TA_WAIT_STATS
-        wait_cycles += clock64() - w0;
-#endif
+        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
         const T *stage = reinterpret_cast<const T *>(smem + s * Smem::stage);
         const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
         const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
@@ -322,12 +312,6 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         if (lane == 0) mbar_arrive(&empty[s]);
     }
     if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
-#ifdef TA_WAIT_STATS
-    if (lane == 0 && k.counters) {
-        (void)wait_cycles;
-        if (warp == 0) atomicAdd(k.counters + kCntTimeout, (unsigned long long)(clock64() - t_begin));  // one warp per CTA
-    }
-#endif
 }
 
 // ----------------------------------------------------------------------------- kernel
