@@ -131,8 +131,9 @@ class TritonFusedAugment(T._BatchAware):
         lay = T._Layout(image, self.same_on_batch, self.same_on_frame, upload=False)
         flat = lay.image.contiguous()
         F_ = F
-        if flat.ndim != 4 or flat.shape[1] not in (1, 3) or flat.dtype not in (torch.float32, torch.float16):
-            raise ValueError(f"expected float32/float16 images with 1 or 3 channels, got {tuple(image.shape)} {image.dtype}")
+        if flat.ndim != 4 or flat.shape[1] not in (1, 3) or flat.dtype not in (torch.float32, torch.float16, torch.uint8):
+            raise ValueError(f"expected float32/float16/uint8 images with 1 or 3 channels, got {tuple(image.shape)} {image.dtype}")
+        work = F._work_dtype(flat)        # float32 for bytes (read as value / 255)
         n, c, h, w = flat.shape
         oh = self.crop_height if self.crop_height is not None else h
         ow = self.crop_width if self.crop_width is not None else w
@@ -147,17 +148,17 @@ class TritonFusedAugment(T._BatchAware):
                 | (_lib.APPLY_SATURATION if flags["saturation"] else 0) | (_lib.APPLY_GRAYSCALE if flags["grayscale"] else 0)
                 | (_lib.APPLY_NORMALIZE if mean is not None else 0))
         if out is None:
-            out = torch.empty((n, c, oh, ow), dtype=flat.dtype, pin_memory=True)
-        elif out.is_cuda or not out.is_contiguous() or out.numel() != n * c * oh * ow or out.dtype != flat.dtype:
+            out = torch.empty((n, c, oh, ow), dtype=work, pin_memory=True)
+        elif out.is_cuda or not out.is_contiguous() or out.numel() != n * c * oh * ow or out.dtype != work:
             raise ValueError("out must be a contiguous host tensor with the output's size and dtype")
         host = lambda t, dt: t.to(dtype=dt).cpu().contiguous()
         keep = [host(top, torch.float32), host(left, torch.float32), host(flip, torch.uint8), matrix,
-                host(b, flat.dtype), host(cf, flat.dtype), host(s, flat.dtype), host(g, torch.uint8)]
+                host(b, work), host(cf, work), host(s, work), host(g, torch.uint8)]
         p = _lib.make_params(flat, out.view(n, c, oh, ow), keep[0], keep[1], keep[2], keep[3],
                              self.fill if self.has_affine else 0.0,
                              self.has_affine and F_._is_bilinear(self.interpolation), bits, keep[4], keep[5], keep[6],
-                             keep[7], F_._rounded_triple(mean, flat.dtype) if mean is not None else None,
-                             F_._rounded_triple(std, flat.dtype) if std is not None else None,
+                             keep[7], F_._rounded_triple(mean, work) if mean is not None else None,
+                             F_._rounded_triple(std, work) if std is not None else None,
                              F_._contrast_mode(self.contrast_mode))
         _lib.launch_fused_host(p, dev)
         return lay.restore(out.view(n, c, oh, ow))

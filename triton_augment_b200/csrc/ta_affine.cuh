@@ -36,11 +36,39 @@ namespace ta {
 constexpr int kConsumerWarps = 16;
 constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
-constexpr int kPlane = kMaxRows * kPitch;          // elements per channel per stage
+
+// Source element type S of a staged kernel whose pixels are T: S = T for float and half
+// images; S = uint8_t with T = float reads bytes and scales them by 1/255 (what ToTensor does
+// before the reference's pipeline) on the way from shared memory to registers.
+template <typename S> struct Src {
+    static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : kPitch;   // staged row pitch, elements
+    static constexpr int plane = kMaxRows * pitch;                         // elements per channel per stage
+    static constexpr int chunk = 16 / (int)sizeof(S);                      // elements per 16 bytes
+};
+constexpr float kInv255 = 1.0f / 255.0f;
+
+// Texel of type S -> pixel of type T.
+template <typename T, typename S> struct Px {
+    static constexpr bool scaled = false;
+    static __device__ __forceinline__ T from(S v) { return v; }
+    static __device__ __forceinline__ float raw_f(S v) { return Elem<T>::to_f(v); }    // blend operand
+    static __device__ __forceinline__ S lds(uint32_t addr) { return Elem<T>::lds(addr); }
+};
+template <> struct Px<float, uint8_t> {
+    static constexpr bool scaled = true;        // blends run on the raw 0..255 values, scaled once afterwards
+    static __device__ __forceinline__ float from(uint8_t v) { return __fmul_rn((float)v, kInv255); }
+    static __device__ __forceinline__ float raw_f(uint8_t v) { return (float)v; }
+    static __device__ __forceinline__ uint8_t lds(uint32_t addr)
+    {
+        uint32_t v;
+        asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+        return (uint8_t)v;
+    }
+};
 constexpr int kNumGroups = kMaxRows / kGroupRows;
 constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
 
-// The input seen as [N*C, H, W].  rows[g] copies a box of kPitch columns x (g + 1) * kGroupRows
+// The input seen as [N*C, H, W].  rows[g] copies a box of Src::pitch columns x (g + 1) * kGroupRows
 // rows of one plane: a window tile is one copy per channel.  rows[0] doubles as the per-group
 // box of tiles whose groups start at different columns.
 struct alignas(64) TMaps {
@@ -51,7 +79,7 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int n, x0, y0;        // image, first output column / row of the tile
     int rows, row0;       // staged source rows (rows == 0: gather this tile from global memory)
     int window;           // every row starts at column xs0: texel (y, x) sits at element
-    int xs0;              //   (y - row0) * kPitch + (x - xs0) of a channel plane
+    int xs0;              //   (y - row0) * pitch + (x - xs0) of a channel plane
     int pad;
     Geom g;
     Colour<T, C, F> col;
@@ -62,8 +90,8 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
 // uses stage i % kStages and descriptor i % kInfoSlots, so the producer can write the descriptor
 // of the stage's next tile while the consumers still read the current one, and only the copy
 // itself has to wait for the stage to be released.
-template <typename T, int C, unsigned F> struct AffineSmem {
-    static constexpr size_t stage = ((size_t)C * kPlane * sizeof(T) + 1023) / 1024 * 1024;
+template <typename T, int C, unsigned F, typename S = T> struct AffineSmem {
+    static constexpr size_t stage = ((size_t)C * Src<S>::plane * sizeof(S) + 1023) / 1024 * 1024;
     static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
     static constexpr size_t total = kStages * stage + kInfoSlots * info;
 };
@@ -103,15 +131,20 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
 }
 
 // Gather rows [y_first, y_first + y_count) of one tile column from global memory (no staging).
-template <typename T, int C, int MODE, unsigned F, bool MIX>
+template <typename T, int C, int MODE, unsigned F, bool MIX, typename S>
 __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g, const Colour<T, C, F> &col,
                                                    int n, int x, int y_first, int y_count)
 {
     if (x >= k.ow) return;
-    const T *img = (const T *)k.in + (size_t)n * C * k.h * k.w;
+    const S *img = (const S *)k.in + (size_t)n * C * k.h * k.w;
     T *out = (T *)k.out + (size_t)n * C * k.oh * k.ow;
     const size_t plane = (size_t)k.h * k.w, oplane = (size_t)k.oh * k.ow;
     const T fillv = Elem<T>::from_f(MODE == 0 ? 0.0f : k.fill);
+    // texel (xx, yy) of a channel plane as a pixel value; outside the image: the fill value
+    auto tap = [&](const S *pl, int xx, int yy) -> T {
+        const bool ok = (unsigned)xx < (unsigned)k.w && (unsigned)yy < (unsigned)k.h;
+        return ok ? Px<T, S>::from(__ldg(pl + (size_t)yy * k.w + xx)) : fillv;
+    };
     const float xi = img_x(g, k.ow, x);
     const float xc = centred(xi, g.half_w);
     for (int i = 0; i < y_count; ++i) {
@@ -129,17 +162,16 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
         if (MODE != 2) {
             const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
 #pragma unroll
-            for (int c = 0; c < C; ++c) s[c] = tap_global(img + c * plane, k.w, k.h, xn, yn, fillv);
+            for (int c = 0; c < C; ++c) s[c] = tap(img + c * plane, xn, yn);
         } else {
             const int x0 = __float2int_rd(sx), y0 = __float2int_rd(sy);
             const float dx = sx - (float)x0, dy = sy - (float)y0;
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                const T *pl = img + c * plane;
-                s[c] = Elem<T>::from_f(blend4(Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0, fillv)),
-                                              Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0, fillv)),
-                                              Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0 + 1, fillv)),
-                                              Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0 + 1, fillv)), dx, dy));
+                const S *pl = img + c * plane;
+                s[c] = Elem<T>::from_f(blend4(Elem<T>::to_f(tap(pl, x0, y0)), Elem<T>::to_f(tap(pl, x0 + 1, y0)),
+                                              Elem<T>::to_f(tap(pl, x0, y0 + 1)), Elem<T>::to_f(tap(pl, x0 + 1, y0 + 1)),
+                                              dx, dy));
             }
         }
         float v[C];

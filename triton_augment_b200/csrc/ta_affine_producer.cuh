@@ -9,17 +9,17 @@
 
 namespace ta {
 
-template <typename T, int C, int MODE, unsigned F>
+template <typename T, int C, int MODE, unsigned F, typename S>
 __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &maps, unsigned char *smem,
                                                 uint64_t *full, uint64_t *empty, volatile int *abort_flag, int p)
 {
     using Info = TileInfo<T, C, F>;
-    using Smem = AffineSmem<T, C, F>;
-    constexpr int CH = 16 / (int)sizeof(T);
+    using Smem = AffineSmem<T, C, F, S>;
+    constexpr int CH = Src<S>::chunk, PITCH = Src<S>::pitch, PLANE = Src<S>::plane;
     static_assert(kNumGroups <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
     const int lane = threadIdx.x & 31;
     const int tiles_per_img = k.tiles_x * k.tiles_y;
-    T *stage = reinterpret_cast<T *>(smem + p * Smem::stage);
+    S *stage = reinterpret_cast<S *>(smem + p * Smem::stage);
     unsigned long long n_staged = 0, n_direct = 0;
     int cur_n = -1;
     Geom g;
@@ -55,7 +55,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         int gxs = 0;
         const int ngroups = (fp.rows + kGroupRows - 1) / kGroupRows;
         if (staged) {
-            window = MODE == 0 ? tile_window_crop(fp, CH, gxs) : tile_window(fp, FMODE, CH, gxs);
+            window = MODE == 0 ? tile_window_crop(fp, CH, PITCH, gxs) : tile_window(fp, FMODE, CH, PITCH, gxs);
             bool inside;
             if (MODE == 0) {
                 staged = window;              // zero outside the image is the crop kernels' rule too
@@ -66,21 +66,21 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                 inside = c0 >= 0 && c1 < k.w;
             } else {
                 // lanes 0 .. kNumGroups-1: columns of row group `lane`; the other lanes hold a neutral entry
-                staged = tile_edges(fp, FMODE, CH, m);
+                staged = tile_edges(fp, FMODE, CH, PITCH, m);
                 int xs = 0, xe = CH;
                 const int r_first = lane * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
                 const bool have = staged && lane < ngroups && tile_rows_range(fp, FMODE, CH, r_first, r_last, xs, xe);
                 if (!have) { xs = 0; xe = CH; }
                 gxs = xs;
-                staged = staged && __all_sync(0xffffffffu, xe - xs <= kPitch);
+                staged = staged && __all_sync(0xffffffffu, xe - xs <= PITCH);
                 inside = __all_sync(0xffffffffu, !have || (xs >= 0 && xe <= k.w));
                 if (staged) {
-                    // rowoff[r] = r * kPitch - (first column of r's group); rows lane, lane + 32, ...
+                    // rowoff[r] = r * PITCH - (first column of r's group); rows lane, lane + 32, ...
 #pragma unroll
                     for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
                         const int r = base + lane;
                         const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, kNumGroups - 1));
-                        if (r < kMaxRows) ti->rowoff[r] = r * kPitch - x_first;
+                        if (r < kMaxRows) ti->rowoff[r] = r * PITCH - x_first;
                     }
                     if (lane == 0) ti->rowoff[kMaxRows] = 0;
                 }
@@ -108,15 +108,15 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         // ---- (3) copies; the warp's own arrival publishes the descriptor
         if (staged) {
             if (lane == 0)
-                mbar_expect_tx(&full[p], (uint32_t)(ngroups * C * kPitch * kGroupRows * (int)sizeof(T)));
+                mbar_expect_tx(&full[p], (uint32_t)(ngroups * C * PITCH * kGroupRows * (int)sizeof(S)));
             __syncwarp();
             if (window) {
                 if (lane < C)         // one box of ngroups * kGroupRows rows per channel
-                    tma_load_3d(stage + lane * kPlane, &maps.rows[ngroups - 1], gxs, fp.row0, n * C + lane, &full[p]);
+                    tma_load_3d(stage + lane * PLANE, &maps.rows[ngroups - 1], gxs, fp.row0, n * C + lane, &full[p]);
             } else if (lane < ngroups) {
 #pragma unroll
                 for (int c = 0; c < C; ++c)
-                    tma_load_3d(stage + c * kPlane + lane * kGroupRows * kPitch, &maps.rows[0], gxs,
+                    tma_load_3d(stage + c * PLANE + lane * kGroupRows * PITCH, &maps.rows[0], gxs,
                                 fp.row0 + lane * kGroupRows, n * C + c, &full[p]);
             }
             ++n_staged;

@@ -61,14 +61,16 @@ namespace ta {
 // Texels of one pixel pair (two output rows, same column) from a stage, two ways.
 //
 // Window path (TileInfo::window): all staged rows start at column xs0, so texel (y, x) lives at
-// byte  stage + ES * ((y - row0) * kPitch + (x - xs0)).  The integers y and x never exist as
+// byte  stage + ES * ((y - row0) * pitch + (x - xs0)).  The integers y and x never exist as
 // such: adding 1.5 * 2^23 to a coordinate leaves rint / floor of it in the low bits of the
-// float, and address = kb + ES * kPitch * bits(y) + ES * bits(x) with every constant (stage
+// float, and address = kb + ES * pitch * bits(y) + ES * bits(x) with every constant (stage
 // base, row0, xs0, the two magic offsets) folded into kb once per tile, modulo 2^32.
 //
 // Table path: each row group has its own first column; rowoff[] translates.
-template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
-    static constexpr uint32_t ES = sizeof(T), ROWB = ES * kPitch, PLANEB = ES * kPlane;
+template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSampler {
+    static constexpr int PITCH = Src<S>::pitch, PLANE = Src<S>::plane;
+    static constexpr uint32_t ES = sizeof(S), ROWB = ES * PITCH, PLANEB = ES * PLANE;
+    using P = Px<T, S>;
 
     // -> smp[j][c], j = 0 / 1 for the pair's first / second row
     static __device__ __forceinline__ void window(const Const2 &k2, uint32_t stage_addr, uint32_t kb, int rows, int row0,
@@ -84,10 +86,10 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                 uint32_t addr = kb + by * ROWB + bx * ES;
                 if (CHECK) {
                     const int r = (int)(by - (uint32_t)kMagicBits) - row0, x = (int)(bx - (uint32_t)kMagicBits) - xs0;
-                    if ((unsigned)r >= (unsigned)rows || (unsigned)x >= (unsigned)kPitch) { ++n_viol; addr = stage_addr; }
+                    if ((unsigned)r >= (unsigned)rows || (unsigned)x >= (unsigned)PITCH) { ++n_viol; addr = stage_addr; }
                 }
 #pragma unroll
-                for (int c = 0; c < C; ++c) smp[j][c] = Elem<T>::lds(addr + c * PLANEB);
+                for (int c = 0; c < C; ++c) smp[j][c] = P::from(P::lds(addr + c * PLANEB));
             }
         } else {
             const float2 tx = pk_add_rd(sx, magic), ty = pk_add_rd(sy, magic);
@@ -101,7 +103,7 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                 addr[j] = kb + by * ROWB + bx * ES;
                 if (CHECK) {
                     const int r = (int)(by - (uint32_t)kMagicBits) - row0, x = (int)(bx - (uint32_t)kMagicBits) - xs0;
-                    if ((unsigned)r >= (unsigned)(rows - 1) || (unsigned)x >= (unsigned)(kPitch - 1)) {
+                    if ((unsigned)r >= (unsigned)(rows - 1) || (unsigned)x >= (unsigned)(PITCH - 1)) {
                         ++n_viol; addr[j] = stage_addr;
                     }
                 }
@@ -112,17 +114,18 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
 #pragma unroll
             for (int c = 0; c < C; ++c) {
                 const uint32_t a0 = addr[0] + c * PLANEB, a1 = addr[1] + c * PLANEB;
-                float2 acc = pk_mul(f2(Elem<T>::to_f(Elem<T>::lds(a0)), Elem<T>::to_f(Elem<T>::lds(a1))), w00);
-                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ES)), Elem<T>::to_f(Elem<T>::lds(a1 + ES))), w10, acc);
-                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ROWB)), Elem<T>::to_f(Elem<T>::lds(a1 + ROWB))), w01, acc);
-                acc = pk_fma(f2(Elem<T>::to_f(Elem<T>::lds(a0 + ROWB + ES)), Elem<T>::to_f(Elem<T>::lds(a1 + ROWB + ES))), w11, acc);
+                float2 acc = pk_mul(f2(P::raw_f(P::lds(a0)), P::raw_f(P::lds(a1))), w00);
+                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ES)), P::raw_f(P::lds(a1 + ES))), w10, acc);
+                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ROWB)), P::raw_f(P::lds(a1 + ROWB))), w01, acc);
+                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ROWB + ES)), P::raw_f(P::lds(a1 + ROWB + ES))), w11, acc);
+                if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
                 smp[0][c] = Elem<T>::from_f(acc.x);
                 smp[1][c] = Elem<T>::from_f(acc.y);
             }
         }
     }
 
-    static __device__ __forceinline__ void table(const Const2 &k2, const T *stage, const int *rowoff, int rows,
+    static __device__ __forceinline__ void table(const Const2 &k2, const S *stage, const int *rowoff, int rows,
                                                  int row0, float2 sx, float2 sy, T (&smp)[2][C],
                                                  unsigned long long &n_viol)
     {
@@ -133,9 +136,9 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                 int r = rint_magic(j ? sy.y : sy.x) - row0;
                 if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
                 int idx = rowoff[r] + xn;
-                if (CHECK && (unsigned)(idx - r * kPitch) >= (unsigned)kPitch) { ++n_viol; idx = 0; }
+                if (CHECK && (unsigned)(idx - r * PITCH) >= (unsigned)PITCH) { ++n_viol; idx = 0; }
 #pragma unroll
-                for (int c = 0; c < C; ++c) smp[j][c] = stage[c * kPlane + idx];
+                for (int c = 0; c < C; ++c) smp[j][c] = P::from(stage[c * PLANE + idx]);
             }
         } else {
             int i0[2], i1[2];
@@ -150,8 +153,8 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
                 if (CHECK && (unsigned)r >= (unsigned)(rows - 1)) { ++n_viol; r = 0; }
                 i0[j] = rowoff[r] + x0;
                 i1[j] = rowoff[r + 1] + x0;
-                if (CHECK && ((unsigned)(i0[j] - r * kPitch) >= (unsigned)(kPitch - 1) ||
-                              (unsigned)(i1[j] - (r + 1) * kPitch) >= (unsigned)(kPitch - 1))) {
+                if (CHECK && ((unsigned)(i0[j] - r * PITCH) >= (unsigned)(PITCH - 1) ||
+                              (unsigned)(i1[j] - (r + 1) * PITCH) >= (unsigned)(PITCH - 1))) {
                     ++n_viol; i0[j] = i1[j] = 0;
                 }
             }
@@ -161,11 +164,12 @@ template <typename T, int C, int MODE, bool CHECK> struct PairSampler {
             const float2 w01 = pk_mul(omx, dy), w11 = pk_mul(dx, dy);
 #pragma unroll
             for (int c = 0; c < C; ++c) {
-                const T *pl = stage + c * kPlane;
-                float2 acc = pk_mul(f2(Elem<T>::to_f(pl[i0[0]]), Elem<T>::to_f(pl[i0[1]])), w00);
-                acc = pk_fma(f2(Elem<T>::to_f(pl[i0[0] + 1]), Elem<T>::to_f(pl[i0[1] + 1])), w10, acc);
-                acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0]]), Elem<T>::to_f(pl[i1[1]])), w01, acc);
-                acc = pk_fma(f2(Elem<T>::to_f(pl[i1[0] + 1]), Elem<T>::to_f(pl[i1[1] + 1])), w11, acc);
+                const S *pl = stage + c * PLANE;
+                float2 acc = pk_mul(f2(P::raw_f(pl[i0[0]]), P::raw_f(pl[i0[1]])), w00);
+                acc = pk_fma(f2(P::raw_f(pl[i0[0] + 1]), P::raw_f(pl[i0[1] + 1])), w10, acc);
+                acc = pk_fma(f2(P::raw_f(pl[i1[0]]), P::raw_f(pl[i1[1]])), w01, acc);
+                acc = pk_fma(f2(P::raw_f(pl[i1[0] + 1]), P::raw_f(pl[i1[1] + 1])), w11, acc);
+                if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
                 smp[0][c] = Elem<T>::from_f(acc.x);
                 smp[1][c] = Elem<T>::from_f(acc.y);
             }
@@ -225,13 +229,13 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
     }
 }
 
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX>
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
                                                 volatile int *abort_flag)
 {
     using Info = TileInfo<T, C, F>;
-    using Sampler = PairSampler<T, C, MODE, CHECK>;
-    using Smem = AffineSmem<T, C, F>;
+    using Sampler = PairSampler<T, C, MODE, CHECK, S>;
+    using Smem = AffineSmem<T, C, F, S>;
     constexpr int ROWS_PER_WARP = kTileH / (kConsumerWarps / 2);     // 4
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
@@ -247,7 +251,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
         const int s = it % kStages, use = it / kStages;
         if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
-        const T *stage = reinterpret_cast<const T *>(smem + s * Smem::stage);
+        const S *stage = reinterpret_cast<const S *>(smem + s * Smem::stage);
         const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
         const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
         const int4 h1 = *reinterpret_cast<const int4 *>(&ti->row0);    // row0, window, xs0, -
@@ -262,7 +266,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         const int y_first = h0.z + wy * ROWS_PER_WARP;
 
         if (rows == 0) {
-            affine_rows_direct<T, C, MODE, F, MIX>(k, g, col, n, x, y_first, ROWS_PER_WARP);
+            affine_rows_direct<T, C, MODE, F, MIX, S>(k, g, col, n, x, y_first, ROWS_PER_WARP);
         } else if (x < k.ow) {
             T *plane[C];
             plane[0] = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
@@ -274,8 +278,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
             const bool window = h1.y != 0;
             const int xs0 = h1.z;
             const uint32_t stage_addr = smem_u32(stage);
-            const uint32_t kb = stage_addr - Sampler::ES * (uint32_t)(row0 * kPitch + xs0)
-                                - Sampler::ES * (uint32_t)(kPitch + 1) * (uint32_t)kMagicBits;
+            const uint32_t kb = stage_addr - Sampler::ES * (uint32_t)(row0 * Sampler::PITCH + xs0)
+                                - Sampler::ES * (uint32_t)(Sampler::PITCH + 1) * (uint32_t)kMagicBits;
 #pragma unroll
             for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
                 // No early exit: rows past the image's last row are computed on the last row's
@@ -316,7 +320,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 
 // ----------------------------------------------------------------------------- kernel
 // MIX: the variant of a swapped bilinear kernel (CoordRecipe) that applies late_x() per pixel.
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false>
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T>
 __global__ void __launch_bounds__(kAffineThreads, 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
@@ -338,9 +342,9 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     __syncthreads();
 
     if ((threadIdx.x >> 5) >= kConsumerWarps)
-        affine_producer<T, C, MODE, F>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
+        affine_producer<T, C, MODE, F, S>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
     else
-        affine_consumer<T, C, MODE, F, CHECK, MIX>(k, smem, full, empty, &abort_flag);
+        affine_consumer<T, C, MODE, F, CHECK, MIX, S>(k, smem, full, empty, &abort_flag);
 
     // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
     // memory: give each stage one more bounded chance to settle before the memory is released.

@@ -37,7 +37,7 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 6, kNumDtypes = 2;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
+constexpr int kNumKinds = 6, kNumDtypes = 3;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
@@ -83,8 +83,15 @@ static int current_device(DeviceState **out, int *index)
     return TA_B200_OK;
 }
 
+// bytes per element of `in` / of `out` and the factor vectors
+static size_t in_bytes(int dtype) { return dtype == TA_B200_F32 ? 4 : dtype == TA_B200_F16 ? 2 : 1; }
+static size_t out_bytes(int dtype) { return dtype == TA_B200_F16 ? 2 : 4; }
+
 static const KernelTable &table_for(int kind, int dtype)
 {
+    if (dtype == TA_B200_U8)      // staged kernels only (launch_fused never asks for kind 0)
+        return kind == 1 ? table_u8_nearest() : kind == 2 ? table_u8_bilinear() : kind == 3 ? table_u8_crop_staged()
+                                                                                           : table_u8_bilinear_mix();
     if (dtype == TA_B200_F32)
         return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : kind == 2 ? table_f32_bilinear()
                : kind == 3 ? table_f32_crop_staged() : table_f32_bilinear_mix();
@@ -122,7 +129,10 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
     if (p->struct_size != sizeof(ta_b200_fused_params))
         return fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", p->struct_size,
                     sizeof(ta_b200_fused_params));
-    if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16) return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
+    if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16 && p->dtype != TA_B200_U8)
+        return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
+    if (p->dtype == TA_B200_U8 && (for_mean || ((p->apply & TA_B200_APPLY_CONTRAST) && p->contrast_mode == TA_B200_CONTRAST_MEAN)))
+        return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale-mean pre-pass and CONTRAST_MEAN take float images, not uint8");
     if (p->c != 1 && p->c != 3)
         return fail(TA_B200_ERR_SHAPE, "channels must be 1 or 3, got %d", p->c);
     if (p->n < 0 || p->h <= 0 || p->w <= 0 || p->oh <= 0 || p->ow <= 0)
@@ -172,9 +182,9 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
     static const unsigned char late_count[32] = {0, 0, 0, 0, 0, 1, 1, 3, 0, 2, 1, 3, 0, 2, 2, 3,
                                                  0, 0, 0, 0, 0, 1, 2, 3, 0, 2, 1, 3, 0, 2, 2, 3};
     k.late_x_slot = 8;
-    if (p->matrix && p->interp == TA_B200_BILINEAR && p->dtype == TA_B200_F32 && p->oh % 16 != 0 && p->ow % 16 != 0)
+    if (p->matrix && p->interp == TA_B200_BILINEAR && p->dtype != TA_B200_F16 && p->oh % 16 != 0 && p->ow % 16 != 0)
         k.late_x_slot = 8 - late_count[p->apply & 31u];
-    const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
+    const size_t es = in_bytes(p->dtype);
     k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
                   ((size_t)p->h * p->w * es) % 16 == 0 &&
                   // the staged path converts coordinates with a 2^22-range shortcut
@@ -206,19 +216,21 @@ static EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
-// Tensor maps over the input seen as [n*c, h, w]: boxes of kPitch columns x 8, 16, ... kMaxRows
-// rows x 1 plane, out-of-range elements read as zero.
+// Tensor maps over the input seen as [n*c, h, w]: boxes of pitch_of(element size) columns x 8, 16,
+// ... kMaxRows rows x 1 plane, out-of-range elements read as zero.
 static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
 {
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const size_t es = p->dtype == TA_B200_F32 ? 4 : 2;
+    const size_t es = in_bytes(p->dtype);
+    const CUtensorMapDataType dt = p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : p->dtype == TA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const cuuint64_t dims[3] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->n * p->c};
     const cuuint64_t strides[2] = {(cuuint64_t)p->w * es, (cuuint64_t)p->w * p->h * es};
     const cuuint32_t estr[3] = {1, 1, 1};
     for (int g = 0; g < kNumGroups; ++g) {
-        const cuuint32_t box[3] = {(cuuint32_t)kPitch, (cuuint32_t)((g + 1) * kGroupRows), 1};
-        CUresult r = enc(&maps.rows[g], p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+        const cuuint32_t box[3] = {(cuuint32_t)pitch_of((int)es), (cuuint32_t)((g + 1) * kGroupRows), 1};
+        CUresult r = enc(&maps.rows[g], dt,
                          3, const_cast<void *>(p->in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
@@ -249,6 +261,10 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
             k.fill = 0.0f;
         }
     }
+    if (kind == 0 && p->dtype == TA_B200_U8) {     // bytes are read by the staged kernels only
+        kind = 3;
+        k.fill = 0.0f;
+    }
     unsigned f = template_flags(p);
     if (kind == 2 && k.late_x_slot < 8 && !checked) kind = 4;     // only swapped fp32 variants get here (fill_kargs)
     const KernelTable &tab = table_for(kind, p->dtype);
@@ -262,7 +278,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         ke = p->c == 3 ? &tab.c3[f] : &tab.c1[f];
     }
     // Crop/flip only: the 128-bit kernel needs whole-vector output rows and vector-aligned tensors.
-    const size_t es_bytes = p->dtype == TA_B200_F32 ? 4 : 2;
+    const size_t es_bytes = in_bytes(p->dtype);
     const int epv = (int)(16 / es_bytes);
     const bool vec = kind == 0 && !g_force_scalar_direct && p->ow % epv == 0 && ((uintptr_t)p->in % 16) == 0 &&
                      ((uintptr_t)p->out % 16) == 0 && ((size_t)p->n * p->c * p->h * p->w * es_bytes) % 16 == 0;

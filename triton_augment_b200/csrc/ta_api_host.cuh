@@ -60,8 +60,8 @@ static int fused_host(const ta_b200_fused_params *hp)
         }
         P.ready = true;
     }
-    const size_t es = hp->dtype == TA_B200_F32 ? 4 : 2;
-    const size_t in_img = (size_t)hp->c * hp->h * hp->w * es, out_img = (size_t)hp->c * hp->oh * hp->ow * es;
+    const size_t es = ta::out_bytes(hp->dtype);          // output elements and factor vectors
+    const size_t in_img = (size_t)hp->c * hp->h * hp->w * ta::in_bytes(hp->dtype), out_img = (size_t)hp->c * hp->oh * hp->ow * es;
     // Slice size: about 48 MiB of input per slice, at least 1 image, at least 4 slices when possible.
     long long per = (long long)((48ull << 20) / (in_img ? in_img : 1));
     if (per < 1) per = 1;
@@ -222,16 +222,16 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
                                  int32_t tile_y, int32_t *row0, int32_t *xs, int32_t *xe, int32_t cap)
 {
     ta::TileFootprint fp;
-    const int chunk = 16 / (elem_bytes == 2 ? 2 : 4);
+    const int chunk = 16 / (elem_bytes == 1 ? 1 : elem_bytes == 2 ? 2 : 4), pitch = ta::pitch_of(elem_bytes);
     const int mode = interp == TA_B200_BILINEAR ? 1 : 0;
     ta::tile_footprint(fp, mode, h, w, oh, ow, top, left, flip != 0, matrix, tile_x, tile_y);
     if (row0) *row0 = fp.row0;
     int group_xs[ta::kMaxRows / ta::kGroupRows];
     bool window = false;
-    if (!ta::tile_plan(fp, mode, chunk, matrix, group_xs, &window)) return 0;
+    if (!ta::tile_plan(fp, mode, chunk, pitch, matrix, group_xs, &window)) return 0;
     for (int r = 0; r < fp.rows && r < cap; ++r) {
         xs[r] = group_xs[r / ta::kGroupRows];
-        xe[r] = xs[r] + ta::kPitch;
+        xe[r] = xs[r] + pitch;
     }
     return fp.rows;
 }

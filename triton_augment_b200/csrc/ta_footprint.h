@@ -29,10 +29,15 @@ constexpr int kTileW = 64;       // output tile, pixels
 constexpr int kTileH = 32;
 constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 groups of 8 rows)
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
-constexpr int kPitch = 96;       // staged row pitch = width of every tensor-copy box, in elements.
-// A pitch that is a multiple of 32 words keeps lanes of one warp that sit in different source
-// rows on different banks (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but
-// 2-way bank conflicts cost more than they saved).
+// Staged row pitch = width of every tensor-copy box, in elements.  A pitch that is a multiple
+// of 32 words keeps lanes of one warp that sit in different source rows on different banks
+// (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but 2-way bank conflicts cost
+// more than they saved).  One-byte elements need 128: a copy starts on a 16-byte boundary, i.e.
+// up to 15 columns left of the footprint, and a 64-pixel tile under +-15 degrees and scale 1.1
+// already spans ~85 columns.
+constexpr int kPitch = 96;
+constexpr int kPitchBytes1 = 128;
+TA_HD int pitch_of(int elem_bytes) { return elem_bytes == 1 ? kPitchBytes1 : kPitch; }
 constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
 constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
 
@@ -95,14 +100,14 @@ TA_HD void column_range(int mode, float lo, float hi, int &c0, int &c1)
     else           { c0 = (int)floorf(lo - kEps);       c1 = (int)floorf(hi + kEps) + 1; }
 }
 
-// The common case: one window of kPitch columns starting at xs (a multiple of `chunk`) covers
+// The common case: one window of `pitch` columns starting at xs (a multiple of `chunk`) covers
 // every row the tile reads, i.e. the bounding box of the corners fits.
-TA_HD bool tile_window(const TileFootprint &t, int mode, int chunk, int &xs)
+TA_HD bool tile_window(const TileFootprint &t, int mode, int chunk, int pitch, int &xs)
 {
     int c0, c1;
     column_range(mode, t.xmin, t.xmax, c0, c1);
     xs = chunk_floor(c0, chunk);
-    return c1 + 1 - xs <= kPitch;
+    return c1 + 1 - xs <= pitch;
 }
 
 // Crop / flip without a matrix: source pixel = (int)(x_img), (int)(y_img) (truncation, as the
@@ -128,17 +133,17 @@ TA_HD void tile_footprint_crop(TileFootprint &t, int oh, int ow, float top, floa
     t.rows = r1 - r0 + 1;
 }
 
-TA_HD bool tile_window_crop(const TileFootprint &t, int chunk, int &xs)
+TA_HD bool tile_window_crop(const TileFootprint &t, int chunk, int pitch, int &xs)
 {
     xs = chunk_floor((int)t.xmin, chunk);
-    return (int)t.xmax + 1 - xs <= kPitch;
+    return (int)t.xmax + 1 - xs <= pitch;
 }
 
 // Otherwise rows are fetched in groups with a window each; this prepares the per-edge terms
 // tile_rows_range() needs and checks that no group can be wider than a window.  Inside a slab
 // of height s in source y, eliminating yc gives sx = (a - b d / e) xc + (b / e) sy + const and
 // eliminating xc gives sx = (b - a e / d) yc + (a / d) sy + const; either bounds a row's span.
-TA_HD bool tile_edges(TileFootprint &t, int mode, int chunk, const float *m)
+TA_HD bool tile_edges(TileFootprint &t, int mode, int chunk, int pitch, const float *m)
 {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -150,7 +155,7 @@ TA_HD bool tile_edges(TileFootprint &t, int mode, int chunk, const float *m)
     if (m[4] != 0.0f) span = fminf(span, fabsf(m[0] - m[1] * m[3] / m[4]) * t.dx + fabsf(m[1] / m[4]) * s);
     if (m[3] != 0.0f) span = fminf(span, fabsf(m[1] - m[0] * m[4] / m[3]) * t.dy + fabsf(m[0] / m[3]) * s);
     // + 2 eps, + the second tap / rounding to nearest, + rounding both ends to whole chunks
-    return span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)kPitch;
+    return span + 2.0f * kEps + 2.0f + 2.0f * (float)(chunk - 1) <= (float)pitch;
 }
 
 // Columns [xs, xe) of source rows row0 + r_first .. row0 + r_last that the tile reads, rounded
@@ -188,26 +193,26 @@ TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_fi
     return true;
 }
 
-// What is actually fetched.  Window case: all rows, kPitch columns from *group_xs.  Otherwise
-// rows in groups of kGroupRows, every group kPitch columns from the smallest xs of its rows
+// What is actually fetched.  Window case: all rows, `pitch` columns from *group_xs.  Otherwise
+// rows in groups of kGroupRows, every group `pitch` columns from the smallest xs of its rows
 // (group_xs has kMaxRows / kGroupRows entries).  Scalar restatement of the producer warp's
 // decisions; returns false when the tile is not staged.
-TA_HD bool tile_plan(TileFootprint &t, int mode, int chunk, const float *m, int *group_xs, bool *window)
+TA_HD bool tile_plan(TileFootprint &t, int mode, int chunk, int pitch, const float *m, int *group_xs, bool *window)
 {
     if (t.rows == 0) return false;
     int xs;
-    *window = tile_window(t, mode, chunk, xs);
+    *window = tile_window(t, mode, chunk, pitch, xs);
     if (*window) {
         for (int g = 0; g < kMaxRows / kGroupRows; ++g) group_xs[g] = xs;
         return true;
     }
-    if (!tile_edges(t, mode, chunk, m)) return false;
+    if (!tile_edges(t, mode, chunk, pitch, m)) return false;
     for (int g = 0; g < kMaxRows / kGroupRows; ++g) {
         int lo = 0, hi = chunk;
         const int r_first = g * kGroupRows;
         const int r_last = r_first + kGroupRows - 1 < t.rows - 1 ? r_first + kGroupRows - 1 : t.rows - 1;
         if (r_first >= t.rows || !tile_rows_range(t, mode, chunk, r_first, r_last, lo, hi)) { lo = 0; hi = chunk; }
-        if (hi - lo > kPitch) return false;
+        if (hi - lo > pitch) return false;
         group_xs[g] = lo;
     }
     return true;

@@ -37,18 +37,19 @@ constexpr bool flags_valid(int channels, unsigned f)
 }
 
 // KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear, 3 crop/flip through the staged kernel,
-// 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only)
-template <typename T, int C, int KIND, unsigned F, bool CHECK = false> KernelEntry kernel_entry()
+// 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only).
+// S: source element type (uint8_t with T = float: bytes scaled by 1/255; staged kernels only).
+template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename S = T> KernelEntry kernel_entry()
 {
     if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
     else if constexpr (KIND == 0) return KernelEntry{(const void *)&direct_kernel<T, C, F>, 0, kThreads};
     else if constexpr (KIND == 4) {
         if constexpr (CoordRecipe<2, F>::swapped && !CHECK)
-            return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true>, AffineSmem<T, C, F>::total,
+            return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true, S>, AffineSmem<T, C, F, S>::total,
                                kAffineThreads};
         else return KernelEntry{nullptr, 0, 0};
-    } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK>,
-                              AffineSmem<T, C, F>::total, kAffineThreads};
+    } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK, false, S>,
+                              AffineSmem<T, C, F, S>::total, kAffineThreads};
 }
 
 template <typename T, int C, unsigned F> KernelEntry vec_entry()
@@ -57,14 +58,14 @@ template <typename T, int C, unsigned F> KernelEntry vec_entry()
     else return KernelEntry{(const void *)&direct_vec_kernel<T, C, F>, 0, kThreads};
 }
 
-template <typename T, int KIND, unsigned... Fs>
+template <typename T, int KIND, typename S, unsigned... Fs>
 void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
 {
-    ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs>()), ...);
-    ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs>()), ...);
+    ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs, false, S>()), ...);
+    ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs, false, S>()), ...);
     if constexpr (KIND != 0) {
-        t.c3_checked = kernel_entry<T, 3, KIND, 0u, true>();
-        t.c1_checked = kernel_entry<T, 1, KIND, 0u, true>();
+        t.c3_checked = kernel_entry<T, 3, KIND, 0u, true, S>();
+        t.c1_checked = kernel_entry<T, 1, KIND, 0u, true, S>();
     } else {
         t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
         ((t.c3_vec[Fs] = vec_entry<T, 3, Fs>()), ...);
@@ -72,11 +73,11 @@ void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
     }
 }
 
-template <typename T, int KIND> const KernelTable &make_table()
+template <typename T, int KIND, typename S = T> const KernelTable &make_table()
 {
     static KernelTable t = [] {
         KernelTable x{};
-        fill_table<T, KIND>(x, std::make_integer_sequence<unsigned, kNumFlagCombos>{});
+        fill_table<T, KIND, S>(x, std::make_integer_sequence<unsigned, kNumFlagCombos>{});
         return x;
     }();
     return t;
@@ -86,6 +87,10 @@ template <typename T, int KIND> const KernelTable &make_table()
 const KernelTable &table_f32_direct();
 const KernelTable &table_f32_crop_staged();
 const KernelTable &table_f32_bilinear_mix();
+const KernelTable &table_u8_crop_staged();
+const KernelTable &table_u8_nearest();
+const KernelTable &table_u8_bilinear();
+const KernelTable &table_u8_bilinear_mix();
 const KernelTable &table_f32_nearest();
 const KernelTable &table_f32_bilinear();
 const KernelTable &table_f16_direct();

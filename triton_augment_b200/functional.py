@@ -33,8 +33,9 @@ class InterpolationMode:
 
 
 # ----------------------------------------------------------------------------- checks and conversions
-def _validate_image_tensor(tensor, name: str = "tensor") -> None:
-    """Reference: functional.py:50-81 (same exception types)."""
+def _validate_image_tensor(tensor, name: str = "tensor", allow_uint8: bool = False) -> None:
+    """Reference: functional.py:50-81 (same exception types).  ``allow_uint8``: the fused entry
+    points also take bytes (an extension, see fused_augment)."""
     if not isinstance(tensor, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor, got {type(tensor)}")
     if not tensor.is_cuda:
@@ -43,8 +44,13 @@ def _validate_image_tensor(tensor, name: str = "tensor") -> None:
         raise ValueError(f"{name} must be a 4D tensor with shape (N, C, H, W), got shape {tensor.shape}")
     if tensor.shape[1] not in (1, 3):
         raise TypeError(f"Input image tensor permitted channel values are 1 or 3, but found {tensor.shape[1]}")
-    if tensor.dtype not in (torch.float32, torch.float16):
+    if tensor.dtype not in (torch.float32, torch.float16) and not (allow_uint8 and tensor.dtype == torch.uint8):
         raise TypeError(f"{name} must be float32 or float16, got {tensor.dtype}")
+
+
+def _work_dtype(image: torch.Tensor):
+    """dtype of the result and of the per-image factors: the image's, float32 for bytes."""
+    return torch.float32 if image.dtype == torch.uint8 else image.dtype
 
 
 def _convert_to_tensor(value, batch_size: int, dtype, device, name: str = "parameter") -> torch.Tensor:
@@ -171,9 +177,11 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
     n, c = image.shape[0], image.shape[1]
     if c == 1 and apply_bits & (_lib.APPLY_SATURATION | _lib.APPLY_GRAYSCALE):
         raise ValueError("saturation and grayscale need a 3-channel image")
-    out = torch.empty(n, c, height, width, dtype=image.dtype, device=image.device)
+    out = torch.empty(n, c, height, width, dtype=_work_dtype(image), device=image.device)
     if n == 0:
         return out
+    if image.dtype == torch.uint8 and (apply_bits & _lib.APPLY_CONTRAST) and contrast_mode == _lib.CONTRAST_MEAN:
+        raise ValueError('contrast_mode="torchvision" needs a float image (its mean pre-pass does not read bytes)')
     params = _lib.make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness,
                               contrast, saturation, gray, mean, std, contrast_mode)
     keep = None
@@ -199,12 +207,17 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     grayscale mean (torchvision's adjust_contrast) instead of 0.5; ``_flags`` lets the
     transform classes state which operations are on, which saves the device-to-host reads
     that deciding it from tensor values needs.
+
+    Extra: a ``torch.uint8`` image is read as ``value / 255`` (torchvision's ToTensor scaling)
+    inside the kernel and gives a float32 result equal, within float32 tolerance, to the call on
+    ``image.float() / 255`` - without that tensor ever existing, and with a quarter of the input
+    traffic.  The reference takes float images only.
     """
-    _validate_image_tensor(image, "image")
+    _validate_image_tensor(image, "image", allow_uint8=True)
     n, _, img_h, img_w = image.shape
     if height <= 0 or width <= 0:
         raise ValueError(f"Crop size must be positive, got height={height}, width={width}")
-    dev, dt = image.device, image.dtype
+    dev, dt = image.device, _work_dtype(image)
 
     brightness = _convert_to_tensor(brightness_factor, n, dt, dev, "brightness_factor")
     contrast = _convert_to_tensor(contrast_factor, n, dt, dev, "contrast_factor")
