@@ -297,6 +297,16 @@ def main():
         for _ in range(e2e_steps):
             aug.forward_host(host_in, out=host_out, device=dev)   # returns when host_out is complete
         ms_e2e = 1e3 * (time.perf_counter() - t0) / e2e_steps
+        # the same end-to-end call fed with bytes (extension: the kernel reads value / 255 itself)
+        host_u8 = torch.randint(0, 256, (N_IMG, 3, SRC, SRC), dtype=torch.uint8).pin_memory()
+        for _ in range(2):
+            aug.forward_host(host_u8, out=host_out, device=dev)
+        if barrier:
+            barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            aug.forward_host(host_u8, out=host_out, device=dev)
+        ms_e2e_u8 = 1e3 * (time.perf_counter() - t0) / e2e_steps
     clk = clocks.summary()
 
     def over_ranks(ms):
@@ -310,6 +320,7 @@ def main():
     other = "nearest" if args.interp == "bilinear" else "bilinear"
     ms_eager_o, ms_kernel_o, ms_step_o = (over_ranks(v) for v in result[other])
     ms_e2e = over_ranks(ms_e2e)
+    ms_e2e_u8 = over_ranks(ms_e2e_u8)
     if rank != 0:
         return
 
@@ -336,6 +347,10 @@ def main():
             "e2e": {"value": world * N_IMG / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": N_IMG * 3 * SRC * SRC * 4, "d2h_bytes_per_step": N_IMG * 3 * CROP * CROP * 4,
                     "api": "TritonFusedAugment.forward_host (pinned host in/out, pipelined slices)"},
+            "e2e_uint8_input": {"value": world * N_IMG / (ms_e2e_u8 * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e_u8,
+                                "h2d_bytes_per_step": N_IMG * 3 * SRC * SRC, "d2h_bytes_per_step": N_IMG * 3 * CROP * CROP * 4,
+                                "what": "not the reference's configuration: the same call with a uint8 host batch, "
+                                        "scaled by 1/255 inside the kernel"},
             "gpu_launches": 2 * args.steps,       # per step: inverse_matrix_kernel + affine_kernel (inside the graph)
             "clocks": clk}
     if world == 1:
