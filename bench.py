@@ -199,10 +199,11 @@ def kernel_only(aug, img, steps, warmup, barrier):
     matrix = None
     if aug.has_affine:
         matrix = F._prepare_affine_matrix_only(n, dev, src_h, src_w, angle, translate, scale, shear, None).contiguous()
-    out = torch.empty(n, 3, crop, crop, device=dev, dtype=img.dtype)
+    work = F._work_dtype(img)
+    out = torch.empty(n, 3, crop, crop, device=dev, dtype=work)
     p = _lib.make_params(img, out, top, left, flip, matrix, 0.0, aug.has_affine and F._is_bilinear(aug.interpolation), 31,
-                         b.to(img.dtype), c.to(img.dtype), s.to(img.dtype), g,
-                         F._rounded_triple(MEAN, img.dtype), F._rounded_triple(STD, img.dtype))
+                         b.to(work), c.to(work), s.to(work), g,
+                         F._rounded_triple(MEAN, work), F._rounded_triple(STD, work))
     return timed(lambda: _lib.launch_fused(p, dev), steps, warmup, barrier)
 
 
@@ -212,6 +213,7 @@ PROFILE_CONFIGS = {
     "c1": (32, 224, 224, torch.float32, False),          # colour + grayscale + normalize only
     "c2": (256, 224, 112, torch.float32, False),         # crop 112 + flip + colour + normalize
     "c3": (N_IMG, SRC, CROP, torch.float32, True),
+    "c3u8": (N_IMG, SRC, CROP, torch.uint8, True),       # C3 fed with bytes (scaled by 1/255 in the kernel), float32 out
     "c4": (512, 512, 448, torch.float16, True),          # fp16 affine + crop 448 + flip + colour + normalize
     "c5b": (4096, 224, 112, torch.float32, False),       # crop 112 + flip + colour + normalize, image batch
 }
@@ -225,12 +227,14 @@ def profile_case(config, images, interp):
     n = images or n
     torch.cuda.set_device(0)
     torch.manual_seed(1234)
-    img = torch.rand(n, 3, src, src, device="cuda:0").to(dtype)
+    img = (torch.randint(0, 256, (n, 3, src, src), device="cuda:0", dtype=torch.uint8) if dtype == torch.uint8
+           else torch.rand(n, 3, src, src, device="cuda:0").to(dtype))
     kw = dict(degrees=15, translate=(0.1, 0.1), scale=(0.9, 1.1), shear=5, interpolation=interp) if affine else {}
     aug = ta.TritonFusedAugment(crop_size=crop, horizontal_flip_p=0.5, brightness=0.2, contrast=0.2, saturation=0.2,
                                 grayscale_p=0.1, mean=MEAN, std=STD, **kw)
     ms = kernel_only(aug, img, 2, 1, None)
-    gbs = 2 * n * 3 * crop * crop * img.element_size() / (ms * 1e-3) / 1e9
+    out_bytes = 4 if dtype == torch.uint8 else img.element_size()
+    gbs = n * 3 * crop * crop * (img.element_size() + out_bytes) / (ms * 1e-3) / 1e9
     print(f"profile case {config}: {n} images, {interp if affine else 'no affine'}, {ms:.4f} ms per launch, "
           f"{gbs:.0f} GB/s algorithmic")
 

@@ -115,6 +115,20 @@ def test_functional_argument_errors_without_a_gpu():
             ta.TritonFusedAugment(crop_size=2)(img)       # class API uploads host tensors; needs CUDA
 
 
+def test_uint8_is_accepted_by_the_fused_entry_points_only():
+    """Bytes are an extension of fused_augment / TritonFusedAugment (result float32); the
+    stand-alone functionals keep the reference's float-only check (tested on the GPU, where
+    the dtype check is reached).  Host-side checks only."""
+    from triton_augment_b200 import functional as F
+    u8 = torch.zeros(2, 3, 8, 8, dtype=torch.uint8)
+    assert F._work_dtype(u8) == torch.float32 and F._work_dtype(u8.half()) == torch.float16
+    with pytest.raises(ValueError, match="CUDA"):
+        ta.fused_augment(u8, 0, 0, 4, 4)                  # the device check comes first, as in the reference
+    assert _lib.U8 == 2 and _lib.F32 == 0 and _lib.F16 == 1
+    header = open(os.path.join(ROOT, "include", "ta_b200.h")).read()
+    assert "TA_B200_F32 = 0, TA_B200_F16 = 1, TA_B200_U8 = 2" in header
+
+
 def test_inverse_matrix_matches_torchvision_and_golden(functional_golden):
     z = functional_golden
     t = lambda k: torch.from_numpy(z[k])
