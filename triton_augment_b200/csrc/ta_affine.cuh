@@ -51,13 +51,22 @@ constexpr float kInv255 = 1.0f / 255.0f;
 template <typename T, typename S> struct Px {
     static constexpr bool scaled = false;
     static __device__ __forceinline__ T from(S v) { return v; }
-    static __device__ __forceinline__ float raw_f(S v) { return Elem<T>::to_f(v); }    // blend operand
+    // two texels as blend operands
+    static __device__ __forceinline__ float2 raw_f2(S a, S b) { return make_float2(Elem<T>::to_f(a), Elem<T>::to_f(b)); }
     static __device__ __forceinline__ S lds(uint32_t addr) { return Elem<T>::lds(addr); }
 };
+// Bytes.  int -> float conversions run on the quarter-rate pipe; for 0..255 the float
+// 2^23 + b is the bit pattern 0x4B000000 | b, and both uses below stay exact: b * k as
+// fma(2^23 + b, k, -2^23 k) (2^23 k is exact, one rounding, the same value as float(b) * k),
+// the blend operand as (2^23 + b) - 2^23, two at once.
 template <> struct Px<float, uint8_t> {
     static constexpr bool scaled = true;        // blends run on the raw 0..255 values, scaled once afterwards
-    static __device__ __forceinline__ float from(uint8_t v) { return __fmul_rn((float)v, kInv255); }
-    static __device__ __forceinline__ float raw_f(uint8_t v) { return (float)v; }
+    static __device__ __forceinline__ float biased(uint8_t v) { return __uint_as_float(0x4B000000u | (uint32_t)v); }
+    static __device__ __forceinline__ float from(uint8_t v) { return __fmaf_rn(biased(v), kInv255, -8388608.0f * kInv255); }
+    static __device__ __forceinline__ float2 raw_f2(uint8_t a, uint8_t b)
+    {
+        return pk_add(make_float2(biased(a), biased(b)), make_float2(-8388608.0f, -8388608.0f));
+    }
     static __device__ __forceinline__ uint8_t lds(uint32_t addr)
     {
         uint32_t v;
@@ -65,6 +74,7 @@ template <> struct Px<float, uint8_t> {
         return (uint8_t)v;
     }
 };
+
 constexpr int kNumGroups = kMaxRows / kGroupRows;
 constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
 

@@ -114,10 +114,10 @@ template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSample
 #pragma unroll
             for (int c = 0; c < C; ++c) {
                 const uint32_t a0 = addr[0] + c * PLANEB, a1 = addr[1] + c * PLANEB;
-                float2 acc = pk_mul(f2(P::raw_f(P::lds(a0)), P::raw_f(P::lds(a1))), w00);
-                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ES)), P::raw_f(P::lds(a1 + ES))), w10, acc);
-                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ROWB)), P::raw_f(P::lds(a1 + ROWB))), w01, acc);
-                acc = pk_fma(f2(P::raw_f(P::lds(a0 + ROWB + ES)), P::raw_f(P::lds(a1 + ROWB + ES))), w11, acc);
+                float2 acc = pk_mul(P::raw_f2(P::lds(a0), P::lds(a1)), w00);
+                acc = pk_fma(P::raw_f2(P::lds(a0 + ES), P::lds(a1 + ES)), w10, acc);
+                acc = pk_fma(P::raw_f2(P::lds(a0 + ROWB), P::lds(a1 + ROWB)), w01, acc);
+                acc = pk_fma(P::raw_f2(P::lds(a0 + ROWB + ES), P::lds(a1 + ROWB + ES)), w11, acc);
                 if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
                 smp[0][c] = Elem<T>::from_f(acc.x);
                 smp[1][c] = Elem<T>::from_f(acc.y);
@@ -165,10 +165,10 @@ template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSample
 #pragma unroll
             for (int c = 0; c < C; ++c) {
                 const S *pl = stage + c * PLANE;
-                float2 acc = pk_mul(f2(P::raw_f(pl[i0[0]]), P::raw_f(pl[i0[1]])), w00);
-                acc = pk_fma(f2(P::raw_f(pl[i0[0] + 1]), P::raw_f(pl[i0[1] + 1])), w10, acc);
-                acc = pk_fma(f2(P::raw_f(pl[i1[0]]), P::raw_f(pl[i1[1]])), w01, acc);
-                acc = pk_fma(f2(P::raw_f(pl[i1[0] + 1]), P::raw_f(pl[i1[1] + 1])), w11, acc);
+                float2 acc = pk_mul(P::raw_f2(pl[i0[0]], pl[i0[1]]), w00);
+                acc = pk_fma(P::raw_f2(pl[i0[0] + 1], pl[i0[1] + 1]), w10, acc);
+                acc = pk_fma(P::raw_f2(pl[i1[0]], pl[i1[1]]), w01, acc);
+                acc = pk_fma(P::raw_f2(pl[i1[0] + 1], pl[i1[1] + 1]), w11, acc);
                 if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
                 smp[0][c] = Elem<T>::from_f(acc.x);
                 smp[1][c] = Elem<T>::from_f(acc.y);
