@@ -118,6 +118,27 @@ def test_staging_assertions_hold_for_bytes():
     assert violations == 0 and timeouts == 0 and staged > 50
 
 
+def test_bytes_single_channel_fill_and_large_rotation():
+    """One channel, a non-zero fill (border tiles are gathered, not staged) and rotations large
+    enough that some tiles need per-group windows or the gather fallback."""
+    import triton_augment_b200 as ta
+    dev = _dev()
+    g = torch.Generator().manual_seed(17)
+    n, h, w, oh, ow = 4, 176, 208, 150, 163
+    img = torch.randint(0, 256, (n, 1, h, w), generator=g, dtype=torch.uint8).to(dev)
+    angle = torch.tensor([40.0, -75.0, 10.0, 0.0], device=dev)
+    scale = torch.tensor([0.6, 1.4, 1.0, 2.0], device=dev)
+    top = torch.tensor([3.0, 0.0, 26.0, 11.0], device=dev)
+    left = torch.tensor([0.0, 45.0, 7.0, 20.0], device=dev)
+    flip = torch.tensor([True, False, True, False], device=dev)
+    bf = torch.tensor([0.9, 1.1, 1.2, 0.8], device=dev)
+    for interp in ("nearest", "bilinear"):
+        kw = dict(angle=angle, scale=scale, interpolation=interp, fill=0.5, brightness_factor=bf, contrast_factor=1.15)
+        got = ta.fused_augment(img, top, left, oh, ow, flip, **kw)
+        want = ta.fused_augment(img.float() * (1.0 / 255.0), top, left, oh, ow, flip, **kw)
+        assert float((got - want).abs().max()) <= TOL, interp
+
+
 def test_transform_class_and_host_path_take_bytes():
     import triton_augment_b200 as ta
     dev = _dev()
