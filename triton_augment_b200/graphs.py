@@ -7,7 +7,7 @@ in a quarter of a millisecond the host cannot issue them fast enough.  `GraphedT
 captures the whole call once and replays it with a single launch.  Every replay draws fresh
 parameters: PyTorch's CUDA generator advances its Philox offset per replay exactly as the
 eager calls would, so graphed and eager runs started from the same seed produce the same
-outputs (tests/test_gpu_api.py checks this).
+outputs (tests/test_gpu_crop_paths.py checks this).
 
 The price is the usual one of CUDA graphs: input and output live at fixed addresses.
 
