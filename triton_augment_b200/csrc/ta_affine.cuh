@@ -28,12 +28,17 @@
 
 namespace ta {
 
-// Launch shape, chosen by measurement on the 1280x1280 -> 1024x1024 workload: 16 consumer
-// warps on 64x32 tiles with a 3-deep ring ran the bilinear kernel in 334 us; 24 consumer
-// warps on 64x48 tiles leave room for only 2 stages and took 389 us (one tile of look-ahead
-// does not cover the copy latency).
-// (24 consumer warps on 64x24 tiles with 4 stages: 350 us.)
-constexpr int kConsumerWarps = 16;
+// Launch shape, chosen by measurement on the 1280x1280 -> 1024x1024 workload.  Two consumer
+// warps side by side per strip of four tile rows, so the tile height sets the warp count:
+//   64x32 tiles, 16 consumer warps, 3 stages: bilinear 283 us, nearest 262 us, and the light
+//                variants (no colour work, matrix-free) 258-265 us                     <- built
+//   64x40 tiles, 20 warps: bilinear 273 us, nearest 256 us, but the light variants 305-332 us,
+//                and a tile needs up to 64 source rows already at 15 degrees / scale 1.1, so
+//                larger rotations would leave the staged path
+//   64x36 tiles, 18 warps: 283 / 261 us; 64x28, 14 warps: 306 / 281 us
+//   64x48 tiles, 24 warps, 2 stages (what then fits): 389 us; 64x24, 24 warps, 4 stages: 350 us
+constexpr int kConsumerWarps = kTileH / 2;        // two warps side by side per strip of four tile rows
+static_assert(kTileH % 4 == 0, "a warp handles four rows");
 constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 
@@ -123,8 +128,8 @@ __device__ __forceinline__ unsigned long long global_ns()
 
 // Wait for a phase of an mbarrier for at most ~2 s, giving up early when another thread
 // of the CTA has already given up.  No sleep between polls: a failed poll already parks the
-// warp for a while (sleeping 256 ns on top of it changed nothing for heavy consumers and cost
-// 5-8 % with light ones, because the producer then reacts late to a released stage).
+// warp for a while; sleeping on top of it (tried for producers, 256 ns, and for consumers, 64 ns)
+// changed nothing for heavy consumers and cost up to 8 % with light ones.
 __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
 {
     if (mbar_try_wait(bar, parity)) return true;
