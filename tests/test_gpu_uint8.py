@@ -155,6 +155,14 @@ def test_transform_class_and_host_path_take_bytes():
     c = aug.forward_host(img.pin_memory(), device=dev)
     assert c.dtype == torch.float32 and not c.is_cuda
     assert torch.equal(c, a.cpu())
+    # the other classes that are one fused call take bytes as well
+    for t in (ta.TritonColorJitterNormalize(brightness=0.2, contrast=0.2, saturation=0.2, grayscale_p=0.3, mean=MEAN, std=STD),
+              ta.TritonRandomCropFlip(size=(100, 120), horizontal_flip_p=0.5)):
+        torch.manual_seed(8)
+        u = t(img.to(dev))
+        torch.manual_seed(8)
+        f = t(img.to(dev).float() * (1.0 / 255.0))
+        assert u.dtype == torch.float32 and float((u - f).abs().max()) <= TOL, type(t).__name__
     with pytest.raises(ValueError):
         ta.fused_augment(img.to(dev), 0, 0, 64, 64, contrast_factor=1.1, contrast_mode="torchvision")
     with pytest.raises(TypeError):

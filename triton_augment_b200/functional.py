@@ -211,7 +211,9 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     Extra: a ``torch.uint8`` image is read as ``value / 255`` (torchvision's ToTensor scaling)
     inside the kernel and gives a float32 result equal, within float32 tolerance, to the call on
     ``image.float() / 255`` - without that tensor ever existing, and with a quarter of the input
-    traffic.  The reference takes float images only.
+    traffic.  The reference takes float images only.  The classes that are one call of this
+    function (TritonFusedAugment, TritonColorJitterNormalize, TritonColorJitter,
+    TritonRandomCropFlip, ...) therefore take bytes too; the stand-alone functionals do not.
     """
     _validate_image_tensor(image, "image", allow_uint8=True)
     n, _, img_h, img_w = image.shape
