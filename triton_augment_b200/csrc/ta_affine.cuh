@@ -37,8 +37,13 @@ namespace ta {
 //                larger rotations would leave the staged path
 //   64x36 tiles, 18 warps: 283 / 261 us; 64x28, 14 warps: 306 / 281 us
 //   64x48 tiles, 24 warps, 2 stages (what then fits): 389 us; 64x24, 24 warps, 4 stages: 350 us
-constexpr int kConsumerWarps = kTileH / 2;        // two warps side by side per strip of four tile rows
-static_assert(kTileH % 4 == 0, "a warp handles four rows");
+//   64x28 tiles, 28 warps with one row pair per thread (64 registers): 322 / 289 us
+#ifndef TA_ROWS_PER_WARP
+#define TA_ROWS_PER_WARP 4
+#endif
+constexpr int kRowsPerWarp = TA_ROWS_PER_WARP;                 // a thread's pixels: this many rows of one column
+constexpr int kConsumerWarps = 2 * kTileH / kRowsPerWarp;      // two warps side by side per strip of rows
+static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are handled in pairs");
 constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 

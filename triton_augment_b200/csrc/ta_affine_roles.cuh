@@ -236,7 +236,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     using Info = TileInfo<T, C, F>;
     using Sampler = PairSampler<T, C, MODE, CHECK, S>;
     using Smem = AffineSmem<T, C, F, S>;
-    constexpr int ROWS_PER_WARP = kTileH / (kConsumerWarps / 2);     // 4
+    constexpr int ROWS_PER_WARP = kRowsPerWarp;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
