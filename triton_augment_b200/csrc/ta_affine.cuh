@@ -1,13 +1,17 @@
-// Fused inverse-affine + crop + flip + colour + normalize kernel (nearest / bilinear).
+// Fused inverse-affine + crop + flip + colour + normalize kernel (nearest / bilinear; MODE 0:
+// the same pipeline without a matrix).
 //
 // Persistent, warp-specialised, one CTA per SM.  The CTA walks output tiles of
 // kTileW x kTileH pixels (grid-stride).  PRODUCER warps (one per stage) work ahead of the
 // CONSUMER warps through a ring of kStages shared-memory stages:
 //
-//   producer  for each tile: work out which source rows the tile reads and, per group of 8
-//             rows, which columns (ta_footprint.h); issue one TMA tensor copy per (group,
-//             channel) into the stage, completing on the stage's "full" mbarrier; publish
-//             the tile's decoded parameters next to the pixels.
+//   producer  for each tile: map the tile's corners to the source (ta_footprint.h).  When
+//             their bounding box fits one window of columns - the usual case - plan one TMA
+//             tensor copy per channel (a box of all the tile's source rows); otherwise clip the
+//             footprint per group of 8 rows and plan one copy per (group, channel).  Write the
+//             tile's descriptor (decoded parameters, window origin) into a slot the consumers
+//             are not reading, wait for the stage to be released, issue the copies; they
+//             complete on the stage's "full" mbarrier.
 //   consumer  wait for "full", sample from shared memory (lanes run along x: conflict-free
 //             reads, every store a full 128-byte line), apply the colour tier in registers,
 //             store, then release the stage on its "empty" mbarrier.

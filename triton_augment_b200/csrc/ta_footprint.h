@@ -1,10 +1,11 @@
 // Source footprint of one output tile under flip -> crop offset -> inverse affine.
 //
-// The staged affine kernel copies, for every source row an output tile touches,
-// only the columns it touches, into shared memory.  This header computes those
-// rows and column ranges.  It is plain arithmetic shared by the device code and
-// by a host-side test hook, so the ranges can be checked on a CPU against a brute
-// force walk over the tile's pixels.
+// The staged affine kernel copies the source rows an output tile touches into shared
+// memory: one window of columns for all rows when the footprint's bounding box fits it,
+// otherwise a window per group of 8 rows that follows the footprint.  This header computes
+// the rows and the windows.  It is plain arithmetic shared by the device code and by a
+// host-side test hook, so the windows can be checked on a CPU against a brute force walk
+// over the tile's pixels.
 //
 // Geometry restated from triton_augment/kernels/geometric_kernel.py:386-415: an
 // output pixel (x, y) maps to x_img = (flip ? ow-1-x : x) + left, y_img = y + top,
