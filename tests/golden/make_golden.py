@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checked out, e.g.
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of triton-augment v0.3.0>
 
 The reference (yuhezhang-ai/triton-augment v0.3.0) only has GPU kernels, so the
 script executes its *unmodified* Python + Triton code on CPU tensors under
@@ -292,7 +292,7 @@ def class_cases(ta):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of an unmodified triton-augment v0.3.0 checkout")
     args = ap.parse_args()
     ta = load_reference(args.reference)
 
