@@ -26,7 +26,9 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
     Colour<T, C, F> col;
 
     // Tile number -> (image, tile row, tile column), then stepped by kStages * gridDim.x tiles per
-    // round with carries instead of divisions.
+    // round with carries instead of divisions.  Consecutive tile numbers are neighbours along x:
+    // the CTAs running at one time then read whole runs of image rows (DRAM page hits) and share
+    // the overlap of their boxes in L2; an order that interleaves images was 20-50 % slower.
     const int first = (int)blockIdx.x + p * (int)gridDim.x, step = kStages * (int)gridDim.x;
     int n = first / tiles_per_img, ty = (first % tiles_per_img) / k.tiles_x, tx = (first % tiles_per_img) % k.tiles_x;
     const int step_n = step / tiles_per_img, step_ty = (step % tiles_per_img) / k.tiles_x,
