@@ -9,7 +9,11 @@ parameters: PyTorch's CUDA generator advances its Philox offset per replay exact
 eager calls would, so graphed and eager runs started from the same seed produce the same
 outputs (tests/test_gpu_crop_paths.py checks this).
 
-The price is the usual one of CUDA graphs: input and output live at fixed addresses.
+The price is the usual one of CUDA graphs: input and output live at fixed addresses, and the
+captured call must not read device values on the host.  The transform classes never do (they
+know from their constructor arguments which operations are on); the functional entry points
+called with tensor-valued factors decide that from the values with one device-to-host read and
+therefore cannot be captured.
 
     aug = ta.TritonFusedAugment(...)
     g = ta.GraphedTransform(aug, batch)      # `batch` is the staging tensor the loader refills
