@@ -33,7 +33,7 @@ N_IMG, SRC, CROP = 64, 1280, 1024
 METRIC, UNIT = "fused-augment throughput, 1280x1280 -> 1024x1024 affine config", "images/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one full 64-image affine-kernel launch (single-pass
 # ncu capture with `--profile-case 64`, summarised under profiles/), divided by 64.
-NCU_TRAFFIC_PER_IMAGE = {"bilinear": (832554496 + 761709824) / 64, "nearest": (831804160 + 760206592) / 64}
+NCU_TRAFFIC_PER_IMAGE = {"bilinear": (832564992 + 761615616) / 64, "nearest": (832006400 + 759964928) / 64}
 
 
 def measured_peak_gbs():
