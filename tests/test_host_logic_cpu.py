@@ -153,6 +153,20 @@ def test_shard_bounds():
     assert p[0].tolist() == [2, 3, 4] and p[1] == 1.0 and p[2].shape == (3, 2)
 
 
+def test_missing_library_fails_loudly():
+    """No fallback: with the shared library gone, the first use raises instead of computing on
+    the CPU.  Run in a child process so that this process keeps its loaded library."""
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from triton_augment_b200 import _lib\n"
+            "try:\n    _lib.load()\nexcept Exception as e:\n    print('RAISED', type(e).__name__)\n"
+            "else:\n    print('LOADED')\n") % ROOT
+    env = dict(os.environ, TA_B200_LIB=os.path.join(ROOT, "no_such_dir", "libta_b200.so"))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300).stdout
+    assert "RAISED" in out and "LOADED" not in out, out
+
+
 def test_library_exports_every_declared_symbol():
     header = open(os.path.join(ROOT, "include", "ta_b200.h")).read()
     declared = set(re.findall(r"\b(ta_b200_[a-z_0-9]+)\s*\(", header))
