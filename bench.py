@@ -44,11 +44,11 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def make_transform(interp):
+def make_transform(interp, fast_rng=False):
     import triton_augment_b200 as ta
     return ta.TritonFusedAugment(crop_size=CROP, horizontal_flip_p=0.5, degrees=15, translate=(0.1, 0.1),
                                  scale=(0.9, 1.1), shear=5, interpolation=interp, brightness=0.2, contrast=0.2,
-                                 saturation=0.2, grayscale_p=0.1, mean=MEAN, std=STD)
+                                 saturation=0.2, grayscale_p=0.1, mean=MEAN, std=STD, fast_rng=fast_rng)
 
 
 class ClockSampler:
@@ -288,6 +288,12 @@ def main():
             ms_graph = timed(lambda: graphed(), args.steps, args.warmup, barrier)
             del graphed
             result[interp] = (ms_step, ms_kernel, ms_graph)
+        # opt-in sampler: all parameters of a step from one launch of the library (its own random stream)
+        fast = make_transform(args.interp, fast_rng=True)
+        ms_fast = timed(lambda: fast(img), args.steps, args.warmup, barrier)
+        graphed = ta.GraphedTransform(fast, img)
+        ms_fast_graph = timed(lambda: graphed(), args.steps, args.warmup, barrier)
+        del graphed
         # end to end: pinned host batch in, pinned host result out, copies inside the timed region
         host_in = torch.empty(N_IMG, 3, SRC, SRC, pin_memory=True).copy_(img)
         host_out = torch.empty(N_IMG, 3, CROP, CROP, pin_memory=True)
@@ -325,6 +331,7 @@ def main():
     ms_eager_o, ms_kernel_o, ms_step_o = (over_ranks(v) for v in result[other])
     ms_e2e = over_ranks(ms_e2e)
     ms_e2e_u8 = over_ranks(ms_e2e_u8)
+    ms_fast, ms_fast_graph = over_ranks(ms_fast), over_ranks(ms_fast_graph)
     if rank != 0:
         return
 
@@ -346,6 +353,10 @@ def main():
             "kernel_only_images_per_s": world * N_IMG / (ms_kernel * 1e-3),
             "eager": {"value": world * N_IMG / (ms_eager * 1e-3), "ms_per_step": ms_eager,
                       "what": "the same forward called directly (about 19 small launches per step issued from Python)"},
+            "fast_rng": {"value": world * N_IMG / (ms_fast_graph * 1e-3), "ms_per_step": ms_fast_graph,
+                         "eager_ms_per_step": ms_fast,
+                         "what": "fast_rng=True (not the reference's random stream): every parameter of the step from "
+                                 "one sampler launch of the library, then the fused kernel"},
             other: {"value": world * N_IMG / (ms_step_o * 1e-3), "ms_per_step": ms_step_o,
                     "eager_ms_per_step": ms_eager_o, "roofline": roof(ms_kernel_o, other)},
             "e2e": {"value": world * N_IMG / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,

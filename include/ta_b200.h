@@ -180,6 +180,44 @@ int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *a
                                   const float *shear, float *matrix, void *stream);
 
 /*
+ * All per-sample parameters of one TritonFusedAugment call in ONE launch: the random draws,
+ * their broadcast over video frames, and the inverse affine matrices.  Replaces, as an opt-in,
+ * the ~18 separate draws and elementwise operations of triton_augment/transforms.py:1431-1531
+ * and functional.py:1308-1397.  The distributions are the reference's (uniform ranges, integer
+ * crop offsets, Bernoulli masks); the random STREAM is not: values come from a Philox4x32-10
+ * generator of this library keyed by *seed (device memory) and the parameter-set index, so a
+ * seed does not reproduce the reference's parameters.  No counterpart in the reference.
+ *
+ * Sample i of `total` uses parameter set p(i): with frames == 1, p = same_on_batch ? 0 : i;
+ * with frames = T > 1 (sample i = frame i % T of video i / T),
+ * p = (same_on_batch ? 0 : i / T) * (same_on_frame ? 1 : T) + (same_on_frame ? 0 : i % T).
+ * Every output pointer may be NULL (not written).  Factors are written in `factor_dtype`
+ * (TA_B200_F32 or TA_B200_F16); a range with lo == hi is written as that constant.
+ */
+typedef struct ta_b200_sample_spec {
+    uint32_t struct_size;       /* sizeof(ta_b200_sample_spec) */
+    int32_t  total, frames;
+    int32_t  same_on_batch, same_on_frame;
+    int32_t  img_h, img_w;      /* input size: translation range and crop range */
+    int32_t  crop_h, crop_w;    /* 0, 0: no crop (top = left = 0) */
+    int32_t  factor_dtype;
+    float    degrees[2];        /* angle ~ U(degrees[0], degrees[1]) */
+    float    translate[2];      /* tx ~ U(-translate[0] * img_w, +...), ty likewise with img_h */
+    float    scale[2];          /* scale ~ U */
+    float    shear[4];          /* shear_x ~ U(shear[0], shear[1]), shear_y ~ U(shear[2], shear[3]) */
+    float    flip_p, grayscale_p;
+    float    brightness[2], contrast[2], saturation[2];
+    const uint64_t *seed;       /* device: 64-bit seed of this call */
+    float   *top, *left;        /* [total] */
+    uint8_t *flip, *gray;       /* [total] */
+    float   *matrix;            /* [total, 6] */
+    void    *brightness_out, *contrast_out, *saturation_out;   /* [total] factor_dtype */
+    float   *angle_out, *translate_out, *scale_out, *shear_out; /* [total], [total,2], [total], [total,2]: the draws behind matrix */
+} ta_b200_sample_spec;
+
+int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream);
+
+/*
  * Diagnostics.  ta_b200_debug_counters copies {tiles staged through shared memory,
  * tiles that took the direct-gather path, staging violations seen by a checked
  * build, barrier waits that ran out} accumulated on the current device since the

@@ -25,7 +25,7 @@ SYMBOLS = (
     "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
     "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
-    "ta_b200_debug_crop_path",
+    "ta_b200_debug_crop_path", "ta_b200_sample_params",
     "ta_b200_debug_tile_shape",
 )
 
@@ -41,6 +41,23 @@ class FusedParams(C.Structure):
         ("brightness", C.c_void_p), ("contrast", C.c_void_p), ("saturation", C.c_void_p), ("gray", C.c_void_p),
         ("mean", C.c_float * 3), ("std", C.c_float * 3),
         ("contrast_mode", C.c_int32), ("gray_mean", C.c_void_p),
+    ]
+
+
+class SampleSpec(C.Structure):
+    """ta_b200_sample_spec of include/ta_b200.h."""
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("total", C.c_int32), ("frames", C.c_int32),
+        ("same_on_batch", C.c_int32), ("same_on_frame", C.c_int32),
+        ("img_h", C.c_int32), ("img_w", C.c_int32), ("crop_h", C.c_int32), ("crop_w", C.c_int32),
+        ("factor_dtype", C.c_int32),
+        ("degrees", C.c_float * 2), ("translate", C.c_float * 2), ("scale", C.c_float * 2), ("shear", C.c_float * 4),
+        ("flip_p", C.c_float), ("grayscale_p", C.c_float),
+        ("brightness", C.c_float * 2), ("contrast", C.c_float * 2), ("saturation", C.c_float * 2),
+        ("seed", C.c_void_p), ("top", C.c_void_p), ("left", C.c_void_p), ("flip", C.c_void_p), ("gray", C.c_void_p),
+        ("matrix", C.c_void_p), ("brightness_out", C.c_void_p), ("contrast_out", C.c_void_p),
+        ("saturation_out", C.c_void_p), ("angle_out", C.c_void_p), ("translate_out", C.c_void_p),
+        ("scale_out", C.c_void_p), ("shear_out", C.c_void_p),
     ]
 
 
@@ -77,6 +94,8 @@ def load():
     lib.ta_b200_fused_augment_host.restype = C.c_int
     lib.ta_b200_inverse_affine_matrix.argtypes = [C.c_int32] + [C.c_void_p] * 7
     lib.ta_b200_inverse_affine_matrix.restype = C.c_int
+    lib.ta_b200_sample_params.argtypes = [C.POINTER(SampleSpec), C.c_void_p]
+    lib.ta_b200_sample_params.restype = C.c_int
     lib.ta_b200_debug_crop_path.argtypes = [C.c_int32]
     lib.ta_b200_debug_crop_path.restype = C.c_int
     lib.ta_b200_debug_counters.argtypes = [C.POINTER(C.c_uint64), C.c_int]
@@ -165,6 +184,13 @@ def inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.Tenso
         check(load().ta_b200_inverse_affine_matrix(n, *[_ptr(t) for t in args], _ptr(out), stream),
               "ta_b200_inverse_affine_matrix")
     return out
+
+
+def launch_sample_params(spec: SampleSpec, device: torch.device) -> None:
+    """Enqueue the fused parameter sampler on torch's current stream of ``device``."""
+    with torch.cuda.device(device):
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        check(load().ta_b200_sample_params(C.byref(spec), stream), "ta_b200_sample_params")
 
 
 def crop_path(path: int) -> None:

@@ -27,13 +27,21 @@ class TritonFusedAugment(T._BatchAware):
 
     ``contrast_mode="torchvision"`` (extra) uses torchvision's mean-based contrast instead
     of the reference's fast formula, at the cost of one more read of the source footprint.
+
+    ``fast_rng=True`` (extra, opt-in) replaces those ~18 separate draws and small elementwise
+    operations by one launch that samples every parameter, spreads it over video frames and
+    builds the affine matrices.  Same distributions; a different random stream (a Philox
+    generator of the library, seeded per call by one draw from torch's generator, so
+    ``torch.manual_seed`` still makes runs repeatable), hence not the reference's parameters
+    for a given seed.
     """
 
     def __init__(self, crop_size=None, horizontal_flip_p: float = 0.0, degrees=0, translate=None, scale=None,
                  shear=None, interpolation=InterpolationMode.NEAREST, fill: float = 0.0, brightness=0, contrast=0,
                  saturation=0, grayscale_p: float = 0.0, mean=None, std=None, same_on_batch: bool = False,
-                 same_on_frame: bool = True, contrast_mode: str = "fast"):
+                 same_on_frame: bool = True, contrast_mode: str = "fast", fast_rng: bool = False):
         super().__init__(same_on_batch, same_on_frame)
+        self.fast_rng = bool(fast_rng)
         if crop_size is None:
             self.crop_height = self.crop_width = None
         elif isinstance(crop_size, int):
@@ -108,8 +116,82 @@ class TritonFusedAugment(T._BatchAware):
             mean=self.color_helper.mean, std=self.color_helper.std, contrast_mode=self.contrast_mode,
             _flags=self.color_helper._colour_flags(affine=self.has_affine))
 
+    def _sample_fast(self, lay, work_dtype, want_draws: bool = False):
+        """Every per-sample parameter of one call from the library's sampler kernel: dict of
+        device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
+        (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
+        scale, shear``, the draws behind the matrix)."""
+        from . import _lib
+        dev = lay.image.device
+        h, w = lay.image.shape[2:]
+        total = lay.total
+        seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
+        words = 8 + 3 + (6 if want_draws else 0)                 # fp32 slots per sample: top, left, matrix(6), 3 factors, draws
+        buf = torch.empty(total * words * 4 + total * 2, dtype=torch.uint8, device=dev)
+        f32 = buf[: total * words * 4].view(torch.float32)
+        u8 = buf[total * words * 4:]
+        top, left, matrix = f32[:total], f32[total: 2 * total], f32[2 * total: 8 * total].view(total, 6)
+        factors = [f32[(8 + i) * total: (9 + i) * total] for i in range(3)]
+        if work_dtype == torch.float16:
+            factors = [f.view(torch.float16)[:total] for f in factors]
+        flip, gray = u8[:total], u8[total:]
+        ch = self.color_helper
+        sp = _lib.SampleSpec()
+        sp.struct_size = _lib.C.sizeof(_lib.SampleSpec)
+        sp.total, sp.frames = total, (lay.frames or 1)
+        sp.same_on_batch, sp.same_on_frame = int(self.same_on_batch), int(self.same_on_frame)
+        sp.img_h, sp.img_w = h, w
+        sp.crop_h, sp.crop_w = (self.crop_height or 0), (self.crop_width or 0)
+        sp.factor_dtype = _lib.F16 if work_dtype == torch.float16 else _lib.F32
+        ah = self.affine_helper if self.has_affine else None
+        sp.degrees[:] = ah.degrees if ah else (0.0, 0.0)
+        sp.translate[:] = ah.translate if ah and ah.translate is not None else (0.0, 0.0)
+        sp.scale[:] = ah.scale if ah and ah.scale is not None else (1.0, 1.0)
+        sp.shear[:] = ah.shear if ah and ah.shear is not None else (0.0, 0.0, 0.0, 0.0)
+        sp.flip_p, sp.grayscale_p = float(self.horizontal_flip_p), float(ch.grayscale_p)
+        sp.brightness[:] = ch.brightness or (1.0, 1.0)
+        sp.contrast[:] = ch.contrast or (1.0, 1.0)
+        sp.saturation[:] = ch.saturation or (1.0, 1.0)
+        sp.seed = seed.data_ptr()
+        sp.top, sp.left, sp.flip, sp.gray = top.data_ptr(), left.data_ptr(), flip.data_ptr(), gray.data_ptr()
+        sp.matrix = matrix.data_ptr() if self.has_affine else None
+        sp.brightness_out, sp.contrast_out, sp.saturation_out = (f.data_ptr() for f in factors)
+        out = dict(top=top, left=left, flip=flip, gray=gray, matrix=matrix if self.has_affine else None,
+                   brightness=factors[0], contrast=factors[1], saturation=factors[2])
+        if want_draws:
+            d = f32[11 * total:]
+            out.update(angle=d[:total], translate=d[total: 3 * total].view(total, 2), scale=d[3 * total: 4 * total],
+                       shear=d[4 * total: 6 * total].view(total, 2))
+            sp.angle_out, sp.translate_out = out["angle"].data_ptr(), out["translate"].data_ptr()
+            sp.scale_out, sp.shear_out = out["scale"].data_ptr(), out["shear"].data_ptr()
+        _lib.launch_sample_params(sp, dev)
+        return out
+
+    def _forward_fast(self, lay):
+        from . import _lib
+        img = lay.image
+        h, w = img.shape[2:]
+        if self.crop_height is not None and (self.crop_height > h or self.crop_width > w):
+            raise ValueError(f"Crop size ({self.crop_height}, {self.crop_width}) is larger than the image ({h}, {w})")
+        work = F._work_dtype(img)
+        p = self._sample_fast(lay, work)
+        flags = self.color_helper._colour_flags(affine=self.has_affine)
+        mean, std = self.color_helper.mean, self.color_helper.std
+        bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
+                | (_lib.APPLY_SATURATION if flags["saturation"] else 0) | (_lib.APPLY_GRAYSCALE if flags["grayscale"] else 0)
+                | (_lib.APPLY_NORMALIZE if mean is not None else 0))
+        return F._run_fused(img, self.crop_height if self.crop_height is not None else h,
+                            self.crop_width if self.crop_width is not None else w, p["top"], p["left"], p["flip"], p["matrix"],
+                            self.has_affine and F._is_bilinear(self.interpolation), self.fill if self.has_affine else 0.0,
+                            p["brightness"], p["contrast"], p["saturation"], p["gray"],
+                            F._rounded_triple(mean, work) if mean is not None else None,
+                            F._rounded_triple(std, work) if std is not None else None, bits,
+                            F._contrast_mode(self.contrast_mode))
+
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         lay = self._layout(image)
+        if self.fast_rng:
+            return lay.restore(self._forward_fast(lay))
         h, w = lay.image.shape[2:]
         # (Drawing the parameters on a side stream so that they overlap the previous call's
         # kernel was tried and measured slower: 0.66 ms instead of 0.41 ms per 64-image call.)

@@ -166,33 +166,96 @@ static int gray_mean_on(const ta_b200_fused_params *p, float *mean_out, void *sc
 }
 
 // ----------------------------------------------------------------------------- inverse affine matrices
-// One thread per image; every operation individually rounded, in the order of
-// triton_augment/functional.py:853-890 (which runs each line as its own elementwise op).
-__global__ void inverse_matrix_kernel(int n, const float *center, const float *angle, const float *translate,
-                                      const float *scale, const float *shear, float *matrix)
+// Every operation individually rounded, in the order of triton_augment/functional.py:853-890
+// (which runs each line as its own elementwise op).
+__device__ __forceinline__ void inverse_matrix_of(float angle, float tx, float ty, float sc, float shear_x, float shear_y,
+                                                  float cx, float cy, float *m)
 {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
     const float d2r = (float)(3.141592653589793 / 180.0);
-    const float rot = __fmul_rn(angle[i], d2r);
-    const float sx = __fmul_rn(shear[2 * i], d2r), sy = __fmul_rn(shear[2 * i + 1], d2r);
-    const float cx = center ? center[2 * i] : 0.0f, cy = center ? center[2 * i + 1] : 0.0f;
-    const float tx = translate[2 * i], ty = translate[2 * i + 1];
+    const float rot = __fmul_rn(angle, d2r);
+    const float sx = __fmul_rn(shear_x, d2r), sy = __fmul_rn(shear_y, d2r);
     const float cos_sy = cosf(sy);
     const float rms = __fsub_rn(rot, sy);
     const float a = __fdiv_rn(cosf(rms), cos_sy);
     const float b = __fsub_rn(__fdiv_rn(__fmul_rn(-cosf(rms), tanf(sx)), cos_sy), sinf(rot));
     const float c = __fdiv_rn(sinf(rms), cos_sy);
     const float d = __fadd_rn(__fdiv_rn(__fmul_rn(-sinf(rms), tanf(sx)), cos_sy), cosf(rot));
-    const float sc = scale[i];
     const float m0 = __fdiv_rn(d, sc), m1 = __fdiv_rn(-b, sc), m3 = __fdiv_rn(-c, sc), m4 = __fdiv_rn(a, sc);
     const float ux = __fsub_rn(-cx, tx), uy = __fsub_rn(-cy, ty);
     float m2 = __fadd_rn(__fmul_rn(m0, ux), __fmul_rn(m1, uy));
     float m5 = __fadd_rn(__fmul_rn(m3, ux), __fmul_rn(m4, uy));
     m2 = __fadd_rn(m2, cx);
     m5 = __fadd_rn(m5, cy);
-    float *m = matrix + 6 * (size_t)i;
     m[0] = m0; m[1] = m1; m[2] = m2; m[3] = m3; m[4] = m4; m[5] = m5;
+}
+
+// One thread per image.
+__global__ void inverse_matrix_kernel(int n, const float *center, const float *angle, const float *translate,
+                                      const float *scale, const float *shear, float *matrix)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    inverse_matrix_of(angle[i], translate[2 * i], translate[2 * i + 1], scale[i], shear[2 * i], shear[2 * i + 1],
+                      center ? center[2 * i] : 0.0f, center ? center[2 * i + 1] : 0.0f, matrix + 6 * (size_t)i);
+}
+
+// ----------------------------------------------------------------------------- fused parameter sampler
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11): a
+// counter-based generator, so the parameter set p of a call is a pure function of (seed, p)
+// and samples that share a parameter set simply compute it again.
+__device__ __forceinline__ uint4 philox4x32_10(uint2 key, uint4 ctr)
+{
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+        ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+        key.x += 0x9E3779B9u;
+        key.y += 0xBB67AE85u;
+    }
+    return ctr;
+}
+
+__device__ __forceinline__ float unit_float(uint32_t bits) { return (float)(bits >> 8) * (1.0f / 16777216.0f); }   // [0, 1)
+__device__ __forceinline__ float uniform_in(uint32_t bits, const float (&r)[2]) { return r[0] == r[1] ? r[0] : r[0] + unit_float(bits) * (r[1] - r[0]); }
+
+template <typename FT>
+__global__ void sample_params_kernel(const __grid_constant__ ta_b200_sample_spec s)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= s.total) return;
+    int p;
+    if (s.frames <= 1) p = s.same_on_batch ? 0 : i;
+    else p = (s.same_on_batch ? 0 : i / s.frames) * (s.same_on_frame ? 1 : s.frames) + (s.same_on_frame ? 0 : i % s.frames);
+    const uint64_t seed = *s.seed;
+    const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+    uint32_t u[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 v = philox4x32_10(key, make_uint4((uint32_t)p, 0u, (uint32_t)j, 0x7461b200u));
+        u[4 * j] = v.x; u[4 * j + 1] = v.y; u[4 * j + 2] = v.z; u[4 * j + 3] = v.w;
+    }
+    const float angle = uniform_in(u[0], s.degrees);
+    const float tr_x[2] = {-s.translate[0] * (float)s.img_w, s.translate[0] * (float)s.img_w};
+    const float tr_y[2] = {-s.translate[1] * (float)s.img_h, s.translate[1] * (float)s.img_h};
+    const float tx = uniform_in(u[1], tr_x), ty = uniform_in(u[2], tr_y);
+    const float sc = uniform_in(u[3], s.scale);
+    const float sh_x[2] = {s.shear[0], s.shear[1]}, sh_y[2] = {s.shear[2], s.shear[3]};
+    const float shx = uniform_in(u[4], sh_x), shy = uniform_in(u[5], sh_y);
+    if (s.matrix) inverse_matrix_of(angle, tx, ty, sc, shx, shy, 0.0f, 0.0f, s.matrix + 6 * (size_t)i);
+    if (s.angle_out) s.angle_out[i] = angle;
+    if (s.translate_out) { s.translate_out[2 * i] = tx; s.translate_out[2 * i + 1] = ty; }
+    if (s.scale_out) s.scale_out[i] = sc;
+    if (s.shear_out) { s.shear_out[2 * i] = shx; s.shear_out[2 * i + 1] = shy; }
+    // crop offsets: integers in [0, size - crop], as floats (what the fused kernel takes)
+    const int span_y = s.crop_h > 0 ? s.img_h - s.crop_h + 1 : 1, span_x = s.crop_w > 0 ? s.img_w - s.crop_w + 1 : 1;
+    if (s.top) s.top[i] = (float)min((int)(unit_float(u[6]) * (float)span_y), span_y - 1);
+    if (s.left) s.left[i] = (float)min((int)(unit_float(u[7]) * (float)span_x), span_x - 1);
+    if (s.flip) s.flip[i] = unit_float(u[8]) < s.flip_p ? 1 : 0;
+    if (s.brightness_out) ((FT *)s.brightness_out)[i] = (FT)uniform_in(u[9], s.brightness);
+    if (s.contrast_out) ((FT *)s.contrast_out)[i] = (FT)uniform_in(u[10], s.contrast);
+    if (s.saturation_out) ((FT *)s.saturation_out)[i] = (FT)uniform_in(u[11], s.saturation);
+    if (s.gray) s.gray[i] = unit_float(u[12]) < s.grayscale_p ? 1 : 0;
 }
 
 }  // namespace ta

@@ -193,6 +193,28 @@ int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *a
     return TA_B200_OK;
 }
 
+int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream)
+{
+    if (!spec) return ta::fail(TA_B200_ERR_NULL, "spec is NULL");
+    if (spec->struct_size != sizeof(ta_b200_sample_spec))
+        return ta::fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", spec->struct_size, sizeof(ta_b200_sample_spec));
+    if (spec->total < 0 || spec->frames < 1 || spec->total % spec->frames != 0)
+        return ta::fail(TA_B200_ERR_SHAPE, "total = %d, frames = %d", spec->total, spec->frames);
+    if (spec->img_h <= 0 || spec->img_w <= 0 || spec->crop_h < 0 || spec->crop_w < 0 || spec->crop_h > spec->img_h ||
+        spec->crop_w > spec->img_w)
+        return ta::fail(TA_B200_ERR_SHAPE, "image %dx%d, crop %dx%d", spec->img_h, spec->img_w, spec->crop_h, spec->crop_w);
+    if (spec->factor_dtype != TA_B200_F32 && spec->factor_dtype != TA_B200_F16)
+        return ta::fail(TA_B200_ERR_DTYPE, "factor_dtype %d", spec->factor_dtype);
+    if (!spec->seed) return ta::fail(TA_B200_ERR_NULL, "seed is NULL");
+    if (spec->total == 0) return TA_B200_OK;
+    const int threads = 128, blocks = (spec->total + threads - 1) / threads;
+    if (spec->factor_dtype == TA_B200_F32) ta::sample_params_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(*spec);
+    else ta::sample_params_kernel<__half><<<blocks, threads, 0, (cudaStream_t)stream>>>(*spec);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return ta::cuda_fail(e, "launch(sample_params)");
+    return TA_B200_OK;
+}
+
 int ta_b200_debug_counters(uint64_t out[4], int reset)
 {
     ta::DeviceState *s = nullptr;
