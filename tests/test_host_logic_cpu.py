@@ -176,3 +176,4 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
     assert _lib.load().ta_b200_abi_version() == _lib.ABI_VERSION
     assert ctypes.sizeof(_lib.FusedParams) == 168       # sizeof(ta_b200_fused_params) on LP64
+    assert ctypes.sizeof(_lib.SampleSpec) == 216        # sizeof(ta_b200_sample_spec) on LP64
