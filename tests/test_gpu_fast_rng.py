@@ -108,3 +108,11 @@ def test_no_affine_no_crop_video_and_graph_capture():
     assert torch.equal(a, c) and not torch.equal(a, b)
     with pytest.raises(ValueError):
         ta.TritonFusedAugment(crop_size=64, fast_rng=True)(torch.rand(1, 3, 32, 48, device=DEV))
+    # the host-buffer entry samples the same way
+    full = _aug(ta)
+    host = torch.rand(5, 3, 64, 80).pin_memory()
+    torch.manual_seed(21)
+    want = full(host.to(DEV))
+    torch.manual_seed(21)
+    got = full.forward_host(host, device=DEV)
+    assert torch.equal(got, want.cpu())

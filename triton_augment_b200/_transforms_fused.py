@@ -116,13 +116,13 @@ class TritonFusedAugment(T._BatchAware):
             mean=self.color_helper.mean, std=self.color_helper.std, contrast_mode=self.contrast_mode,
             _flags=self.color_helper._colour_flags(affine=self.has_affine))
 
-    def _sample_fast(self, lay, work_dtype, want_draws: bool = False):
+    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None):
         """Every per-sample parameter of one call from the library's sampler kernel: dict of
         device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
         (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
         scale, shear``, the draws behind the matrix)."""
         from . import _lib
-        dev = lay.image.device
+        dev = lay.image.device if device is None else torch.device(device)     # host batches: where to sample
         h, w = lay.image.shape[2:]
         total = lay.total
         seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
@@ -219,11 +219,17 @@ class TritonFusedAugment(T._BatchAware):
         n, c, h, w = flat.shape
         oh = self.crop_height if self.crop_height is not None else h
         ow = self.crop_width if self.crop_width is not None else w
-        params = self._spread_all(lay, self._get_params(lay.count, dev, (h, w)))
-        angle, translate, scale, shear, top, left, flip, b, cf, s, g = params
         matrix = None
-        if self.has_affine:
-            matrix = F_._prepare_affine_matrix_only(n, dev, h, w, angle, translate, scale, shear, None).cpu().contiguous()
+        if self.fast_rng:
+            fp = self._sample_fast(lay, work, device=dev)
+            top, left, flip, b, cf, s, g = (fp[k] for k in ("top", "left", "flip", "brightness", "contrast", "saturation", "gray"))
+            if self.has_affine:
+                matrix = fp["matrix"].cpu().contiguous()
+        else:
+            params = self._spread_all(lay, self._get_params(lay.count, dev, (h, w)))
+            angle, translate, scale, shear, top, left, flip, b, cf, s, g = params
+            if self.has_affine:
+                matrix = F_._prepare_affine_matrix_only(n, dev, h, w, angle, translate, scale, shear, None).cpu().contiguous()
         flags = self.color_helper._colour_flags(affine=self.has_affine)
         mean, std = self.color_helper.mean, self.color_helper.std
         bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
