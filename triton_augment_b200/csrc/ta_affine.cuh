@@ -155,9 +155,21 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
 }
 
 // Gather rows [y_first, y_first + y_count) of one tile column from global memory (no staging).
-template <typename T, int C, int MODE, unsigned F, bool MIX, typename S>
+// Value the grayscale-mean pre-pass sums for one pixel: gray(clamp(brightness * sample)), the
+// image torchvision's contrast blends towards (fp32 images only).
+template <int C, unsigned F>
+__device__ __forceinline__ float mean_term(const Colour<float, C, F> &col, const float (&s)[C])
+{
+    float v[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) v[c] = (F & kB) ? __saturatef(s[c] * col.bf) : s[c];
+    return C == 3 ? gray_of(v[0], v[C > 1 ? 1 : 0], v[C - 1]) : v[0];
+}
+
+// REDUCE: add mean_term() of every pixel to *acc instead of applying the colour tier and storing.
+template <typename T, int C, int MODE, unsigned F, bool MIX, typename S, bool REDUCE = false>
 __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g, const Colour<T, C, F> &col,
-                                                   int n, int x, int y_first, int y_count)
+                                                   int n, int x, int y_first, int y_count, float *acc = nullptr)
 {
     if (x >= k.ow) return;
     const S *img = (const S *)k.in + (size_t)n * C * k.h * k.w;
@@ -198,10 +210,14 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
                                               dx, dy));
             }
         }
-        float v[C];
-        col.apply(k, s, v);
+        if constexpr (REDUCE) {
+            *acc += mean_term<C, F>(col, s);
+        } else {
+            float v[C];
+            col.apply(k, s, v);
 #pragma unroll
-        for (int c = 0; c < C; ++c) Elem<T>::store(out + c * oplane + (size_t)y * k.ow + x, v[c]);
+            for (int c = 0; c < C; ++c) Elem<T>::store(out + c * oplane + (size_t)y * k.ow + x, v[c]);
+        }
     }
 }
 

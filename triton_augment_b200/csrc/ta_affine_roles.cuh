@@ -229,7 +229,7 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
     }
 }
 
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S>
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S, bool REDUCE>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
                                                 volatile int *abort_flag)
 {
@@ -264,9 +264,10 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         }
         const int x = h0.y + wx * 32 + lane;
         const int y_first = h0.z + wy * ROWS_PER_WARP;
+        float mean_acc = 0.0f;               // REDUCE: this lane's share of the tile's sum
 
         if (rows == 0) {
-            affine_rows_direct<T, C, MODE, F, MIX, S>(k, g, col, n, x, y_first, ROWS_PER_WARP);
+            affine_rows_direct<T, C, MODE, F, MIX, S, REDUCE>(k, g, col, n, x, y_first, ROWS_PER_WARP, &mean_acc);
         } else if (x < k.ow) {
             T *plane[C];
             plane[0] = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
@@ -309,10 +310,22 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 T smp[2][C];
                 if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                 else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                finish_pair<T, C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
+                if constexpr (REDUCE) {
+                    if (a_ok) mean_acc += mean_term<C, F>(col, smp[0]);
+                    if (b_ok) mean_acc += mean_term<C, F>(col, smp[1]);
+                } else {
+                    finish_pair<T, C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
+                }
             }
         }
         __syncwarp();
+        if constexpr (REDUCE) {
+            // one partial per (tile, warp), lanes added in a fixed order: the mean does not
+            // depend on which CTA ran the tile or when
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mean_acc += __shfl_xor_sync(0xffffffffu, mean_acc, o);
+            if (lane == 0) k.mean_partials[(size_t)tile * kConsumerWarps + warp] = mean_acc;
+        }
         if (lane == 0) mbar_arrive(&empty[s]);
     }
     if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
@@ -320,7 +333,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 
 // ----------------------------------------------------------------------------- kernel
 // MIX: the variant of a swapped bilinear kernel (CoordRecipe) that applies late_x() per pixel.
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T>
+// REDUCE: the grayscale-mean pre-pass on the same machinery (no colour tier, no image output).
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T, bool REDUCE = false>
 __global__ void __launch_bounds__(kAffineThreads, 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
@@ -344,7 +358,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     if ((threadIdx.x >> 5) >= kConsumerWarps)
         affine_producer<T, C, MODE, F, S>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
     else
-        affine_consumer<T, C, MODE, F, CHECK, MIX, S>(k, smem, full, empty, &abort_flag);
+        affine_consumer<T, C, MODE, F, CHECK, MIX, S, REDUCE>(k, smem, full, empty, &abort_flag);
 
     // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
     // memory: give each stage one more bounded chance to settle before the memory is released.

@@ -37,7 +37,7 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 6, kNumDtypes = 3;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
+constexpr int kNumKinds = 7, kNumDtypes = 3;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,

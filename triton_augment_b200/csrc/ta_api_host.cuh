@@ -106,8 +106,10 @@ static int fused_host(const ta_b200_fused_params *hp)
     TA_CU(up(hp->gray, o_g, n), "upload gray");
     if (need_mean && hp->gray_mean) TA_CU(up(hp->gray_mean, o_gm, n * 4), "upload gray_mean");
     if (need_mean && !hp->gray_mean) {
-        const size_t need = mean_partials_offset(slice) + (size_t)slice * mean_blocks_per_image(hp->oh, hp->ow) * 4;
-        TA_CU(grow(&P.d_scratch, &P.scratch_cap, need), "cudaMalloc(scratch)");
+        ta_b200_fused_params one = *hp;          // a slice: device input at a 256-byte aligned address
+        one.n = slice;
+        one.in = P.d_in[0];
+        TA_CU(grow(&P.d_scratch, &P.scratch_cap, mean_scratch_need(&one)), "cudaMalloc(scratch)");
     }
 
     const int slices = (hp->n + slice - 1) / slice;
@@ -169,7 +171,7 @@ int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream)
 size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p)
 {
     if (!p || p->n <= 0 || p->oh <= 0 || p->ow <= 0) return 256;
-    return ta::mean_partials_offset(p->n) + (size_t)p->n * ta::mean_blocks_per_image(p->oh, p->ow) * sizeof(float);
+    return ta::mean_scratch_need(p);
 }
 
 int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,

@@ -30,6 +30,7 @@ struct KArgs {
     const void *bf, *cf, *sf;
     const uint8_t *gray;
     const float *gray_mean;
+    float *mean_partials;              // staged grayscale-mean pre-pass: [num_tiles][consumer warps] sums
     unsigned long long *counters;
     int n, h, w, oh, ow;
     int tiles_x, tiles_y, num_tiles;

@@ -83,6 +83,16 @@ template <typename T, int KIND, typename S = T> const KernelTable &make_table()
     return t;
 }
 
+// Staged grayscale-mean pre-pass (fp32): mode 0 no matrix / 1 nearest / 2 bilinear, with or
+// without brightness, 3 or 1 channels.  Defined in ta_inst_f32_mean.cu.
+KernelEntry mean_kernel_entry(int mode, bool bright, int channels);
+
+template <int C, int MODE, unsigned F> KernelEntry mean_entry()
+{
+    return KernelEntry{(const void *)&affine_kernel<float, C, MODE, F, false, false, float, true>,
+                       AffineSmem<float, C, F, float>::total, kAffineThreads};
+}
+
 // Defined one per translation unit (ta_inst_*.cu).
 const KernelTable &table_f32_direct();
 const KernelTable &table_f32_crop_staged();
