@@ -122,7 +122,9 @@ int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream);
  * its bit is set).  Writes mean_out[n] (device, fp32 holding image-dtype-rounded
  * values).  `scratch` is device memory of at least ta_b200_gray_mean_scratch_bytes(p)
  * bytes, 256-byte aligned; it needs no initialisation and may be reused by the next
- * call on the same stream.
+ * call on the same stream.  (That size includes room for the faster of the two kernels that
+ * implement the pass; with less, but at least round_up(4 n, 256) + 4 n min(128, ceil(oh ow /
+ * 4096)) bytes, the slower one runs.  Both are deterministic; they differ in the last bits.)
  * Replaces: rgb_to_grayscale + torch.mean + cast, triton_augment/functional.py:366-376.
  */
 int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out,
