@@ -187,8 +187,9 @@ def run_reference_arm(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def kernel_only(aug, img, steps, warmup, barrier):
-    """The fused kernel alone (parameters drawn once, then fixed): ms per launch, CUDA events."""
+def kernel_only(aug, img, steps, warmup, barrier, exact_contrast=False):
+    """The fused kernel alone (parameters drawn once, then fixed): ms per launch, CUDA events.
+    ``exact_contrast``: the grayscale-mean pre-pass + the fused kernel in mean-contrast mode."""
     from triton_augment_b200 import _lib, functional as F
     from triton_augment_b200.transforms import _Layout
     dev = img.device
@@ -205,7 +206,15 @@ def kernel_only(aug, img, steps, warmup, barrier):
     p = _lib.make_params(img, out, top, left, flip, matrix, 0.0, aug.has_affine and F._is_bilinear(aug.interpolation), 31,
                          b.to(work), c.to(work), s.to(work), g,
                          F._rounded_triple(MEAN, work), F._rounded_triple(STD, work))
-    return timed(lambda: _lib.launch_fused(p, dev), steps, warmup, barrier)
+    if not exact_contrast:
+        return timed(lambda: _lib.launch_fused(p, dev), steps, warmup, barrier)
+    p.contrast_mode = _lib.CONTRAST_MEAN
+
+    def both():
+        means = _lib.launch_gray_mean(p, dev)
+        p.gray_mean = means.data_ptr()
+        _lib.launch_fused(p, dev)
+    return timed(both, steps, warmup, barrier)
 
 
 # Other configurations of the reference's benchmark list, for profiler captures (--profile-config):
@@ -214,6 +223,7 @@ PROFILE_CONFIGS = {
     "c1": (32, 224, 224, torch.float32, False),          # colour + grayscale + normalize only
     "c2": (256, 224, 112, torch.float32, False),         # crop 112 + flip + colour + normalize
     "c3": (N_IMG, SRC, CROP, torch.float32, True),
+    "c3exact": (N_IMG, SRC, CROP, torch.float32, True),  # C3 with torchvision-exact contrast: mean pre-pass + fused kernel
     "c3u8": (N_IMG, SRC, CROP, torch.uint8, True),       # C3 fed with bytes (scaled by 1/255 in the kernel), float32 out
     "c4": (512, 512, 448, torch.float16, True),          # fp16 affine + crop 448 + flip + colour + normalize
     "c5b": (4096, 224, 112, torch.float32, False),       # crop 112 + flip + colour + normalize, image batch
@@ -233,9 +243,10 @@ def profile_case(config, images, interp):
     kw = dict(degrees=15, translate=(0.1, 0.1), scale=(0.9, 1.1), shear=5, interpolation=interp) if affine else {}
     aug = ta.TritonFusedAugment(crop_size=crop, horizontal_flip_p=0.5, brightness=0.2, contrast=0.2, saturation=0.2,
                                 grayscale_p=0.1, mean=MEAN, std=STD, **kw)
-    ms = kernel_only(aug, img, 2, 1, None)
+    exact = config == "c3exact"
+    ms = kernel_only(aug, img, 2, 1, None, exact_contrast=exact)
     out_bytes = 4 if dtype == torch.uint8 else img.element_size()
-    gbs = n * 3 * crop * crop * (img.element_size() + out_bytes) / (ms * 1e-3) / 1e9
+    gbs = n * 3 * crop * crop * (img.element_size() * (2 if exact else 1) + out_bytes) / (ms * 1e-3) / 1e9
     print(f"profile case {config}: {n} images, {interp if affine else 'no affine'}, {ms:.4f} ms per launch, "
           f"{gbs:.0f} GB/s algorithmic")
 
