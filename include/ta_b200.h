@@ -43,8 +43,8 @@ typedef enum ta_b200_status {
 /* TA_B200_U8: `in` holds bytes, `out` and the factor vectors are float32; a byte b enters the
  * pipeline as b / 255 (torchvision's ToTensor scaling), so the result equals the float32 call on
  * in.float() / 255 within the float32 tolerance.  No counterpart in the reference, which takes
- * float tensors only; it saves three quarters of the input traffic.  Not available with
- * TA_B200_CONTRAST_MEAN. */
+ * float tensors only; it saves three quarters of the input traffic.  Its grayscale-mean
+ * pre-pass (TA_B200_CONTRAST_MEAN) needs rows of whole 16-byte units. */
 enum { TA_B200_F32 = 0, TA_B200_F16 = 1, TA_B200_U8 = 2 };
 enum { TA_B200_NEAREST = 0, TA_B200_BILINEAR = 1 };
 enum { TA_B200_CONTRAST_FAST = 0, TA_B200_CONTRAST_MEAN = 1 };

@@ -163,7 +163,14 @@ def test_transform_class_and_host_path_take_bytes():
         torch.manual_seed(8)
         f = t(img.to(dev).float() * (1.0 / 255.0))
         assert u.dtype == torch.float32 and float((u - f).abs().max()) <= TOL, type(t).__name__
-    with pytest.raises(ValueError):
-        ta.fused_augment(img.to(dev), 0, 0, 64, 64, contrast_factor=1.1, contrast_mode="torchvision")
+    # torchvision-exact contrast: its mean pre-pass reads bytes through the staged kernel
+    kw = dict(brightness_factor=1.1, contrast_factor=torch.tensor([0.7, 1.3, 1.1, 0.9, 1.2, 0.8], device=dev),
+              contrast_mode="torchvision", angle=7.0, interpolation="bilinear")
+    u = ta.fused_augment(img.to(dev), 3, 5, 100, 120, **kw)
+    f = ta.fused_augment(img.to(dev).float() * (1.0 / 255.0), 3, 5, 100, 120, **kw)
+    assert float((u - f).abs().max()) <= TOL
+    odd = torch.randint(0, 256, (2, 3, 50, 70), dtype=torch.uint8, device=dev)      # rows of 70 bytes cannot be staged
+    with pytest.raises(Exception, match="16-byte"):
+        ta.fused_augment(odd, 0, 0, 40, 40, contrast_factor=1.1, contrast_mode="torchvision")
     with pytest.raises(TypeError):
         ta.functional.crop(img.to(dev), 0, 0, 64, 64)      # the stand-alone functionals stay float-only

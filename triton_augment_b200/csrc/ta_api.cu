@@ -131,8 +131,6 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
                     sizeof(ta_b200_fused_params));
     if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16 && p->dtype != TA_B200_U8)
         return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
-    if (p->dtype == TA_B200_U8 && (for_mean || ((p->apply & TA_B200_APPLY_CONTRAST) && p->contrast_mode == TA_B200_CONTRAST_MEAN)))
-        return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale-mean pre-pass and CONTRAST_MEAN take float images, not uint8");
     if (p->c != 1 && p->c != 3)
         return fail(TA_B200_ERR_SHAPE, "channels must be 1 or 3, got %d", p->c);
     if (p->n < 0 || p->h <= 0 || p->w <= 0 || p->oh <= 0 || p->ow <= 0)
@@ -379,6 +377,7 @@ static int gray_mean_static(const ta_b200_fused_params *p, float *mean_out, cuda
     if (!mean_out) return fail(TA_B200_ERR_NULL, "mean_out is NULL");
     if (p->n == 0) return TA_B200_OK;
     if (p->n > 65535) return fail(TA_B200_ERR_TOO_LARGE, "at most 65535 images per call");
+    if (p->dtype == TA_B200_U8) return fail(TA_B200_ERR_UNSUPPORTED, "the built-in scratch serves float images only");
     const int bpi = mean_blocks_per_image(p->oh, p->ow);
     const size_t need = mean_partials_offset(p->n) + (size_t)p->n * bpi * sizeof(float);
     if (need > kStaticScratchBytes)

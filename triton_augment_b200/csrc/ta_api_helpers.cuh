@@ -131,7 +131,7 @@ static cudaError_t launch_gray_mean(const KArgs &k, int c, int kind, bool bright
 }
 
 // ----------------------------------------------------------------------------- staged pre-pass
-// fp32 images whose rows the tensor copies can read run the pre-pass on the staged kernel
+// fp32 and uint8 images whose rows the tensor copies can read run the pre-pass on the staged kernel
 // (REDUCE variant): the same sampling as the fused pass, one partial sum per (tile, consumer
 // warp) written to scratch, then one block per image adds that image's partials in a fixed
 // order in double.  Measured on 64 x 3 x 1280^2 -> 1024^2: the pre-pass takes 0.24 ms (bilinear)
@@ -159,8 +159,9 @@ static long long mean_staged_tiles(const ta_b200_fused_params *p)
 
 static bool mean_staged_applicable(const ta_b200_fused_params *p)
 {
-    if (p->dtype != TA_B200_F32 || p->n <= 0) return false;
-    if (((size_t)p->w * 4) % 16 != 0 || ((uintptr_t)p->in % 16) != 0 || ((size_t)p->h * p->w * 4) % 16 != 0) return false;
+    if (p->dtype == TA_B200_F16 || p->n <= 0) return false;
+    const size_t es = in_bytes(p->dtype);
+    if (((size_t)p->w * es) % 16 != 0 || ((uintptr_t)p->in % 16) != 0 || ((size_t)p->h * p->w * es) % 16 != 0) return false;
     if (p->h >= (1 << 22) || p->w >= (1 << 22) || p->oh >= (1 << 22) || p->ow >= (1 << 22)) return false;
     if ((double)p->n * p->c >= 2147483648.0) return false;
     return mean_staged_tiles(p) < (1LL << 24);
@@ -188,9 +189,9 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     if (!k.staged_ok) return fail(TA_B200_ERR_UNSUPPORTED, "rows cannot be staged");
     const int mode = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
     const bool bright = (p->apply & TA_B200_APPLY_BRIGHTNESS) != 0;
-    const KernelEntry ke = mean_kernel_entry(mode, bright, p->c);
+    const KernelEntry ke = mean_kernel_entry(mode, bright, p->c, p->dtype == TA_B200_U8);
     int blocks = 0;
-    rc = prepare_kernel(*s, ke, 6, TA_B200_F32, p->c, (unsigned)(mode * 2 + (bright ? 1 : 0)), &blocks);
+    rc = prepare_kernel(*s, ke, 6, p->dtype, p->c, (unsigned)(mode * 2 + (bright ? 1 : 0)), &blocks);
     if (rc != TA_B200_OK) return rc;
     k.out = nullptr;
     k.mean_partials = partials;
@@ -231,6 +232,10 @@ static int gray_mean_on(const ta_b200_fused_params *p, float *mean_out, void *sc
     // a scratch buffer sized by ta_b200_gray_mean_scratch_bytes() has room for the staged kernel's partials
     if (mean_staged_applicable(p) && scratch_bytes >= mean_scratch_need(p))
         return gray_mean_staged(p, mean_out, (float *)((char *)scratch + mean_staged_offset(p)), stream);
+    if (p->dtype == TA_B200_U8)
+        return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale mean of a uint8 image needs rows of whole 16-byte units "
+                    "(width and plane size multiples of 16, 16-byte aligned base) and %zu bytes of scratch",
+                    mean_scratch_need(p));
     DeviceState *s = nullptr;
     rc = current_device(&s, nullptr);
     if (rc != TA_B200_OK) return rc;

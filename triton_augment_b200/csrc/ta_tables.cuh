@@ -83,14 +83,14 @@ template <typename T, int KIND, typename S = T> const KernelTable &make_table()
     return t;
 }
 
-// Staged grayscale-mean pre-pass (fp32): mode 0 no matrix / 1 nearest / 2 bilinear, with or
-// without brightness, 3 or 1 channels.  Defined in ta_inst_f32_mean.cu.
-KernelEntry mean_kernel_entry(int mode, bool bright, int channels);
+// Staged grayscale-mean pre-pass (float32 pixels from float or uint8 images): mode 0 no matrix /
+// 1 nearest / 2 bilinear, with or without brightness, 3 or 1 channels.  Defined in ta_inst_f32_mean.cu.
+KernelEntry mean_kernel_entry(int mode, bool bright, int channels, bool bytes);
 
-template <int C, int MODE, unsigned F> KernelEntry mean_entry()
+template <int C, int MODE, unsigned F, typename S> KernelEntry mean_entry()
 {
-    return KernelEntry{(const void *)&affine_kernel<float, C, MODE, F, false, false, float, true>,
-                       AffineSmem<float, C, F, float>::total, kAffineThreads};
+    return KernelEntry{(const void *)&affine_kernel<float, C, MODE, F, false, false, S, true>,
+                       AffineSmem<float, C, F, S>::total, kAffineThreads};
 }
 
 // Defined one per translation unit (ta_inst_*.cu).

@@ -180,8 +180,6 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
     out = torch.empty(n, c, height, width, dtype=_work_dtype(image), device=image.device)
     if n == 0:
         return out
-    if image.dtype == torch.uint8 and (apply_bits & _lib.APPLY_CONTRAST) and contrast_mode == _lib.CONTRAST_MEAN:
-        raise ValueError('contrast_mode="torchvision" needs a float image (its mean pre-pass does not read bytes)')
     params = _lib.make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness,
                               contrast, saturation, gray, mean, std, contrast_mode)
     keep = None
@@ -214,6 +212,8 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     traffic.  The reference takes float images only.  The classes that are one call of this
     function (TritonFusedAugment, TritonColorJitterNormalize, TritonColorJitter,
     TritonRandomCropFlip, ...) therefore take bytes too; the stand-alone functionals do not.
+    ``contrast_mode="torchvision"`` on bytes needs a width that is a multiple of 16 (the mean
+    pre-pass stages whole 16-byte units of a row) and raises otherwise.
     """
     _validate_image_tensor(image, "image", allow_uint8=True)
     n, _, img_h, img_w = image.shape
