@@ -248,3 +248,32 @@ def test_staging_assertions_hold_on_random_geometry():
     staged, direct, violations, timeouts = _lib.debug_counters()
     assert violations == 0 and timeouts == 0
     assert staged > 100
+
+
+def test_one_large_image():
+    """A single 2048x3072 image (coordinates in the thousands, thousands of tiles of one image,
+    staged and gathered tiles side by side): nearest picks the oracle's texel for every pixel,
+    bilinear stays within tolerance."""
+    ta = _ta()
+    dev = _dev()
+    n, h, w, oh, ow = 1, 2048, 3072, 1900, 2900
+    idx = np.arange(h * w, dtype=np.float32).reshape(1, 1, h, w)          # < 2^24: exact in fp32
+    img = np.broadcast_to(idx, (n, 3, h, w)).copy()
+    angle = np.array([9.0], np.float32)
+    translate = np.array([[31.0, -17.0]], np.float32)
+    scale = np.array([1.05], np.float32)
+    shear = np.array([[3.0, 0.0]], np.float32)
+    top, left, flip = np.array([70.0], np.float32), np.array([90.0], np.float32), np.array([True])
+    t = lambda a: torch.from_numpy(a).to(dev)
+    akw = dict(angle=t(angle), translate=t(translate), scale=t(scale), shear=t(shear))
+    matrix = ta.functional._prepare_affine_matrix_only(n, dev, h, w, t(angle), t(translate), t(scale), t(shear),
+                                                       None).cpu().numpy()
+    out = ta.fused_augment(t(img), t(top), t(left), oh, ow, t(flip), interpolation="nearest", fill=-1.0, **akw)
+    _, want_idx = O.fused_augment(img, top, left, oh, ow, flip, matrix=matrix, fill=-1.0, want_index=True)
+    assert np.array_equal(out[:, 0].cpu().numpy().astype(np.int64), want_idx.astype(np.int64))
+    pix = np.random.default_rng(5).random((n, 3, h, w), dtype=np.float32)
+    got = ta.fused_augment(t(pix), t(top), t(left), oh, ow, t(flip), interpolation="bilinear",
+                           brightness_factor=1.1, saturation_factor=0.9, mean=MEAN, std=STD, **akw).cpu().numpy()
+    want = O.fused_augment(pix, top, left, oh, ow, flip, matrix=matrix, interpolation="bilinear",
+                           brightness=np.float32(1.1), saturation=np.float32(0.9), mean=MEAN, std=STD)
+    assert float(np.abs(got - want).max()) <= FP32_TOL
