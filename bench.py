@@ -44,12 +44,12 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
-def make_transform(interp, fast_rng=False, contrast_mode="fast"):
+def make_transform(interp, fast_rng=False, contrast_mode="fast", out_dtype=None):
     import triton_augment_b200 as ta
     return ta.TritonFusedAugment(crop_size=CROP, horizontal_flip_p=0.5, degrees=15, translate=(0.1, 0.1),
                                  scale=(0.9, 1.1), shear=5, interpolation=interp, brightness=0.2, contrast=0.2,
                                  saturation=0.2, grayscale_p=0.1, mean=MEAN, std=STD, fast_rng=fast_rng,
-                                 contrast_mode=contrast_mode)
+                                 contrast_mode=contrast_mode, out_dtype=out_dtype)
 
 
 class ClockSampler:
@@ -332,6 +332,17 @@ def main():
         for _ in range(e2e_steps):
             aug.forward_host(host_u8, out=host_out, device=dev)
         ms_e2e_u8 = 1e3 * (time.perf_counter() - t0) / e2e_steps
+        # ... and with a float16 result (half the download)
+        aug_h = make_transform(args.interp, out_dtype=torch.float16)
+        host_out_h = torch.empty(N_IMG, 3, CROP, CROP, dtype=torch.float16).pin_memory()
+        for _ in range(2):
+            aug_h.forward_host(host_u8, out=host_out_h, device=dev)
+        if barrier:
+            barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            aug_h.forward_host(host_u8, out=host_out_h, device=dev)
+        ms_e2e_u8h = 1e3 * (time.perf_counter() - t0) / e2e_steps
     clk = clocks.summary()
 
     def over_ranks(ms):
@@ -346,6 +357,7 @@ def main():
     ms_eager_o, ms_kernel_o, ms_step_o = (over_ranks(v) for v in result[other])
     ms_e2e = over_ranks(ms_e2e)
     ms_e2e_u8 = over_ranks(ms_e2e_u8)
+    ms_e2e_u8h = over_ranks(ms_e2e_u8h)
     ms_fast, ms_fast_graph = over_ranks(ms_fast), over_ranks(ms_fast_graph)
     ms_exact = over_ranks(ms_exact)
     if rank != 0:
@@ -387,6 +399,10 @@ def main():
                                 "h2d_bytes_per_step": N_IMG * 3 * SRC * SRC, "d2h_bytes_per_step": N_IMG * 3 * CROP * CROP * 4,
                                 "what": "not the reference's configuration: the same call with a uint8 host batch, "
                                         "scaled by 1/255 inside the kernel"},
+            "e2e_uint8_to_float16": {"value": world * N_IMG / (ms_e2e_u8h * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e_u8h,
+                                     "h2d_bytes_per_step": N_IMG * 3 * SRC * SRC, "d2h_bytes_per_step": N_IMG * 3 * CROP * CROP * 2,
+                                     "what": "not the reference's configuration: uint8 host batch in, float16 result out "
+                                             "(out_dtype=torch.float16)"},
             "gpu_launches": 2 * args.steps,       # per step: inverse_matrix_kernel + affine_kernel (inside the graph)
             "clocks": clk}
     if world == 1:

@@ -32,7 +32,7 @@ typedef enum ta_b200_status {
     TA_B200_OK = 0,
     TA_B200_ERR_NULL = -1,         /* a required pointer is NULL */
     TA_B200_ERR_SHAPE = -2,        /* sizes not positive, or channels not in {1, 3} */
-    TA_B200_ERR_DTYPE = -3,        /* dtype not TA_B200_F32 / TA_B200_F16 / TA_B200_U8 */
+    TA_B200_ERR_DTYPE = -3,        /* dtype is none of the TA_B200_F32 ... TA_B200_U8_F16 codes */
     TA_B200_ERR_UNSUPPORTED = -4,  /* e.g. saturation/grayscale on 1-channel images */
     TA_B200_ERR_CUDA = -5,         /* a CUDA runtime call failed; see ta_b200_last_error() */
     TA_B200_ERR_SCRATCH = -6,      /* scratch buffer missing or too small */
@@ -44,8 +44,11 @@ typedef enum ta_b200_status {
  * pipeline as b / 255 (torchvision's ToTensor scaling), so the result equals the float32 call on
  * in.float() / 255 within the float32 tolerance.  No counterpart in the reference, which takes
  * float tensors only; it saves three quarters of the input traffic.  Its grayscale-mean
- * pre-pass (TA_B200_CONTRAST_MEAN) needs rows of whole 16-byte units. */
-enum { TA_B200_F32 = 0, TA_B200_F16 = 1, TA_B200_U8 = 2 };
+ * pre-pass (TA_B200_CONTRAST_MEAN) needs rows of whole 16-byte units.
+ * TA_B200_U8_F16: bytes in, `out` and the factor vectors float16; b / 255 is rounded to half
+ * and the pixel then takes the float16 path (result within the float16 tolerance of the
+ * float16 call on (in.float() / 255).half()).  TA_B200_CONTRAST_MEAN is not available. */
+enum { TA_B200_F32 = 0, TA_B200_F16 = 1, TA_B200_U8 = 2, TA_B200_U8_F16 = 3 };
 enum { TA_B200_NEAREST = 0, TA_B200_BILINEAR = 1 };
 enum { TA_B200_CONTRAST_FAST = 0, TA_B200_CONTRAST_MEAN = 1 };
 
@@ -71,7 +74,7 @@ enum {
  */
 typedef struct ta_b200_fused_params {
     uint32_t struct_size;     /* sizeof(ta_b200_fused_params), for ABI checking */
-    int32_t  dtype;           /* TA_B200_F32 / TA_B200_F16: type of in, out and the factor vectors; TA_B200_U8 see above */
+    int32_t  dtype;           /* TA_B200_F32 / TA_B200_F16: type of in, out and the factor vectors; TA_B200_U8, TA_B200_U8_F16 see above */
     int32_t  n, c, h, w;      /* input  [n, c, h, w]; c in {1, 3} */
     int32_t  oh, ow;          /* output [n, c, oh, ow] (the crop size) */
     const void *in;

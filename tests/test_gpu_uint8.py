@@ -174,3 +174,62 @@ def test_transform_class_and_host_path_take_bytes():
         ta.fused_augment(odd, 0, 0, 40, 40, contrast_factor=1.1, contrast_mode="torchvision")
     with pytest.raises(TypeError):
         ta.functional.crop(img.to(dev), 0, 0, 64, 64)      # the stand-alone functionals stay float-only
+
+
+@pytest.mark.parametrize("interp", ["none", "nearest", "bilinear"])
+@pytest.mark.parametrize("shape", [(3, 160, 192, 120, 144), (2, 97, 131, 61, 77), (4, 256, 256, 224, 224)])
+def test_bytes_to_half_equal_the_half_call_on_scaled_image(interp, shape):
+    """out_dtype=float16: within the float16 tolerance of the task (1e-2) of the float16 call on
+    (image / 255).half(); plain crop + flip is that image indexed, bit for bit."""
+    import triton_augment_b200 as ta
+    n, h, w, oh, ow = shape
+    p = _case(9, n, h, w, oh, ow)
+    scaled = (p["img"].float() * (1.0 / 255.0)).half()
+    dev = _dev()
+    for bits in (0, 5, 14, 31):
+        kw = {}
+        d = lambda t: t.to(dev)
+        if interp != "none":
+            kw.update(angle=d(p["angle"]), translate=d(p["translate"]), scale=d(p["scale"]), shear=d(p["shear"]),
+                      interpolation=interp)
+        if bits & 1: kw["brightness_factor"] = d(p["b"])
+        if bits & 2: kw["contrast_factor"] = d(p["c"])
+        if bits & 4: kw["saturation_factor"] = d(p["s"])
+        if bits & 8: kw["grayscale"] = d(p["g"])
+        if bits & 16: kw.update(mean=MEAN, std=STD)
+        got = ta.fused_augment(d(p["img"]), d(p["top"]), d(p["left"]), oh, ow, d(p["flip"]), out_dtype=torch.float16, **kw)
+        want = ta.fused_augment(d(scaled), d(p["top"]), d(p["left"]), oh, ow, d(p["flip"]), **kw)
+        assert got.dtype == torch.float16 and got.shape == want.shape
+        err = float((got.float() - want.float()).abs().max())
+        assert err <= 1e-2, (interp, shape, bits, err)
+        if bits == 0 and interp != "bilinear":
+            assert torch.equal(got, want), (interp, shape)
+
+
+def test_half_output_through_the_transform_and_its_limits():
+    import triton_augment_b200 as ta
+    dev = _dev()
+    img = torch.randint(0, 256, (6, 3, 96, 128), dtype=torch.uint8, device=dev)
+    kw = dict(crop_size=(64, 80), horizontal_flip_p=0.5, degrees=10, interpolation="bilinear", brightness=0.2,
+              contrast=0.2, saturation=0.2, grayscale_p=0.2, mean=MEAN, std=STD)
+    for fast in (False, True):
+        torch.manual_seed(3)
+        got = ta.TritonFusedAugment(out_dtype=torch.float16, fast_rng=fast, **kw)(img)
+        torch.manual_seed(3)
+        want = ta.TritonFusedAugment(fast_rng=fast, **kw)((img.float() * (1.0 / 255.0)).half())
+        assert got.dtype == torch.float16
+        assert float((got.float() - want.float()).abs().max()) <= 1e-2
+    # a float batch keeps its dtype whatever the transform's out_dtype says
+    assert ta.TritonFusedAugment(out_dtype=torch.float16, **kw)(img.float() / 255).dtype == torch.float32
+    # host-buffer path
+    torch.manual_seed(4)
+    host = ta.TritonFusedAugment(out_dtype=torch.float16, **kw).forward_host(img.cpu())
+    torch.manual_seed(4)
+    want = ta.TritonFusedAugment(out_dtype=torch.float16, **kw)(img)
+    assert host.dtype == torch.float16 and torch.equal(host, want.cpu())
+    with pytest.raises(ValueError):
+        ta.fused_augment(img, 0, 0, 64, 64, contrast_factor=1.1, contrast_mode="torchvision", out_dtype=torch.float16)
+    with pytest.raises(ValueError):
+        ta.fused_augment(img.float(), 0, 0, 64, 64, out_dtype=torch.float16)
+    with pytest.raises(TypeError):
+        ta.fused_augment(img, 0, 0, 64, 64, out_dtype=torch.float64)

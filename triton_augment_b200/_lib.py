@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TA_B200_LIB") or os.path.join(_HERE, "lib", "libta_b200.so")
 
 ABI_VERSION = 1
-F32, F16, U8 = 0, 1, 2       # U8: bytes in (read as value / 255), float32 out
+F32, F16, U8, U8_F16 = 0, 1, 2, 3       # U8 / U8_F16: bytes in (read as value / 255), float32 / float16 out
 NEAREST, BILINEAR = 0, 1
 CONTRAST_FAST, CONTRAST_MEAN = 0, 1
 APPLY_BRIGHTNESS, APPLY_CONTRAST, APPLY_SATURATION, APPLY_GRAYSCALE, APPLY_NORMALIZE = 1, 2, 4, 8, 16
@@ -127,7 +127,10 @@ def make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits,
     """Fill a FusedParams from tensors (device or host; the caller picks the entry point)."""
     p = FusedParams()
     p.struct_size = C.sizeof(FusedParams)
-    p.dtype = F16 if image.dtype == torch.float16 else U8 if image.dtype == torch.uint8 else F32
+    if image.dtype == torch.uint8:
+        p.dtype = U8_F16 if out.dtype == torch.float16 else U8
+    else:
+        p.dtype = F16 if image.dtype == torch.float16 else F32
     p.n, p.c, p.h, p.w = image.shape
     p.oh, p.ow = out.shape[2], out.shape[3]
     p.inp, p.out = _ptr(image), _ptr(out)

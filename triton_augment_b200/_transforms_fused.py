@@ -34,14 +34,21 @@ class TritonFusedAugment(T._BatchAware):
     generator of the library, seeded per call by one draw from torch's generator, so
     ``torch.manual_seed`` still makes runs repeatable), hence not the reference's parameters
     for a given seed.
+
+    ``out_dtype=torch.float16`` (extra) makes a uint8 batch come out as float16 instead of
+    float32 (see ``functional.fused_augment``); float batches are not affected.
     """
 
     def __init__(self, crop_size=None, horizontal_flip_p: float = 0.0, degrees=0, translate=None, scale=None,
                  shear=None, interpolation=InterpolationMode.NEAREST, fill: float = 0.0, brightness=0, contrast=0,
                  saturation=0, grayscale_p: float = 0.0, mean=None, std=None, same_on_batch: bool = False,
-                 same_on_frame: bool = True, contrast_mode: str = "fast", fast_rng: bool = False):
+                 same_on_frame: bool = True, contrast_mode: str = "fast", fast_rng: bool = False,
+                 out_dtype=None):
         super().__init__(same_on_batch, same_on_frame)
         self.fast_rng = bool(fast_rng)
+        if out_dtype not in (None, torch.float32, torch.float16):
+            raise TypeError(f"out_dtype must be torch.float32 or torch.float16, got {out_dtype}")
+        self.out_dtype = out_dtype             # result dtype for uint8 images (None: float32)
         if crop_size is None:
             self.crop_height = self.crop_width = None
         elif isinstance(crop_size, int):
@@ -114,6 +121,7 @@ class TritonFusedAugment(T._BatchAware):
             fill=self.fill if self.has_affine else 0.0,
             brightness_factor=b, contrast_factor=c, saturation_factor=s, grayscale=g,
             mean=self.color_helper.mean, std=self.color_helper.std, contrast_mode=self.contrast_mode,
+            out_dtype=self.out_dtype if image4d.dtype == torch.uint8 else None,
             _flags=self.color_helper._colour_flags(affine=self.has_affine))
 
     def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None):
@@ -173,7 +181,8 @@ class TritonFusedAugment(T._BatchAware):
         h, w = img.shape[2:]
         if self.crop_height is not None and (self.crop_height > h or self.crop_width > w):
             raise ValueError(f"Crop size ({self.crop_height}, {self.crop_width}) is larger than the image ({h}, {w})")
-        work = F._work_dtype(img)
+        out_dtype = self.out_dtype if img.dtype == torch.uint8 else None
+        work = F._work_dtype(img, out_dtype)
         p = self._sample_fast(lay, work)
         flags = self.color_helper._colour_flags(affine=self.has_affine)
         mean, std = self.color_helper.mean, self.color_helper.std
@@ -186,7 +195,7 @@ class TritonFusedAugment(T._BatchAware):
                             p["brightness"], p["contrast"], p["saturation"], p["gray"],
                             F._rounded_triple(mean, work) if mean is not None else None,
                             F._rounded_triple(std, work) if std is not None else None, bits,
-                            F._contrast_mode(self.contrast_mode))
+                            F._contrast_mode(self.contrast_mode), out_dtype)
 
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         lay = self._layout(image)
@@ -215,7 +224,7 @@ class TritonFusedAugment(T._BatchAware):
         F_ = F
         if flat.ndim != 4 or flat.shape[1] not in (1, 3) or flat.dtype not in (torch.float32, torch.float16, torch.uint8):
             raise ValueError(f"expected float32/float16/uint8 images with 1 or 3 channels, got {tuple(image.shape)} {image.dtype}")
-        work = F._work_dtype(flat)        # float32 for bytes (read as value / 255)
+        work = F._work_dtype(flat, self.out_dtype if flat.dtype == torch.uint8 else None)    # bytes: float32 unless out_dtype
         n, c, h, w = flat.shape
         oh = self.crop_height if self.crop_height is not None else h
         ow = self.crop_width if self.crop_width is not None else w

@@ -52,7 +52,7 @@ constexpr int kStages = 3;
 constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 
 // Source element type S of a staged kernel whose pixels are T: S = T for float and half
-// images; S = uint8_t with T = float reads bytes and scales them by 1/255 (what ToTensor does
+// images; S = uint8_t with T = float or half reads bytes and scales them by 1/255 (what ToTensor does
 // before the reference's pipeline) on the way from shared memory to registers.
 template <typename S> struct Src {
     static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : kPitch;   // staged row pitch, elements
@@ -87,6 +87,15 @@ template <> struct Px<float, uint8_t> {
         asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
         return (uint8_t)v;
     }
+};
+
+// Bytes to half pixels: the same exact scaling, rounded once to half; blends run in fp32 on the
+// raw values like the float case.
+template <> struct Px<__half, uint8_t> {
+    static constexpr bool scaled = true;
+    static __device__ __forceinline__ __half from(uint8_t v) { return __float2half_rn(Px<float, uint8_t>::from(v)); }
+    static __device__ __forceinline__ float2 raw_f2(uint8_t a, uint8_t b) { return Px<float, uint8_t>::raw_f2(a, b); }
+    static __device__ __forceinline__ uint8_t lds(uint32_t addr) { return Px<float, uint8_t>::lds(addr); }
 };
 
 constexpr int kNumGroups = kMaxRows / kGroupRows;

@@ -37,7 +37,7 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 7, kNumDtypes = 3;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
+constexpr int kNumKinds = 7, kNumDtypes = 4;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
@@ -85,13 +85,15 @@ static int current_device(DeviceState **out, int *index)
 
 // bytes per element of `in` / of `out` and the factor vectors
 static size_t in_bytes(int dtype) { return dtype == TA_B200_F32 ? 4 : dtype == TA_B200_F16 ? 2 : 1; }
-static size_t out_bytes(int dtype) { return dtype == TA_B200_F16 ? 2 : 4; }
+static size_t out_bytes(int dtype) { return dtype == TA_B200_F16 || dtype == TA_B200_U8_F16 ? 2 : 4; }
 
 static const KernelTable &table_for(int kind, int dtype)
 {
     if (dtype == TA_B200_U8)      // staged kernels only (launch_fused never asks for kind 0)
         return kind == 1 ? table_u8_nearest() : kind == 2 ? table_u8_bilinear() : kind == 3 ? table_u8_crop_staged()
                                                                                            : table_u8_bilinear_mix();
+    if (dtype == TA_B200_U8_F16)
+        return kind == 1 ? table_u8h_nearest() : kind == 2 ? table_u8h_bilinear() : table_u8h_crop_staged();
     if (dtype == TA_B200_F32)
         return kind == 0 ? table_f32_direct() : kind == 1 ? table_f32_nearest() : kind == 2 ? table_f32_bilinear()
                : kind == 3 ? table_f32_crop_staged() : table_f32_bilinear_mix();
@@ -129,7 +131,7 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
     if (p->struct_size != sizeof(ta_b200_fused_params))
         return fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", p->struct_size,
                     sizeof(ta_b200_fused_params));
-    if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16 && p->dtype != TA_B200_U8)
+    if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16 && p->dtype != TA_B200_U8 && p->dtype != TA_B200_U8_F16)
         return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
     if (p->c != 1 && p->c != 3)
         return fail(TA_B200_ERR_SHAPE, "channels must be 1 or 3, got %d", p->c);
@@ -143,6 +145,8 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
     if ((p->apply & TA_B200_APPLY_BRIGHTNESS) && !p->brightness) return fail(TA_B200_ERR_NULL, "brightness is NULL");
     if (p->matrix && p->interp != TA_B200_NEAREST && p->interp != TA_B200_BILINEAR)
         return fail(TA_B200_ERR_UNSUPPORTED, "interp %d", p->interp);
+    if (p->dtype == TA_B200_U8_F16 && (for_mean || ((p->apply & TA_B200_APPLY_CONTRAST) && p->contrast_mode == TA_B200_CONTRAST_MEAN)))
+        return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale-mean contrast reads bytes into float32 pixels only");
     if (for_mean) return TA_B200_OK;     // the pre-pass reads geometry and brightness only
     if ((p->apply & TA_B200_APPLY_CONTRAST) && !p->contrast) return fail(TA_B200_ERR_NULL, "contrast is NULL");
     if ((p->apply & TA_B200_APPLY_SATURATION) && !p->saturation) return fail(TA_B200_ERR_NULL, "saturation is NULL");
@@ -180,7 +184,7 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
     static const unsigned char late_count[32] = {0, 0, 0, 0, 0, 1, 1, 3, 0, 2, 1, 3, 0, 2, 2, 3,
                                                  0, 0, 0, 0, 0, 1, 2, 3, 0, 2, 1, 3, 0, 2, 2, 3};
     k.late_x_slot = 8;
-    if (p->matrix && p->interp == TA_B200_BILINEAR && p->dtype != TA_B200_F16 && p->oh % 16 != 0 && p->ow % 16 != 0)
+    if (p->matrix && p->interp == TA_B200_BILINEAR && out_bytes(p->dtype) == 4 && p->oh % 16 != 0 && p->ow % 16 != 0)
         k.late_x_slot = 8 - late_count[p->apply & 31u];
     const size_t es = in_bytes(p->dtype);
     k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
@@ -221,8 +225,8 @@ static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return fail(TA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     const size_t es = in_bytes(p->dtype);
-    const CUtensorMapDataType dt = p->dtype == TA_B200_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                 : p->dtype == TA_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapDataType dt = es == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : es == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     const cuuint64_t dims[3] = {(cuuint64_t)p->w, (cuuint64_t)p->h, (cuuint64_t)p->n * p->c};
     const cuuint64_t strides[2] = {(cuuint64_t)p->w * es, (cuuint64_t)p->w * p->h * es};
     const cuuint32_t estr[3] = {1, 1, 1};
@@ -259,7 +263,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
             k.fill = 0.0f;
         }
     }
-    if (kind == 0 && p->dtype == TA_B200_U8) {     // bytes are read by the staged kernels only
+    if (kind == 0 && in_bytes(p->dtype) == 1) {     // bytes are read by the staged kernels only
         kind = 3;
         k.fill = 0.0f;
     }
@@ -377,7 +381,7 @@ static int gray_mean_static(const ta_b200_fused_params *p, float *mean_out, cuda
     if (!mean_out) return fail(TA_B200_ERR_NULL, "mean_out is NULL");
     if (p->n == 0) return TA_B200_OK;
     if (p->n > 65535) return fail(TA_B200_ERR_TOO_LARGE, "at most 65535 images per call");
-    if (p->dtype == TA_B200_U8) return fail(TA_B200_ERR_UNSUPPORTED, "the built-in scratch serves float images only");
+    if (in_bytes(p->dtype) == 1) return fail(TA_B200_ERR_UNSUPPORTED, "the built-in scratch serves float images only");
     const int bpi = mean_blocks_per_image(p->oh, p->ow);
     const size_t need = mean_partials_offset(p->n) + (size_t)p->n * bpi * sizeof(float);
     if (need > kStaticScratchBytes)

@@ -189,7 +189,7 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     if (!k.staged_ok) return fail(TA_B200_ERR_UNSUPPORTED, "rows cannot be staged");
     const int mode = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
     const bool bright = (p->apply & TA_B200_APPLY_BRIGHTNESS) != 0;
-    const KernelEntry ke = mean_kernel_entry(mode, bright, p->c, p->dtype == TA_B200_U8);
+    const KernelEntry ke = mean_kernel_entry(mode, bright, p->c, in_bytes(p->dtype) == 1);
     int blocks = 0;
     rc = prepare_kernel(*s, ke, 6, p->dtype, p->c, (unsigned)(mode * 2 + (bright ? 1 : 0)), &blocks);
     if (rc != TA_B200_OK) return rc;
@@ -232,7 +232,7 @@ static int gray_mean_on(const ta_b200_fused_params *p, float *mean_out, void *sc
     // a scratch buffer sized by ta_b200_gray_mean_scratch_bytes() has room for the staged kernel's partials
     if (mean_staged_applicable(p) && scratch_bytes >= mean_scratch_need(p))
         return gray_mean_staged(p, mean_out, (float *)((char *)scratch + mean_staged_offset(p)), stream);
-    if (p->dtype == TA_B200_U8)
+    if (in_bytes(p->dtype) == 1)
         return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale mean of a uint8 image needs rows of whole 16-byte units "
                     "(width and plane size multiples of 16, 16-byte aligned base) and %zu bytes of scratch",
                     mean_scratch_need(p));

@@ -38,7 +38,7 @@ constexpr bool flags_valid(int channels, unsigned f)
 
 // KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear, 3 crop/flip through the staged kernel,
 // 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only).
-// S: source element type (uint8_t with T = float: bytes scaled by 1/255; staged kernels only).
+// S: source element type (uint8_t with T = float or half: bytes scaled by 1/255; staged kernels only).
 template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename S = T> KernelEntry kernel_entry()
 {
     if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
@@ -101,6 +101,9 @@ const KernelTable &table_u8_crop_staged();
 const KernelTable &table_u8_nearest();
 const KernelTable &table_u8_bilinear();
 const KernelTable &table_u8_bilinear_mix();
+const KernelTable &table_u8h_crop_staged();     // bytes in, half out
+const KernelTable &table_u8h_nearest();
+const KernelTable &table_u8h_bilinear();
 const KernelTable &table_f32_nearest();
 const KernelTable &table_f32_bilinear();
 const KernelTable &table_f16_direct();

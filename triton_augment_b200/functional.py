@@ -48,9 +48,16 @@ def _validate_image_tensor(tensor, name: str = "tensor", allow_uint8: bool = Fal
         raise TypeError(f"{name} must be float32 or float16, got {tensor.dtype}")
 
 
-def _work_dtype(image: torch.Tensor):
-    """dtype of the result and of the per-image factors: the image's, float32 for bytes."""
-    return torch.float32 if image.dtype == torch.uint8 else image.dtype
+def _work_dtype(image: torch.Tensor, out_dtype=None):
+    """dtype of the result and of the per-image factors: the image's; for bytes float32, or
+    float16 when ``out_dtype`` asks for it."""
+    if image.dtype == torch.uint8:
+        if out_dtype not in (None, torch.float32, torch.float16):
+            raise TypeError(f"out_dtype must be torch.float32 or torch.float16, got {out_dtype}")
+        return torch.float32 if out_dtype is None else out_dtype
+    if out_dtype is not None and out_dtype != image.dtype:
+        raise ValueError(f"out_dtype applies to uint8 images; a {image.dtype} image gives a {image.dtype} result")
+    return image.dtype
 
 
 def _convert_to_tensor(value, batch_size: int, dtype, device, name: str = "parameter") -> torch.Tensor:
@@ -171,19 +178,23 @@ def _contrast_mode(mode) -> int:
 
 # ----------------------------------------------------------------------------- the one launch
 def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, brightness, contrast,
-               saturation, gray, mean, std, apply_bits, contrast_mode=_lib.CONTRAST_FAST):
+               saturation, gray, mean, std, apply_bits, contrast_mode=_lib.CONTRAST_FAST, out_dtype=None):
     """Allocate the output and enqueue the kernel(s) on torch's current stream."""
     image = image.contiguous()
     n, c = image.shape[0], image.shape[1]
     if c == 1 and apply_bits & (_lib.APPLY_SATURATION | _lib.APPLY_GRAYSCALE):
         raise ValueError("saturation and grayscale need a 3-channel image")
-    out = torch.empty(n, c, height, width, dtype=_work_dtype(image), device=image.device)
+    work = _work_dtype(image, out_dtype)
+    mean_mode = bool(apply_bits & _lib.APPLY_CONTRAST) and contrast_mode == _lib.CONTRAST_MEAN
+    if mean_mode and image.dtype == torch.uint8 and work == torch.float16:
+        raise ValueError('contrast_mode="torchvision" reads uint8 images into float32 results only')
+    out = torch.empty(n, c, height, width, dtype=work, device=image.device)
     if n == 0:
         return out
     params = _lib.make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness,
                               contrast, saturation, gray, mean, std, contrast_mode)
     keep = None
-    if (apply_bits & _lib.APPLY_CONTRAST) and contrast_mode == _lib.CONTRAST_MEAN:
+    if mean_mode:
         keep = _lib.launch_gray_mean(params, image.device)
         params.gray_mean = keep.data_ptr()
     _lib.launch_fused(params, image.device)
@@ -193,7 +204,8 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
 def fused_augment(image, top, left, height: int, width: int, flip_horizontal=False, angle=0.0,
                   translate=[0.0, 0.0], scale=1.0, shear=[0.0, 0.0], interpolation="nearest", fill: float = 0.0,
                   center=None, brightness_factor=1.0, contrast_factor=1.0, saturation_factor=1.0,
-                  grayscale=False, mean=None, std=None, *, contrast_mode="fast", _flags=None, _matrix=None) -> torch.Tensor:
+                  grayscale=False, mean=None, std=None, *, contrast_mode="fast", out_dtype=None, _flags=None,
+                  _matrix=None) -> torch.Tensor:
     """Affine + crop + flip + brightness + contrast + saturation + grayscale + normalize, one pass.
 
     Drop-in for the reference's ``fused_augment`` (functional.py:1218-1433): per-image
@@ -214,12 +226,16 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     TritonRandomCropFlip, ...) therefore take bytes too; the stand-alone functionals do not.
     ``contrast_mode="torchvision"`` on bytes needs a width that is a multiple of 16 (the mean
     pre-pass stages whole 16-byte units of a row) and raises otherwise.
+    ``out_dtype=torch.float16`` (uint8 images only) rounds ``value / 255`` to half and continues
+    like a float16 image: half the output bytes of the float32 result, equal to the call on
+    ``(image.float() / 255).half()`` within the float16 tolerance; not with
+    ``contrast_mode="torchvision"``.
     """
     _validate_image_tensor(image, "image", allow_uint8=True)
     n, _, img_h, img_w = image.shape
     if height <= 0 or width <= 0:
         raise ValueError(f"Crop size must be positive, got height={height}, width={width}")
-    dev, dt = image.device, _work_dtype(image)
+    dev, dt = image.device, _work_dtype(image, out_dtype)
 
     brightness = _convert_to_tensor(brightness_factor, n, dt, dev, "brightness_factor")
     contrast = _convert_to_tensor(contrast_factor, n, dt, dev, "contrast_factor")
@@ -247,7 +263,7 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     return _run_fused(image, height, width, top_t, left_t, flip_t, matrix, _flags["affine"] and _is_bilinear(interpolation),
                       float(fill), brightness, contrast, saturation, gray,
                       _rounded_triple(mean, dt) if apply_norm else None, _rounded_triple(std, dt) if apply_norm else None,
-                      bits, _contrast_mode(contrast_mode))
+                      bits, _contrast_mode(contrast_mode), out_dtype)
 
 
 def _flags_from_values(angle, translate, scale, shear, bf_arg, cf_arg, sf_arg, gray_arg, bf, cf, sf, gray):
