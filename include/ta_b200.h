@@ -168,6 +168,9 @@ int ta_b200_gray_mean_static(const ta_b200_fused_params *p, float *mean_out, voi
  * matrix are host pointers too.  The batch is cut into slices that flow through
  * upload -> kernel -> download on three streams, so copies overlap the kernel.
  * Device staging buffers are allocated on first use and cached per device.
+ * Of image planes of 1 MiB or more only the box of source pixels that the call
+ * reads (known from top / left / matrix and the output size) is uploaded, when
+ * that is cheaper than copying whole slices (priced from measured copy rates).
  * Synchronous: returns when p->out is complete.
  * Replaces: the host-tensor path of the transform classes, which upload with
  * .cuda() before calling the kernel (triton_augment/transforms.py:1498-1504).
@@ -249,6 +252,10 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
  * the crop kernels), 1 = always the crop kernels, 2 = the staged kernel whenever the tensors
  * allow it.  Both produce identical output; the switch exists so that tests can compare them. */
 int ta_b200_debug_crop_path(int32_t path);
+/* ta_b200_fused_augment_host(): 1 = upload only the box of each large image that the call reads
+ * when the copy plan is cheaper than whole slices (default), 0 = upload every image whole, 2 =
+ * boxes for every call on large images.  Identical output; for tests and measurements. */
+int ta_b200_debug_host_upload(int32_t trimmed);
 /* Tile shape of the staged affine kernel: out[0] = width, out[1] = height,
  * out[2] = row capacity, out[3] = row pitch in elements. */
 void ta_b200_debug_tile_shape(int32_t out[4]);

@@ -25,7 +25,7 @@ SYMBOLS = (
     "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
     "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
-    "ta_b200_debug_crop_path", "ta_b200_sample_params",
+    "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
     "ta_b200_debug_tile_shape",
 )
 
@@ -98,6 +98,8 @@ def load():
     lib.ta_b200_sample_params.restype = C.c_int
     lib.ta_b200_debug_crop_path.argtypes = [C.c_int32]
     lib.ta_b200_debug_crop_path.restype = C.c_int
+    lib.ta_b200_debug_host_upload.argtypes = [C.c_int32]
+    lib.ta_b200_debug_host_upload.restype = C.c_int
     lib.ta_b200_debug_counters.argtypes = [C.POINTER(C.c_uint64), C.c_int]
     lib.ta_b200_debug_counters.restype = C.c_int
     lib.ta_b200_debug_tile_footprint.argtypes = (
@@ -199,6 +201,12 @@ def launch_sample_params(spec: SampleSpec, device: torch.device) -> None:
 def crop_path(path: int) -> None:
     """0: pick the kernel for matrix-free calls by size, 1: crop kernels only, 2: staged kernel (tests)."""
     check(load().ta_b200_debug_crop_path(int(path)), "ta_b200_debug_crop_path")
+
+
+def host_upload(mode: int) -> None:
+    """Host-buffer path: 1 = upload the box of each large image that is read where that is cheaper
+    (default), 0 = whole images, 2 = boxes for every call on large images (tests)."""
+    check(load().ta_b200_debug_host_upload(int(mode)), "ta_b200_debug_host_upload")
 
 
 def debug_counters(reset: bool = False):

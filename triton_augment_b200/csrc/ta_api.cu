@@ -12,6 +12,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/ta_b200.h"
 #include "ta_tables.cuh"

@@ -21,6 +21,9 @@ struct HostPipe {
     size_t scratch_cap = 0;
 };
 static HostPipe g_pipe[kMaxDevices];
+// ta_b200_debug_host_upload(): 0 whole images always, 1 per-image boxes where they pay, 2 boxes
+// whenever the images are large enough (tests compare them)
+static std::atomic<int> g_host_trim{1};
 
 static cudaError_t grow(void **ptr, size_t *cap, size_t need)
 {
@@ -29,6 +32,41 @@ static cudaError_t grow(void **ptr, size_t *cap, size_t need)
     cudaError_t e = cudaMalloc(ptr, need);
     if (e == cudaSuccess) *cap = need;
     return e;
+}
+
+// The part of source image `i` that a call reads, as a box [x0, x1) x [y0, y1) clipped to the
+// image: the host-buffer path uploads nothing else.  The map output pixel -> source position is
+// affine (triton_augment/kernels/geometric_kernel.py:386-415), so the extreme positions belong
+// to the four corners of the output; two pixels of margin cover the taps of either sampling
+// mode (rint, or floor and floor + 1, zero-weight taps included) and the float32 evaluation in
+// the kernels.  Coordinates that are not finite or huge give the whole image.
+static void source_box(const ta_b200_fused_params *hp, int i, int &x0, int &x1, int &y0, int &y1)
+{
+    x0 = 0; x1 = hp->w; y0 = 0; y1 = hp->h;
+    const double left = hp->left ? (double)hp->left[i] : 0.0, top = hp->top ? (double)hp->top[i] : 0.0;
+    const double xa = left, xb = left + (hp->ow - 1), ya = top, yb = top + (hp->oh - 1);
+    double xmin, xmax, ymin, ymax;
+    if (hp->matrix) {
+        const float *m = hp->matrix + (size_t)i * 6;
+        const double hw = 0.5 * hp->w, hh = 0.5 * hp->h;
+        xmin = ymin = INFINITY; xmax = ymax = -INFINITY;
+        for (int k = 0; k < 4; ++k) {
+            const double xc = ((k & 1) ? xb : xa) - hw + 0.5, yc = ((k & 2) ? yb : ya) - hh + 0.5;
+            const double sx = (double)m[0] * xc + (double)m[1] * yc + (double)m[2] + hw - 0.5;
+            const double sy = (double)m[3] * xc + (double)m[4] * yc + (double)m[5] + hh - 0.5;
+            if (!(fabs(sx) < 1.0e6) || !(fabs(sy) < 1.0e6)) return;
+            xmin = fmin(xmin, sx); xmax = fmax(xmax, sx); ymin = fmin(ymin, sy); ymax = fmax(ymax, sy);
+        }
+    } else {
+        if (!(fabs(xa) < 1.0e6) || !(fabs(ya) < 1.0e6)) return;
+        xmin = xa; xmax = xb; ymin = ya; ymax = yb;
+    }
+    const long long bx0 = (long long)floor(xmin) - 2, bx1 = (long long)ceil(xmax) + 3;
+    const long long by0 = (long long)floor(ymin) - 2, by1 = (long long)ceil(ymax) + 3;
+    x0 = (int)(bx0 < 0 ? 0 : bx0 > hp->w ? hp->w : bx0);
+    x1 = (int)(bx1 < 0 ? 0 : bx1 > hp->w ? hp->w : bx1);
+    y0 = (int)(by0 < 0 ? 0 : by0 > hp->h ? hp->h : by0);
+    y1 = (int)(by1 < 0 ? 0 : by1 > hp->h ? hp->h : by1);
 }
 
 #define TA_CU(call, what) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return cuda_fail(e_, what); } while (0)
@@ -112,13 +150,72 @@ static int fused_host(const ta_b200_fused_params *hp)
         TA_CU(grow(&P.d_scratch, &P.scratch_cap, mean_scratch_need(&one)), "cudaMalloc(scratch)");
     }
 
+    // Upload plan.  Of a large image only the box that is read needs to go up, as one copy per
+    // image: either its rows whole (a run of bytes per channel) or the box itself (strided).
+    // Measured with pinned batches: a strided copy moves rows of 2-4 KB at about 0.6 of the 50 GB/s
+    // of a contiguous one (shorter rows: less), and a separate copy per image costs up to as much
+    // as 1 MB of payload.  With those two figures the plan is priced per image, and the call uses
+    // it only when it undercuts the plain slice copies by 10 % (128 x 3 x 1024^2 -> 512^2 float32
+    // crops: 30.1 ms -> 12.7-13.0 ms; 64 x 3 x 1280^2 -> 1024^2 crops: 24.8 -> 22.1-22.5 ms; the same
+    // with +-15 degrees reads nearly every row, gained 2-6 % on float32 and lost 6 % on bytes when
+    // forced, and keeps the plain copies).
+    const size_t es_in = ta::in_bytes(hp->dtype), row_bytes = (size_t)hp->w * es_in, plane_bytes = row_bytes * hp->h;
+    const int col_unit = (int)(32 / es_in);
+    struct Box { int x0, x1, y0, y1; bool strided; };
+    std::vector<Box> boxes;
+    bool trim = g_host_trim.load(std::memory_order_relaxed) != 0 && plane_bytes >= (1u << 20);
+    if (trim) {
+        boxes.resize((size_t)hp->n);
+        const double per_copy = 1.0e6;
+        double planned = 0.0;
+        for (int i = 0; i < hp->n; ++i) {
+            Box &bx = boxes[(size_t)i];
+            source_box(hp, i, bx.x0, bx.x1, bx.y0, bx.y1);
+            bx.strided = false;
+            if (bx.x1 <= bx.x0 || bx.y1 <= bx.y0) { bx.x0 = bx.x1 = 0; continue; }     // nothing of this image is read
+            bx.x0 = bx.x0 / col_unit * col_unit;                                        // 32-byte units
+            bx.x1 = (bx.x1 + col_unit - 1) / col_unit * col_unit;
+            if (bx.x1 > hp->w) bx.x1 = hp->w;
+            const double rows_cost = (double)hp->c * (bx.y1 - bx.y0) * (double)row_bytes;
+            const double box_bytes = (double)hp->c * (bx.y1 - bx.y0) * (double)(bx.x1 - bx.x0) * (double)es_in;
+            bx.strided = (size_t)(bx.x1 - bx.x0) * es_in >= 2048 && box_bytes / 0.6 < rows_cost;
+            if (!bx.strided) { bx.x0 = 0; bx.x1 = hp->w; }
+            planned += per_copy + (bx.strided ? box_bytes / 0.6 : rows_cost);
+        }
+        trim = planned <= 0.90 * (double)hp->n * (double)in_img || g_host_trim.load(std::memory_order_relaxed) == 2;
+    }
     const int slices = (hp->n + slice - 1) / slice;
     for (int i = 0; i < slices; ++i) {
         const int b = i & 1, first = i * slice, cnt = (first + slice <= hp->n) ? slice : hp->n - first;
         // upload: the input buffer is free once the kernel of slice i-2 has run
         if (i >= 2) TA_CU(cudaStreamWaitEvent(P.up, P.computed[b], 0), "cudaStreamWaitEvent");
-        TA_CU(cudaMemcpyAsync(P.d_in[b], (const char *)hp->in + (size_t)first * in_img, (size_t)cnt * in_img,
-                              cudaMemcpyHostToDevice, P.up), "cudaMemcpyAsync(upload)");
+        if (!trim) {
+            TA_CU(cudaMemcpyAsync(P.d_in[b], (const char *)hp->in + (size_t)first * in_img, (size_t)cnt * in_img,
+                                  cudaMemcpyHostToDevice, P.up), "cudaMemcpyAsync(upload)");
+        } else {
+            // the rest of the device buffer keeps stale bytes, which no kernel reads
+            for (int j = 0; j < cnt; ++j) {
+                const Box &bx = boxes[(size_t)(first + j)];
+                if (bx.x1 <= bx.x0) continue;
+                char *dst_img = (char *)P.d_in[b] + (size_t)j * in_img;
+                const char *src_img = (const char *)hp->in + (size_t)(first + j) * in_img;
+                if (!bx.strided) {
+                    // rows y0..y1 of every channel: c runs of bytes, plane_bytes apart
+                    const size_t at = (size_t)bx.y0 * row_bytes;
+                    TA_CU(cudaMemcpy2DAsync(dst_img + at, plane_bytes, src_img + at, plane_bytes, (size_t)(bx.y1 - bx.y0) * row_bytes,
+                                            (size_t)hp->c, cudaMemcpyHostToDevice, P.up), "cudaMemcpy2DAsync(upload rows)");
+                } else {
+                    cudaMemcpy3DParms cp;
+                    memset(&cp, 0, sizeof(cp));
+                    cp.srcPtr = make_cudaPitchedPtr(const_cast<char *>(src_img), row_bytes, row_bytes, (size_t)hp->h);
+                    cp.dstPtr = make_cudaPitchedPtr(dst_img, row_bytes, row_bytes, (size_t)hp->h);
+                    cp.srcPos = cp.dstPos = make_cudaPos((size_t)bx.x0 * es_in, (size_t)bx.y0, 0);
+                    cp.extent = make_cudaExtent((size_t)(bx.x1 - bx.x0) * es_in, (size_t)(bx.y1 - bx.y0), (size_t)hp->c);
+                    cp.kind = cudaMemcpyHostToDevice;
+                    TA_CU(cudaMemcpy3DAsync(&cp, P.up), "cudaMemcpy3DAsync(upload box)");
+                }
+            }
+        }
         TA_CU(cudaEventRecord(P.uploaded[b], P.up), "cudaEventRecord");
         // run: needs its upload, and its output buffer back from the download of slice i-2
         TA_CU(cudaStreamWaitEvent(P.run, P.uploaded[b], 0), "cudaStreamWaitEvent");
@@ -181,6 +278,13 @@ int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out, void *scra
 }
 
 int ta_b200_fused_augment_host(const ta_b200_fused_params *p) { return ta::fused_host(p); }
+
+int ta_b200_debug_host_upload(int32_t trimmed)
+{
+    if (trimmed < 0 || trimmed > 2) return ta::fail(TA_B200_ERR_UNSUPPORTED, "mode %d", trimmed);
+    ta::g_host_trim.store(trimmed, std::memory_order_relaxed);
+    return TA_B200_OK;
+}
 
 int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *angle, const float *translate,
                                   const float *scale, const float *shear, float *matrix, void *stream)
