@@ -201,7 +201,7 @@ def kernel_only(aug, img, steps, warmup, barrier, exact_contrast=False):
     matrix = None
     if aug.has_affine:
         matrix = F._prepare_affine_matrix_only(n, dev, src_h, src_w, angle, translate, scale, shear, None).contiguous()
-    work = F._work_dtype(img)
+    work = F._work_dtype(img, aug.out_dtype if img.dtype == torch.uint8 else None)
     out = torch.empty(n, 3, crop, crop, device=dev, dtype=work)
     p = _lib.make_params(img, out, top, left, flip, matrix, 0.0, aug.has_affine and F._is_bilinear(aug.interpolation), 31,
                          b.to(work), c.to(work), s.to(work), g,
@@ -225,6 +225,7 @@ PROFILE_CONFIGS = {
     "c3": (N_IMG, SRC, CROP, torch.float32, True),
     "c3exact": (N_IMG, SRC, CROP, torch.float32, True),  # C3 with torchvision-exact contrast: mean pre-pass + fused kernel
     "c3u8": (N_IMG, SRC, CROP, torch.uint8, True),       # C3 fed with bytes (scaled by 1/255 in the kernel), float32 out
+    "c3u8h": (N_IMG, SRC, CROP, torch.uint8, True),      # ... float16 out
     "c4": (512, 512, 448, torch.float16, True),          # fp16 affine + crop 448 + flip + colour + normalize
     "c5b": (4096, 224, 112, torch.float32, False),       # crop 112 + flip + colour + normalize, image batch
 }
@@ -242,10 +243,11 @@ def profile_case(config, images, interp):
            else torch.rand(n, 3, src, src, device="cuda:0").to(dtype))
     kw = dict(degrees=15, translate=(0.1, 0.1), scale=(0.9, 1.1), shear=5, interpolation=interp) if affine else {}
     aug = ta.TritonFusedAugment(crop_size=crop, horizontal_flip_p=0.5, brightness=0.2, contrast=0.2, saturation=0.2,
-                                grayscale_p=0.1, mean=MEAN, std=STD, **kw)
+                                grayscale_p=0.1, mean=MEAN, std=STD,
+                                out_dtype=torch.float16 if config == "c3u8h" else None, **kw)
     exact = config == "c3exact"
     ms = kernel_only(aug, img, 2, 1, None, exact_contrast=exact)
-    out_bytes = 4 if dtype == torch.uint8 else img.element_size()
+    out_bytes = 2 if config == "c3u8h" else 4 if dtype == torch.uint8 else img.element_size()
     gbs = n * 3 * crop * crop * (img.element_size() * (2 if exact else 1) + out_bytes) / (ms * 1e-3) / 1e9
     print(f"profile case {config}: {n} images, {interp if affine else 'no affine'}, {ms:.4f} ms per launch, "
           f"{gbs:.0f} GB/s algorithmic")

@@ -38,7 +38,8 @@ constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
 // (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but 2-way bank conflicts cost
 // more than they saved).  One-byte elements need 128: a copy starts on a 16-byte boundary, i.e.
 // up to 15 columns left of the footprint, and a 64-pixel tile under +-15 degrees and scale 1.1
-// already spans ~85 columns.
+// already spans ~85 columns.  (144 was tried for bytes, to spread rows over the banks: fewer
+// conflicts, no gain - the byte kernels are bound by instruction issue.)
 constexpr int kPitch = 96;
 constexpr int kPitchBytes1 = 128;
 TA_HD int pitch_of(int elem_bytes) { return elem_bytes == 1 ? kPitchBytes1 : kPitch; }
