@@ -191,6 +191,16 @@ def test_vectorised_crop_flip_kernel_every_shift(dtype):
             got = ta.fused_augment(t(img), t(top), t(left), oh, ow, t(flip)).cpu().numpy()
             want = O.fused_augment(img, top, left, oh, ow, flip)
             assert np.array_equal(got, want), (dtype, h, w, flip_all)
+    # channel planes that are not whole vectors although the tensor is (51 * 394 elements, 4 images):
+    # the channels of a strip then sit at different offsets within a vector
+    img = rng.random((4, 3, 51, 394), dtype=np.float32).astype(dtype)
+    top = np.array([5.0, 7.0, 0.0, 21.0], np.float32)
+    left = np.array([31.0, 134.0, 0.0, 190.0], np.float32)
+    for flip_all in (False, True):
+        flip = np.array([flip_all, flip_all, not flip_all, flip_all])
+        t = lambda a: torch.from_numpy(a).to(dev)
+        got = ta.fused_augment(t(img), t(top), t(left), 30, 204, t(flip)).cpu().numpy()
+        assert np.array_equal(got, O.fused_augment(img, top, left, 30, 204, flip)), (dtype, "odd planes", flip_all)
     # windows partly outside the image: left beyond w - ow, negative top
     img = rng.random((4, 3, 32, 64), dtype=np.float32).astype(dtype)
     top = np.array([-3.0, 0.0, 5.0, 30.0], np.float32)

@@ -283,8 +283,10 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     // Crop/flip only: the 128-bit kernel needs whole-vector output rows and vector-aligned tensors.
     const size_t es_bytes = in_bytes(p->dtype);
     const int epv = (int)(16 / es_bytes);
+    // (every channel plane a whole number of vectors: the kernel takes the shift of a strip from
+    // its first channel)
     const bool vec = kind == 0 && !g_force_scalar_direct && p->ow % epv == 0 && ((uintptr_t)p->in % 16) == 0 &&
-                     ((uintptr_t)p->out % 16) == 0 && ((size_t)p->n * p->c * p->h * p->w * es_bytes) % 16 == 0;
+                     ((uintptr_t)p->out % 16) == 0 && ((size_t)p->h * p->w * es_bytes) % 16 == 0;
     if (vec) ke = p->c == 3 ? &tab.c3_vec[f] : &tab.c1_vec[f];
     if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;

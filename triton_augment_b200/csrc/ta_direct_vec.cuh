@@ -6,8 +6,9 @@
 // loads the two ALIGNED 16-byte vectors that cover its run and shifts the wanted elements
 // out of the 8 words with funnel shifts (the shift is the same for the whole warp); a flipped
 // image reads the mirrored run and reverses it in registers.  Launched only when the host
-// has checked that rows of the output are whole vectors and that both tensors are 16-byte
-// aligned and a whole number of vectors long; anything else uses direct_kernel.
+// has checked that rows of the output are whole vectors, that both tensors are 16-byte
+// aligned and that every channel plane of the input is a whole number of vectors (so all
+// channels of a strip share one shift); anything else uses direct_kernel.
 // Strips whose source run leaves its image row (an invalid crop window) take the scalar
 // route with the same read-as-zero rule.
 #pragma once
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(kThreads, VecTraits<T>::blocks) direct_vec_ker
     const int warps_total = (gridDim.x * kThreads) >> 5;
     const int strips_per_img = k.tiles_x * k.tiles_y;        // tiles_x = ceil(ow / (32 EPV)), tiles_y = ceil(oh / kVecRows)
     const size_t plane = (size_t)k.h * k.w, oplane = (size_t)k.oh * k.ow;
-    const size_t total_vecs = (size_t)k.n * C * plane / EPV;  // the input is a whole number of vectors
+    const size_t total_vecs = (size_t)k.n * C * plane / EPV;  // planes are whole numbers of vectors
     const uint4 *in_vec = reinterpret_cast<const uint4 *>(k.in);
 
     for (int strip = warp_global; strip < k.num_tiles; strip += warps_total) {
