@@ -13,7 +13,7 @@ from oracle import fused_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def run_cases(seed, count):
+def run_cases(seed, count, big=False, channels=(3,)):
     import triton_augment_b200 as ta
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(seed)
@@ -21,8 +21,10 @@ def run_cases(seed, count):
     for case in range(count):
         kind = ["f32", "f16", "u8", "u8h"][int(rng.integers(0, 4))]
         interp = ["none", "nearest", "bilinear"][int(rng.integers(0, 3))]
-        n = int(rng.integers(1, 5))
-        h, w = int(rng.integers(20, 300)), int(rng.integers(20, 400))
+        n = int(rng.integers(1, 3 if big else 5))
+        ch = int(rng.choice(channels))
+        h, w = (int(rng.integers(300, 1300)), int(rng.integers(300, 1300))) if big else \
+               (int(rng.integers(20, 300)), int(rng.integers(20, 400)))
         if rng.random() < 0.6:
             w = (w + 15) // 16 * 16                          # rows that can be staged, for every dtype
         oh, ow = int(rng.integers(1, h + 1)), int(rng.integers(1, w + 1))
@@ -36,17 +38,17 @@ def run_cases(seed, count):
         scale = rng.uniform(0.3 if wild else 0.8, 3.0 if wild else 1.25, n).astype(np.float32)
         shear = rng.uniform(-20 if wild else -5, 20 if wild else 5, (n, 2)).astype(np.float32)
         fill = float(rng.choice([0.0, 0.0, 0.5, -1.0]))
-        bits = int(rng.integers(0, 32))
+        bits = int(rng.integers(0, 32)) & (31 if ch == 3 else 19)       # one channel: no saturation, no grayscale
         bytes_in = kind in ("u8", "u8h")
         half = kind in ("f16", "u8h")
         fdt = np.float16 if half else np.float32
         if bytes_in:
-            raw = rng.integers(0, 256, (n, 3, h, w), dtype=np.uint8)
+            raw = rng.integers(0, 256, (n, ch, h, w), dtype=np.uint8)
             scaled = raw.astype(np.float32) * np.float32(1.0 / 255.0)
             ref_img = scaled.astype(np.float16) if half else scaled
             img = raw
         else:
-            img = rng.random((n, 3, h, w), dtype=np.float32).astype(fdt)
+            img = rng.random((n, ch, h, w), dtype=np.float32).astype(fdt)
             ref_img = img
         b = rng.uniform(0.6, 1.4, n).astype(np.float32) if bits & 1 else np.ones(n, np.float32)
         c = rng.uniform(0.6, 1.4, n).astype(np.float32) if bits & 2 else np.ones(n, np.float32)
@@ -81,9 +83,14 @@ def run_cases(seed, count):
         allowed = 0 if interp != "nearest" else max(2, diff.size // 20000)
         key = (kind, interp)
         worst[key] = max(worst.get(key, 0.0), err if bad == 0 else 0.0)
-        assert bad <= allowed, (case, kind, interp, (n, h, w, oh, ow), bits, wild, err, bad)
+        assert bad <= allowed, (case, kind, interp, (n, ch, h, w, oh, ow), bits, wild, err, bad)
     return worst
 
 
 def test_random_cases():
     run_cases(2024, 120)
+
+
+def test_random_cases_large_images_and_single_channel():
+    run_cases(2025, 24, big=True)
+    run_cases(2026, 40, channels=(1,))
