@@ -189,6 +189,15 @@ def test_host_buffer_entry_point_matches_device_path():
         torch.manual_seed(21); want = aug(host.to(DEV)).cpu()
         torch.manual_seed(21); got = aug.forward_host(host)
         assert not got.is_cuda and got.equal(want)
+    # output sizes that are not multiples of 16: the reference's per-pixel coordinate recipe follows
+    # the pixel's index in the whole batch, also when the batch goes through in slices
+    odd = ta.TritonFusedAugment(crop_size=(41, 50), horizontal_flip_p=0.5, degrees=15, translate=(0.1, 0.1),
+                                scale=(0.9, 1.1), shear=5, interpolation="bilinear", brightness=0.2, contrast=0.2,
+                                saturation=0.2, grayscale_p=0.3, mean=MEAN, std=STD)
+    host = torch.rand(37, 3, 64, 72).pin_memory()
+    torch.manual_seed(22); want = odd(host.to(DEV)).cpu()
+    torch.manual_seed(22); got = odd.forward_host(host)
+    assert got.equal(want)
     mean_mode = ta.TritonFusedAugment(crop_size=32, contrast=0.3, brightness=0.2, contrast_mode="torchvision")
     host = torch.rand(9, 3, 48, 48).pin_memory()
     torch.manual_seed(3); want = mean_mode(host.to(DEV)).cpu()

@@ -199,7 +199,7 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
         const float yc = centred(yi, g.half_h);
         float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
         if constexpr (MIX) {
-            if (late_x(k, (uint32_t)n * (uint32_t)oplane + (uint32_t)(y * k.ow + x)))
+            if (late_x(k, k.lin_base + (uint32_t)n * (uint32_t)oplane + (uint32_t)(y * k.ow + x)))
                 sx = src_coord_r<1>(xc, yc, g.a, g.b, g.c, g.half_w);
         }
         const float sy = MODE == 0 ? truncf(yi) : src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);

@@ -302,7 +302,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                     sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
                     if constexpr (MIX) {                  // see late_x()
                         const float2 alt = src_coord2<1>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                        const uint32_t base = (uint32_t)n * oplane + (uint32_t)x;
+                        const uint32_t base = k.lin_base + (uint32_t)n * oplane + (uint32_t)x;
                         if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
                         if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
                     }

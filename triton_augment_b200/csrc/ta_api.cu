@@ -241,7 +241,10 @@ static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
     return TA_B200_OK;
 }
 
-static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool checked)
+// first_image: index of p's first image in the batch the caller is working through in pieces (the
+// host-buffer pipeline); the per-pixel rule of late_x() follows the index within that batch, as one
+// launch of the reference over the whole batch would.
+static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool checked, unsigned first_image = 0)
 {
     int rc = validate(p);
     if (rc != TA_B200_OK) return rc;
@@ -252,6 +255,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
 
     KArgs k;
     fill_kargs(k, p, *s);
+    k.lin_base = first_image * (unsigned)p->oh * (unsigned)p->ow;      // modulo 2^32: late_x() reads bits 7-9
     int kind = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
     if (kind == 0 && p->dtype == TA_B200_F32 && k.staged_ok) {
         // Large fp32 batches run faster through the staged kernel (tensor copies cost no

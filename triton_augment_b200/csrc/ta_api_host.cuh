@@ -237,7 +237,7 @@ static int fused_host(const ta_b200_fused_params *hp)
             rc = gray_mean_on(&q, (float *)(dp + o_gm) + first, P.d_scratch, P.scratch_cap, P.run, true);
             if (rc != TA_B200_OK) return rc;
         }
-        rc = launch_fused(&q, P.run, false);
+        rc = launch_fused(&q, P.run, false, (unsigned)first);
         if (rc != TA_B200_OK) return rc;
         TA_CU(cudaEventRecord(P.computed[b], P.run), "cudaEventRecord");
         // download

@@ -36,6 +36,7 @@ struct KArgs {
     int tiles_x, tiles_y, num_tiles;
     int staged_ok;                     // source rows can be bulk-copied (16-byte aligned pitch and base)
     int late_x_slot;                   // see late_x(): 8 = never
+    unsigned lin_base;                 // linear index of this launch's first output element within the caller's batch (late_x())
     float fill;
     float mean[3], stdv[3];            // image-dtype-rounded values
     float inv_std[3], nbias[3];        // 1/std and -mean/std (fp32 path)
