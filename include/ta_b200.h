@@ -120,6 +120,16 @@ const char *ta_b200_last_error(void);
 int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream);
 
 /*
+ * The same for a piece of a larger batch (a shard, a slice): first_image is the index of p's
+ * first image within that batch.  The reference's compiled kernel evaluates the source x
+ * coordinate of some pixels in a second operation order that depends on the pixel's linear
+ * index in the launch (bilinear float32 outputs whose height and width are both not multiples of
+ * 16); with first_image the pieces reproduce one reference launch over the whole batch bit for
+ * bit.  ta_b200_fused_augment() is first_image = 0.  No counterpart in the reference.
+ */
+int ta_b200_fused_augment_at(const ta_b200_fused_params *p, uint32_t first_image, void *stream);
+
+/*
  * Per-image mean of the grayscale of the image that contrast would see in a
  * sequential pipeline: geometry (as described by *p) followed by brightness (if
  * its bit is set).  Writes mean_out[n] (device, fp32 holding image-dtype-rounded

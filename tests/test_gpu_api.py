@@ -230,6 +230,13 @@ def test_sharded_wrapper_equals_single_device():
         outs.append(ta.ShardedAugment.for_rank(aug, rank, 3, device=DEV)((x[a:b], tuple(x.shape))))
     torch.manual_seed(79)
     assert torch.cat(outs).equal(aug(x))
+    # bilinear float32 with an output whose sides are not multiples of 16: the per-pixel coordinate
+    # recipe follows the pixel's index in the whole batch, so shards must be told where they start
+    odd = ta.TritonFusedAugment(crop_size=(29, 37), horizontal_flip_p=0.5, degrees=12, scale=(0.9, 1.1), shear=4,
+                                interpolation="bilinear", brightness=0.2, saturation=0.2, grayscale_p=0.2, mean=MEAN, std=STD)
+    torch.manual_seed(80); want = odd(x)
+    torch.manual_seed(80); parts = ta.ShardedAugment(odd, devices)(x)
+    assert torch.cat([p.to(DEV) for p in parts]).equal(want)
 
 
 def test_matrix_kernel_is_bit_identical_to_torch_ops():

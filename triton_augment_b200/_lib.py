@@ -22,7 +22,7 @@ APPLY_BRIGHTNESS, APPLY_CONTRAST, APPLY_SATURATION, APPLY_GRAYSCALE, APPLY_NORMA
 
 # Every symbol include/ta_b200.h declares.
 SYMBOLS = (
-    "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_gray_mean",
+    "ta_b200_abi_version", "ta_b200_last_error", "ta_b200_fused_augment", "ta_b200_fused_augment_at", "ta_b200_gray_mean",
     "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
     "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
@@ -84,6 +84,8 @@ def load():
     lib.ta_b200_fused_augment.restype = C.c_int
     lib.ta_b200_debug_fused_checked.argtypes = [C.POINTER(FusedParams), C.c_void_p]
     lib.ta_b200_debug_fused_checked.restype = C.c_int
+    lib.ta_b200_fused_augment_at.argtypes = [C.POINTER(FusedParams), C.c_uint32, C.c_void_p]
+    lib.ta_b200_fused_augment_at.restype = C.c_int
     lib.ta_b200_gray_mean.argtypes = [C.POINTER(FusedParams), C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.ta_b200_gray_mean.restype = C.c_int
     lib.ta_b200_gray_mean_scratch_bytes.argtypes = [C.POINTER(FusedParams)]
@@ -151,12 +153,18 @@ def make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits,
     return p
 
 
-def launch_fused(params: FusedParams, device: torch.device, checked: bool = False) -> None:
+def launch_fused(params: FusedParams, device: torch.device, checked: bool = False, first_image: int = 0) -> None:
+    """``first_image``: index of the first image within the batch this call is a piece of (see
+    ta_b200_fused_augment_at in the header)."""
     lib = load()
     with torch.cuda.device(device):
         stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-        fn = lib.ta_b200_debug_fused_checked if checked else lib.ta_b200_fused_augment
-        check(fn(C.byref(params), stream), "ta_b200_fused_augment")
+        if checked:
+            check(lib.ta_b200_debug_fused_checked(C.byref(params), stream), "ta_b200_fused_augment")
+        elif first_image:
+            check(lib.ta_b200_fused_augment_at(C.byref(params), int(first_image), stream), "ta_b200_fused_augment_at")
+        else:
+            check(lib.ta_b200_fused_augment(C.byref(params), stream), "ta_b200_fused_augment")
 
 
 def launch_fused_host(params: FusedParams, device: torch.device) -> None:

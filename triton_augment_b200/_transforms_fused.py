@@ -108,8 +108,9 @@ class TritonFusedAugment(T._BatchAware):
         angle, translate, scale, shear = spread_params[:4]
         return F._prepare_affine_matrix_only(total, device, h, w, angle, translate, scale, shear, None).contiguous()
 
-    def _apply(self, image4d, spread_params, matrix=None):
-        """Run the kernel on a (slice of a) flattened batch with per-sample parameters."""
+    def _apply(self, image4d, spread_params, matrix=None, first_image=0):
+        """Run the kernel on a (slice of a) flattened batch with per-sample parameters;
+        ``first_image`` is the slice's position in the batch."""
         angle, translate, scale, shear, top, left, flip, b, c, s, g = spread_params
         h, w = image4d.shape[2:]
         return F.fused_augment(
@@ -121,7 +122,7 @@ class TritonFusedAugment(T._BatchAware):
             fill=self.fill if self.has_affine else 0.0,
             brightness_factor=b, contrast_factor=c, saturation_factor=s, grayscale=g,
             mean=self.color_helper.mean, std=self.color_helper.std, contrast_mode=self.contrast_mode,
-            out_dtype=self.out_dtype if image4d.dtype == torch.uint8 else None,
+            out_dtype=self.out_dtype if image4d.dtype == torch.uint8 else None, _first_image=first_image,
             _flags=self.color_helper._colour_flags(affine=self.has_affine))
 
     def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None):

@@ -265,6 +265,11 @@ int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream)
     return ta::launch_fused(p, (cudaStream_t)stream, false);
 }
 
+int ta_b200_fused_augment_at(const ta_b200_fused_params *p, uint32_t first_image, void *stream)
+{
+    return ta::launch_fused(p, (cudaStream_t)stream, false, first_image);
+}
+
 size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p)
 {
     if (!p || p->n <= 0 || p->oh <= 0 || p->ow <= 0) return 256;

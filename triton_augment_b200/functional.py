@@ -178,7 +178,7 @@ def _contrast_mode(mode) -> int:
 
 # ----------------------------------------------------------------------------- the one launch
 def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, brightness, contrast,
-               saturation, gray, mean, std, apply_bits, contrast_mode=_lib.CONTRAST_FAST, out_dtype=None):
+               saturation, gray, mean, std, apply_bits, contrast_mode=_lib.CONTRAST_FAST, out_dtype=None, first_image=0):
     """Allocate the output and enqueue the kernel(s) on torch's current stream."""
     image = image.contiguous()
     n, c = image.shape[0], image.shape[1]
@@ -197,7 +197,7 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
     if mean_mode:
         keep = _lib.launch_gray_mean(params, image.device)
         params.gray_mean = keep.data_ptr()
-    _lib.launch_fused(params, image.device)
+    _lib.launch_fused(params, image.device, first_image=first_image)
     return out
 
 
@@ -205,7 +205,7 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
                   translate=[0.0, 0.0], scale=1.0, shear=[0.0, 0.0], interpolation="nearest", fill: float = 0.0,
                   center=None, brightness_factor=1.0, contrast_factor=1.0, saturation_factor=1.0,
                   grayscale=False, mean=None, std=None, *, contrast_mode="fast", out_dtype=None, _flags=None,
-                  _matrix=None) -> torch.Tensor:
+                  _matrix=None, _first_image=0) -> torch.Tensor:
     """Affine + crop + flip + brightness + contrast + saturation + grayscale + normalize, one pass.
 
     Drop-in for the reference's ``fused_augment`` (functional.py:1218-1433): per-image
@@ -263,7 +263,7 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     return _run_fused(image, height, width, top_t, left_t, flip_t, matrix, _flags["affine"] and _is_bilinear(interpolation),
                       float(fill), brightness, contrast, saturation, gray,
                       _rounded_triple(mean, dt) if apply_norm else None, _rounded_triple(std, dt) if apply_norm else None,
-                      bits, _contrast_mode(contrast_mode), out_dtype)
+                      bits, _contrast_mode(contrast_mode), out_dtype, _first_image)
 
 
 def _flags_from_values(angle, translate, scale, shear, bf_arg, cf_arg, sf_arg, gray_arg, bf, cf, sf, gray):

@@ -111,14 +111,14 @@ class ShardedAugment:
             if flat.shape[0] != stop - start:
                 raise ValueError(f"rank {self._rank} owns samples [{start}, {stop}) but got {flat.shape[0]}")
             with torch.cuda.device(self.devices[0]):
-                return self.transform._apply(flat.to(self.devices[0]), slice_params(spread, start, stop))
+                return self.transform._apply(flat.to(self.devices[0]), slice_params(spread, start, stop), first_image=start)
         lay, spread, bounds = self.plan(tuple(batch.shape), self.devices[0])
         flat = batch.reshape(-1, *batch.shape[-3:]) if batch.ndim != 4 else batch
         outs = []
         for dev, (start, stop) in zip(self.devices, bounds):
             with torch.cuda.device(dev):
                 part = flat[start:stop].to(dev, non_blocking=True)
-                outs.append(self.transform._apply(part, slice_params(spread, start, stop, dev)))
+                outs.append(self.transform._apply(part, slice_params(spread, start, stop, dev), first_image=start))
         if gather_to is None:
             return outs
         whole = torch.cat([o.to(gather_to) for o in outs], dim=0)
