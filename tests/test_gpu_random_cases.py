@@ -94,3 +94,41 @@ def test_random_cases():
 def test_random_cases_large_images_and_single_channel():
     run_cases(2025, 24, big=True)
     run_cases(2026, 40, channels=(1,))
+
+
+def test_random_transforms_agree_across_entry_points():
+    """TritonFusedAugment on random image and video batches: the host-buffer call and the sharded
+    wrapper (three shards on one GPU) give the bits of the plain forward for the same seed."""
+    import triton_augment_b200 as ta
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(5)
+    for case in range(60):
+        dtype = [torch.float32, torch.float16, torch.uint8][int(rng.integers(0, 3))]
+        video = rng.random() < 0.4
+        n, t = int(rng.integers(1, 12)), int(rng.integers(1, 5))
+        h, w = int(rng.integers(24, 200)), int(rng.integers(24, 260))
+        if rng.random() < 0.5:
+            w = (w + 15) // 16 * 16
+        oh, ow = int(rng.integers(8, h + 1)), int(rng.integers(8, w + 1))
+        kw = {}
+        if rng.random() < 0.7:
+            kw = dict(degrees=float(rng.choice([5, 15, 90])), translate=(0.1, 0.1), scale=(0.8, 1.2),
+                      shear=float(rng.uniform(0, 10)), interpolation=str(rng.choice(["nearest", "bilinear"])),
+                      fill=float(rng.choice([0.0, 0.3])))
+        colour = dict(brightness=0.2, contrast=0.2, saturation=0.2, grayscale_p=0.3, mean=MEAN, std=STD) \
+            if rng.random() < 0.7 else {}
+        exact = bool(colour) and rng.random() < 0.3 and not (dtype == torch.uint8 and w % 16)
+        aug = ta.TritonFusedAugment(crop_size=(oh, ow), horizontal_flip_p=0.5,
+                                    contrast_mode="torchvision" if exact else "fast", fast_rng=bool(rng.random() < 0.5),
+                                    same_on_batch=bool(rng.random() < 0.2), same_on_frame=bool(rng.random() < 0.6),
+                                    **kw, **colour)
+        shape = (n, t, 3, h, w) if video else (n, 3, h, w)
+        g = torch.Generator().manual_seed(case)
+        x = (torch.randint(0, 256, shape, generator=g, dtype=torch.uint8) if dtype == torch.uint8
+             else torch.rand(shape, generator=g).to(dtype))
+        torch.manual_seed(case); want = aug(x.to(dev))
+        torch.manual_seed(case); host = aug.forward_host(x.pin_memory(), device=dev)
+        assert host.equal(want.cpu()), (case, dtype, shape, (oh, ow), kw)
+        if not aug.fast_rng:
+            torch.manual_seed(case); got = ta.ShardedAugment(aug, [0, 0, 0])(x.to(dev), gather_to=dev)
+            assert got.equal(want), (case, dtype, shape, (oh, ow), kw)
