@@ -112,7 +112,8 @@ def crop(image, top, left, height: int, width: int):
 
 
 def center_crop(image, output_size):
-    """Reference: functional.py:693-747."""
+    """Reference: functional.py:693-747.  Offsets are (size - crop) // 2 as there; torchvision
+    rounds (size - crop) / 2 instead, which differs by one pixel when the difference is odd."""
     _F._validate_image_tensor(image, "image")
     if isinstance(output_size, int):
         ch = cw = output_size
