@@ -257,3 +257,27 @@ def test_matrix_kernel_is_bit_identical_to_torch_ops():
         finally:
             F._MATRIX_KERNEL = old
         assert torch.equal(got.view(torch.int32), want.contiguous().view(torch.int32))
+
+
+def test_null_offset_vectors_mean_zero():
+    """C ABI: top, left and flip may be NULL (zero offsets, no flip), on the device entry point
+    and on the host-buffer one (whose upload plan reads them too)."""
+    from triton_augment_b200 import _lib
+    for dtype in (torch.float32, torch.float16, torch.uint8):
+        for (n, h, w, oh, ow) in ((3, 64, 96, 64, 96), (2, 70, 130, 33, 41), (2, 600, 1040, 300, 320)):
+            img = (torch.randint(0, 256, (n, 3, h, w), dtype=torch.uint8, device=DEV) if dtype == torch.uint8
+                   else torch.rand(n, 3, h, w, device=DEV).to(dtype))
+            work = torch.float32 if dtype == torch.uint8 else dtype
+            z, zf = torch.zeros(n, device=DEV), torch.zeros(n, dtype=torch.uint8, device=DEV)
+            for matrix in (None, torch.tensor([[0.98, 0.1, 2.0, -0.1, 0.97, -1.5]] * n, device=DEV)):
+                for bilinear in ((False, True) if matrix is not None else (False,)):
+                    a = torch.empty(n, 3, oh, ow, dtype=work, device=DEV)
+                    b = torch.empty_like(a)
+                    rest = (0.0, bilinear, 0, None, None, None, None, None, None)
+                    _lib.launch_fused(_lib.make_params(img, a, None, None, None, matrix, *rest), DEV)
+                    _lib.launch_fused(_lib.make_params(img, b, z, z, zf, matrix, *rest), DEV)
+                    assert torch.equal(a, b)
+                    host_in, host_out = img.cpu().pin_memory(), torch.empty(n, 3, oh, ow, dtype=work).pin_memory()
+                    host_matrix = matrix.cpu().contiguous() if matrix is not None else None
+                    _lib.launch_fused_host(_lib.make_params(host_in, host_out, None, None, None, host_matrix, *rest), DEV)
+                    assert torch.equal(host_out, b.cpu())
