@@ -7,7 +7,7 @@
  * replaces (paths relative to the reference project's root).
  *
  * Conventions
- *   - Every function returns TA_B200_OK (0) or a negative ta_b200_status.  Nothing
+ *   - Every function returns TA_B200_OK (0) or a negative ta_b200_status_code.  Nothing
  *     throws, exits, or synchronises the device unless the comment says so.
  *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
  *     Work is enqueued on it and the call returns immediately.
@@ -28,7 +28,7 @@ extern "C" {
 
 #define TA_B200_ABI_VERSION 1
 
-typedef enum ta_b200_status {
+typedef enum ta_b200_status_code {
     TA_B200_OK = 0,
     TA_B200_ERR_NULL = -1,         /* a required pointer is NULL */
     TA_B200_ERR_SHAPE = -2,        /* sizes not positive, or channels not in {1, 3} */
@@ -37,8 +37,9 @@ typedef enum ta_b200_status {
     TA_B200_ERR_CUDA = -5,         /* a CUDA runtime call failed; see ta_b200_last_error() */
     TA_B200_ERR_SCRATCH = -6,      /* scratch buffer missing or too small */
     TA_B200_ERR_DEVICE = -7,       /* current device is not compute capability 10.x */
-    TA_B200_ERR_TOO_LARGE = -8     /* a size exceeds what the entry point supports */
-} ta_b200_status;
+    TA_B200_ERR_TOO_LARGE = -8,    /* a size exceeds what the entry point supports */
+    TA_B200_ERR_TIMEOUT = -9       /* a kernel gave up a bounded wait: see ta_b200_status() */
+} ta_b200_status_code;
 
 /* TA_B200_U8: `in` holds bytes, `out` and the factor vectors are float32; a byte b enters the
  * pipeline as b / 255 (torchvision's ToTensor scaling), so the result equals the float32 call on
@@ -107,6 +108,21 @@ int ta_b200_abi_version(void);
 const char *ta_b200_last_error(void);
 
 /*
+ * Did a kernel of this library give up on the current device?  The staged kernels wait on
+ * shared-memory barriers with a time limit (2 s); a wait that runs out makes its thread block
+ * stop, leave the rest of its tiles unwritten and raise a flag in host-visible memory.  The
+ * launch itself has long returned TA_B200_OK by then, so the condition is reported here and by
+ * the NEXT call of ta_b200_fused_augment(), ta_b200_fused_augment_at(), ta_b200_gray_mean() on
+ * the device, and by ta_b200_fused_augment_host() at its final synchronisation: they return
+ * TA_B200_ERR_TIMEOUT and enqueue nothing until the flag is acknowledged.  Reading the flag
+ * does not synchronise anything; call this after your own stream synchronisation to learn
+ * whether the outputs produced since the last check are complete.
+ * acknowledge != 0 clears the flag.  Returns TA_B200_OK or TA_B200_ERR_TIMEOUT.
+ * No counterpart in the reference (a Triton launch has no waits of its own).
+ */
+int ta_b200_status(int acknowledge);
+
+/*
  * The fused pass on device buffers: inverse-affine / crop / flip gather with
  * nearest or bilinear sampling, then brightness, contrast, saturation,
  * per-image grayscale and normalize, one read of the source footprint and one
@@ -154,8 +170,12 @@ size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p);
  * stall or is forbidden.  For them the scratch lives inside the library, in a fixed 1 MiB
  * array of device memory that every GPU using the library holds from load to process exit.
  * The call itself allocates nothing and frees nothing, on the host's CUDA heap or through
- * any library; the caller still supplies the input image, the parameter vectors and
- * mean_out[n], exactly as for ta_b200_gray_mean().
+ * any library (the very first launch of a kernel on a device may still make the CUDA runtime
+ * load that kernel's code, so count on "allocates nothing" from the second call on); the
+ * caller still supplies the input image, the parameter vectors and mean_out[n], exactly as
+ * for ta_b200_gray_mean() - p->out may be NULL, the pre-pass writes no image.
+ * This entry always runs the gather kernel (the slower of the two that ta_b200_gray_mean()
+ * chooses from): the faster one needs megabytes of partial sums, more than the fixed array.
  *
  * Limit: counters plus partial sums must fit the array, i.e.
  *     round_up(4 n, 256) + 4 n min(128, ceil(oh ow / 4096))  <=  1 048 576 bytes
@@ -186,6 +206,10 @@ int ta_b200_gray_mean_static(const ta_b200_fused_params *p, float *mean_out, voi
  * .cuda() before calling the kernel (triton_augment/transforms.py:1498-1504).
  */
 int ta_b200_fused_augment_host(const ta_b200_fused_params *p);
+
+/* Frees what ta_b200_fused_augment_host() keeps on the current device between calls (staging
+ * buffers, three streams, events) after waiting for them; the next host call re-creates them. */
+int ta_b200_host_release(void);
 
 /*
  * Inverse affine matrices on the device in one launch: angle[n], translate[n,2],
@@ -257,6 +281,13 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
                                  int32_t oh, int32_t ow, float top, float left, int32_t flip,
                                  const float matrix[6], int32_t tile_x, int32_t tile_y,
                                  int32_t *row0, int32_t *xs, int32_t *xe, int32_t cap);
+/* Time limit of the kernels' barrier waits in nanoseconds (0 restores the default of 2 s), and the
+ * number of one tile whose producer warp leaves without signalling the tile's barrier in the staged
+ * kernels launched from now on (-1: none), process-wide.  With a small limit and a tile number a
+ * test makes a wait run out on purpose - nothing faults, traps or spins without bound: the
+ * thread block that owns the tile gives up after the limit, the launch completes, and
+ * ta_b200_status() / ta_b200_debug_counters()[3] report it. */
+int ta_b200_debug_wait(uint64_t limit_ns, int32_t skip_arrive_tile);
 /* Which kernel runs calls without a matrix (crop / flip / colour), process-wide: 0 = chosen
  * by size (default: large fp32 batches go through the staged kernel, everything else through
  * the crop kernels), 1 = always the crop kernels, 2 = the staged kernel whenever the tensors

@@ -177,3 +177,36 @@ def test_library_exports_every_declared_symbol():
     assert _lib.load().ta_b200_abi_version() == _lib.ABI_VERSION
     assert ctypes.sizeof(_lib.FusedParams) == 168       # sizeof(ta_b200_fused_params) on LP64
     assert ctypes.sizeof(_lib.SampleSpec) == 216        # sizeof(ta_b200_sample_spec) on LP64
+
+
+def test_a_failing_shard_does_not_stop_the_others():
+    """ShardedAugment runs every shard even when one raises and reports the failure per shard
+    (host logic only: the 'devices' are the CPU and the transform's kernel call is a stand-in)."""
+    import triton_augment_b200 as ta
+
+    class Stub(ta.TritonFusedAugment):
+        def _apply(self, image4d, spread_params, matrix=None, first_image=0):
+            if first_image == 4:                                     # the second of three shards
+                raise RuntimeError("device lost")
+            top = spread_params[4]
+            assert top.shape[0] == image4d.shape[0]
+            return image4d[:, :, :8, :8] + first_image
+
+    aug = Stub(crop_size=8, horizontal_flip_p=0.5, brightness=0.2, grayscale_p=0.1)
+    cpu = torch.device("cpu")
+    x = torch.zeros(10, 3, 16, 16)
+    sharder = ta.ShardedAugment(aug, [cpu, cpu, cpu])
+    with pytest.raises(ta.ShardError) as info:
+        sharder(x)
+    err = info.value
+    assert list(err.errors) == [1] and "device lost" in str(err) and "shard 1 (samples 4..7)" in str(err)
+    assert err.bounds == [(0, 4), (4, 7), (7, 10)]
+    assert err.outputs[1] is None
+    assert err.outputs[0].shape[0] == 4 and float(err.outputs[2].max()) == 7.0       # both others completed
+
+    class Fine(Stub):
+        def _apply(self, image4d, spread_params, matrix=None, first_image=0):
+            return image4d[:, :, :8, :8] + first_image
+
+    parts = ta.ShardedAugment(Fine(crop_size=8), [cpu, cpu])(x)
+    assert [p.shape[0] for p in parts] == [5, 5]

@@ -6,7 +6,9 @@ its scratch is a fixed array inside the library instead of a buffer the caller p
 test calls it through the C ABI and requires the same means as the ordinary entry point
 (ta_b200_gray_mean with caller-provided scratch) gives - on two calls in a row with different
 batch sizes, because the array is shared and keeps the previous call's contents.  It also
-checks that a batch too large for the fixed array is refused with a clear error.
+checks that a batch too large for the fixed array is refused with a clear error, and the
+property the entry point exists for: once warm, a call leaves the amount of free device memory
+and torch's allocator counters exactly where they were.
 
 This file sorts last on purpose: if it fails, a run that stops at the first failure has
 already run every other test.
@@ -70,3 +72,35 @@ def test_static_scratch_refuses_what_does_not_fit():
     rc = lib.ta_b200_gray_mean_static(C.byref(p), C.c_void_p(256), None)
     assert rc == -8
     assert b"built-in buffer" in lib.ta_b200_last_error()
+
+
+def test_static_scratch_call_allocates_no_device_memory():
+    """Free device memory (cudaMemGetInfo) and torch's allocator statistics are identical before
+    and after warm calls; p->out is NULL, which this entry accepts because it writes no image."""
+    from triton_augment_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    n = 6
+    image = torch.rand(n, 3, 96, 112, device=dev)
+    dummy = torch.empty(n, 3, 80, 96, device=dev)
+    top = torch.full((n,), 3.0, device=dev)
+    left = torch.full((n,), 5.0, device=dev)
+    bright = torch.full((n,), 1.1, device=dev)
+    means = torch.zeros(n, device=dev)
+    p = _lib.make_params(image, dummy, top, left, None, None, 0.0, False, _lib.APPLY_BRIGHTNESS, bright, None, None,
+                         None, None, None)
+    p.out = None
+    del dummy
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    call = lambda: lib.ta_b200_gray_mean_static(C.byref(p), C.c_void_p(means.data_ptr()), stream)
+    assert call() == 0, lib.ta_b200_last_error().decode()      # warm: symbol lookup, kernel code loaded
+    torch.cuda.synchronize()
+    first = means.clone()
+    torch.cuda.synchronize()
+    before = (torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize()
+    after = (torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+    assert after == before
+    assert means.equal(first) and bool((first > 0.3).all())

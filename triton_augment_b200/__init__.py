@@ -16,7 +16,7 @@ from .functional import (InterpolationMode, adjust_brightness, adjust_contrast, 
                          apply_saturation, center_crop, crop, fused_augment, horizontal_flip, normalize,
                          rgb_to_grayscale, rotate)
 from .graphs import GraphedTransform
-from .multi_gpu import ShardedAugment, shard_bounds
+from .multi_gpu import ShardedAugment, ShardError, shard_bounds
 from .transforms import (TritonCenterCrop, TritonColorJitter, TritonColorJitterNormalize, TritonFusedAugment,
                          TritonGrayscale, TritonNormalize, TritonRandomAffine, TritonRandomCrop,
                          TritonRandomCropFlip, TritonRandomGrayscale, TritonRandomHorizontalFlip,
@@ -33,5 +33,5 @@ __all__ = [
     "TritonRandomRotation", "TritonFusedAugment", "adjust_brightness", "adjust_contrast",
     "adjust_contrast_fast", "adjust_saturation", "normalize", "rgb_to_grayscale", "apply_brightness",
     "apply_contrast", "apply_saturation", "apply_normalize", "crop", "center_crop", "horizontal_flip",
-    "affine", "rotate", "fused_augment", "ShardedAugment", "shard_bounds", "GraphedTransform",
+    "affine", "rotate", "fused_augment", "ShardedAugment", "ShardError", "shard_bounds", "GraphedTransform",
 ]

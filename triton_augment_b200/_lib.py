@@ -18,6 +18,7 @@ ABI_VERSION = 1
 F32, F16, U8, U8_F16 = 0, 1, 2, 3       # U8 / U8_F16: bytes in (read as value / 255), float32 / float16 out
 NEAREST, BILINEAR = 0, 1
 CONTRAST_FAST, CONTRAST_MEAN = 0, 1
+ERR_TIMEOUT = -9
 APPLY_BRIGHTNESS, APPLY_CONTRAST, APPLY_SATURATION, APPLY_GRAYSCALE, APPLY_NORMALIZE = 1, 2, 4, 8, 16
 
 # Every symbol include/ta_b200.h declares.
@@ -26,7 +27,7 @@ SYMBOLS = (
     "ta_b200_gray_mean_scratch_bytes", "ta_b200_gray_mean_static", "ta_b200_fused_augment_host", "ta_b200_inverse_affine_matrix",
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
     "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
-    "ta_b200_debug_tile_shape",
+    "ta_b200_debug_tile_shape", "ta_b200_status", "ta_b200_host_release", "ta_b200_debug_wait",
 )
 
 
@@ -110,6 +111,12 @@ def load():
     lib.ta_b200_debug_tile_footprint.restype = C.c_int
     lib.ta_b200_debug_tile_shape.argtypes = [C.POINTER(C.c_int32)]
     lib.ta_b200_debug_tile_shape.restype = None
+    lib.ta_b200_status.argtypes = [C.c_int]
+    lib.ta_b200_status.restype = C.c_int
+    lib.ta_b200_host_release.argtypes = []
+    lib.ta_b200_host_release.restype = C.c_int
+    lib.ta_b200_debug_wait.argtypes = [C.c_uint64, C.c_int32]
+    lib.ta_b200_debug_wait.restype = C.c_int
     if lib.ta_b200_abi_version() != ABI_VERSION:
         raise RuntimeError(f"libta_b200.so has ABI {lib.ta_b200_abi_version()}, this package expects {ABI_VERSION}")
     _lib = lib
@@ -215,6 +222,35 @@ def host_upload(mode: int) -> None:
     """Host-buffer path: 1 = upload the box of each large image that is read where that is cheaper
     (default), 0 = whole images, 2 = boxes for every call on large images (tests)."""
     check(load().ta_b200_debug_host_upload(int(mode)), "ta_b200_debug_host_upload")
+
+
+def status(device=None, acknowledge: bool = False) -> bool:
+    """True if a kernel of the library gave up a bounded wait on ``device`` (default: the current
+    one) since the last acknowledged check, i.e. some launch left its output incomplete.  Does not
+    synchronise: call it after your own synchronisation point."""
+    with torch.cuda.device(device):
+        rc = load().ta_b200_status(int(acknowledge))
+    if rc not in (0, ERR_TIMEOUT):
+        check(rc, "ta_b200_status")
+    return rc == ERR_TIMEOUT
+
+
+def check_status(device=None) -> None:
+    """Raise ``LibraryError`` (and acknowledge) if ``status(device)`` is raised."""
+    if status(device, acknowledge=True):
+        raise LibraryError("a kernel of libta_b200 gave up a bounded barrier wait on this device: "
+                           "outputs produced since the last check may be incomplete")
+
+
+def host_release(device=None) -> None:
+    """Free the staging buffers and streams the host-buffer entry point keeps on ``device``."""
+    with torch.cuda.device(device):
+        check(load().ta_b200_host_release(), "ta_b200_host_release")
+
+
+def debug_wait(limit_ns: int = 0, skip_arrive_tile: int = -1) -> None:
+    """Barrier wait limit of the staged kernels and the tile whose barrier is never signalled (tests)."""
+    check(load().ta_b200_debug_wait(int(limit_ns), int(skip_arrive_tile)), "ta_b200_debug_wait")
 
 
 def debug_counters(reset: bool = False):

@@ -50,8 +50,7 @@ def up_to_date() -> bool:
 
 def _compile(unit: str, verbose: bool) -> str:
     out = os.path.join(OBJ, unit.replace(".cu", ".o"))
-    extra = os.environ.get("TA_B200_NVCC_FLAGS", "").split()     # e.g. -DTA_PLAIN_STORES for experiments
-    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, unit), "-o", out]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, unit), "-o", out]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)

@@ -22,8 +22,10 @@
 // aligned; fill != 0 at the image border) is gathered from global memory with per-tap bounds
 // tests instead: the producer marks it and the consumers take that path.
 //
-// Every wait is bounded; when one runs out the CTA raises an abort flag, counts the event in
-// the device counters and leaves (the host treats a non-zero count as a failed launch).
+// Every wait is bounded (KArgs::wait_ns).  When one runs out the CTA raises an abort flag, leaves
+// its remaining tiles unwritten, counts the event in the device counters and sets the host-mapped
+// status word, which the library's entry points read without synchronising: the next call on
+// the device (and ta_b200_status()) reports the time-out.
 #pragma once
 
 #include <cuda.h>
@@ -42,10 +44,7 @@ namespace ta {
 //   64x36 tiles, 18 warps: 283 / 261 us; 64x28, 14 warps: 306 / 281 us
 //   64x48 tiles, 24 warps, 2 stages (what then fits): 389 us; 64x24, 24 warps, 4 stages: 350 us
 //   64x28 tiles, 28 warps with one row pair per thread (64 registers): 322 / 289 us
-#ifndef TA_ROWS_PER_WARP
-#define TA_ROWS_PER_WARP 4
-#endif
-constexpr int kRowsPerWarp = TA_ROWS_PER_WARP;                 // a thread's pixels: this many rows of one column
+constexpr int kRowsPerWarp = 4;                                // a thread's pixels: this many rows of one column
 constexpr int kConsumerWarps = 2 * kTileH / kRowsPerWarp;      // two warps side by side per strip of rows
 static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are handled in pairs");
 constexpr int kStages = 3;
@@ -144,11 +143,12 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 
-// Wait for a phase of an mbarrier for at most ~2 s, giving up early when another thread
+// Wait for a phase of an mbarrier for at most limit_ns, giving up early when another thread
 // of the CTA has already given up.  No sleep between polls: a failed poll already parks the
 // warp for a while; sleeping on top of it (tried for producers, 256 ns, and for consumers, 64 ns)
 // changed nothing for heavy consumers and cost up to 8 % with light ones.
-__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                   unsigned long long limit_ns)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
@@ -156,7 +156,7 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint64_t *bar, uint32_t parit
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > 2000000000ull) break;
+            if (global_ns() - t0 > limit_ns) break;
         }
     }
     *abort_flag = 1;

@@ -105,7 +105,8 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         __syncwarp();
 
         // ---- (2) the stage must have been released by every consumer warp before it is overwritten
-        if (use > 0 && !mbar_wait_or_abort(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag)) return;
+        if (tile == k.skip_arrive_tile) return;      // diagnostics only: lets the consumers' wait run out
+        if (use > 0 && !mbar_wait_or_abort(&empty[p], (uint32_t)(use - 1) & 1u, abort_flag, k.wait_ns)) return;
 
         // ---- (3) copies; the warp's own arrival publishes the descriptor
         if (staged) {

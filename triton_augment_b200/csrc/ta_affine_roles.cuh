@@ -12,9 +12,7 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 __device__ __forceinline__ float2 bcast(float v)
 {
     float2 p = make_float2(v, v);
-#ifndef TA_NO_PINNED_PAIRS
     asm volatile("" : "+f"(p.x), "+f"(p.y));
-#endif
     return p;
 }
 
@@ -191,11 +189,7 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
     // fp32: packed colour arithmetic (measured 3 % faster than per-pixel scalar code, although
     // most of its operands are broadcast pairs); fp16 follows the reference's mixed-precision
     // steps per pixel.
-#ifdef TA_COLOUR_SCALAR
-    constexpr bool packed_colour = false;
-#else
     constexpr bool packed_colour = sizeof(T) == 4;
-#endif
     if constexpr (packed_colour) {
         float2 v2[C];
 #pragma unroll
@@ -207,17 +201,6 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
             if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
         }
     } else {
-#if defined(TA_HALF_COLOUR_SCALAR) || defined(TA_COLOUR_SCALAR)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            float v[C];
-            col.apply(k, smp[j], v);
-            if (j == 0 ? a_ok : b_ok) {
-#pragma unroll
-                for (int c = 0; c < C; ++c) Elem<T>::store(at(c, row + j), v[c]);
-            }
-        }
-#else
         float2 v2[C];
         col.apply2(k, smp[0], smp[1], v2);
 #pragma unroll
@@ -225,7 +208,6 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F
             if (a_ok) Elem<T>::store(at(c, row), v2[c].x);
             if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
         }
-#endif
     }
 }
 
@@ -250,7 +232,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     int it = 0;
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
         const int s = it % kStages, use = it / kStages;
-        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag)) return;
+        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag, k.wait_ns)) return;
         const S *stage = reinterpret_cast<const S *>(smem + s * Smem::stage);
         const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
         const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
@@ -364,7 +346,13 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     // memory: give each stage one more bounded chance to settle before the memory is released.
     __syncthreads();
     if (abort_flag) {
-        if (threadIdx.x == 0 && k.counters) atomicAdd(k.counters + kCntTimeout, 1ull);
+        if (threadIdx.x == 0) {
+            if (k.counters) atomicAdd(k.counters + kCntTimeout, 1ull);
+            if (k.status) {
+                *(volatile unsigned *)k.status = 1u;
+                __threadfence_system();
+            }
+        }
         if (threadIdx.x < kStages) {
             for (int i = 0; i < 4096; ++i)
                 if (mbar_try_wait(&full[threadIdx.x], 0) || mbar_try_wait(&full[threadIdx.x], 1)) break;

@@ -44,6 +44,11 @@ static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_S
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
 // 2 = the staged kernel whenever the tensors allow it (ta_b200_debug_crop_path).
 static std::atomic<int> g_crop_path{0};
+// Limit of the kernels' barrier waits, and (diagnostics) the tile whose producer withholds its
+// arrival in launches of the staged kernel: ta_b200_debug_wait().
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;
+static std::atomic<unsigned long long> g_wait_ns{kDefaultWaitNs};
+static std::atomic<int> g_skip_arrive_tile{-1};
 
 struct DeviceState {
     std::mutex mu;
@@ -51,6 +56,7 @@ struct DeviceState {
     int sm_count = 0;
     int cc_major = 0;
     unsigned long long *counters = nullptr;          // 4 words of device memory
+    unsigned *status = nullptr;                      // pinned, mapped host word the kernels set on a time-out
     // launch shape per kernel: resident CTAs per SM (0 = not prepared yet)
     unsigned char blocks_per_sm[kNumKinds][kNumDtypes][2][kNumFlagCombos + 1] = {};
 };
@@ -77,10 +83,24 @@ static int current_device(DeviceState **out, int *index)
         if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(counters)");
         e = cudaMemset(s.counters, 0, 4 * sizeof(unsigned long long));
         if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(counters)");
+        e = cudaHostAlloc((void **)&s.status, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaHostAlloc(status word)");
+        *s.status = 0u;
         s.probed = true;
     }
     *out = &s;
     if (index) *index = d;
+    return TA_B200_OK;
+}
+
+// A barrier wait of an earlier launch on this device ran out: that launch left part of its output
+// unwritten.  Read from the host-mapped word, so no synchronisation; stays raised until
+// ta_b200_status(1) acknowledges it.
+static int pending_timeout(const DeviceState &s)
+{
+    if (s.status && *(volatile unsigned *)s.status != 0u)
+        return fail(TA_B200_ERR_TIMEOUT, "a barrier wait of an earlier launch on this device ran out and that launch left "
+                    "its output incomplete; acknowledge with ta_b200_status(1)");
     return TA_B200_OK;
 }
 
@@ -140,7 +160,8 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
         return fail(TA_B200_ERR_SHAPE, "bad sizes n=%d h=%d w=%d oh=%d ow=%d", p->n, p->h, p->w, p->oh, p->ow);
     if ((double)p->h * p->w >= 2147483648.0 || (double)p->oh * p->ow >= 2147483648.0)
         return fail(TA_B200_ERR_TOO_LARGE, "one image plane must stay below 2^31 elements");
-    if (p->n > 0 && (!p->in || !p->out)) return fail(TA_B200_ERR_NULL, "in/out is NULL");
+    // (the grayscale-mean pre-pass writes no image: it needs `in` only)
+    if (p->n > 0 && (!p->in || (!p->out && !for_mean))) return fail(TA_B200_ERR_NULL, "in/out is NULL");
     if (p->c == 1 && (p->apply & (TA_B200_APPLY_SATURATION | TA_B200_APPLY_GRAYSCALE)))
         return fail(TA_B200_ERR_UNSUPPORTED, "saturation / grayscale need 3 channels");
     if ((p->apply & TA_B200_APPLY_BRIGHTNESS) && !p->brightness) return fail(TA_B200_ERR_NULL, "brightness is NULL");
@@ -170,6 +191,9 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
     k.bf = p->brightness; k.cf = p->contrast; k.sf = p->saturation; k.gray = p->gray;
     k.gray_mean = p->gray_mean;
     k.counters = s.counters;
+    k.status = s.status;
+    k.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+    k.skip_arrive_tile = g_skip_arrive_tile.load(std::memory_order_relaxed);
     k.n = p->n; k.h = p->h; k.w = p->w; k.oh = p->oh; k.ow = p->ow;
     k.fill = p->fill;
     for (int i = 0; i < 3; ++i) {
@@ -251,6 +275,8 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     if (p->n == 0) return TA_B200_OK;
     DeviceState *s = nullptr;
     rc = current_device(&s, nullptr);
+    if (rc != TA_B200_OK) return rc;
+    rc = pending_timeout(*s);
     if (rc != TA_B200_OK) return rc;
 
     KArgs k;
@@ -399,7 +425,7 @@ static int gray_mean_static(const ta_b200_fused_params *p, float *mean_out, cuda
     void *scratch = nullptr;
     rc = static_scratch_for_current_device(&scratch);
     if (rc != TA_B200_OK) return rc;
-    static DeviceState no_counters;                                    // only its null `counters` is read
+    static DeviceState no_counters;                                    // only its null `counters` and `status` are read
     KArgs k;
     fill_kargs(k, p, no_counters);
     unsigned *counters = (unsigned *)scratch;

@@ -184,6 +184,8 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     DeviceState *s = nullptr;
     int rc = current_device(&s, nullptr);
     if (rc != TA_B200_OK) return rc;
+    rc = pending_timeout(*s);
+    if (rc != TA_B200_OK) return rc;
     KArgs k;
     fill_kargs(k, p, *s);
     if (!k.staged_ok) return fail(TA_B200_ERR_UNSUPPORTED, "rows cannot be staged");

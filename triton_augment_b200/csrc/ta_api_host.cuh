@@ -71,6 +71,19 @@ static void source_box(const ta_b200_fused_params *hp, int i, int &x0, int &x1, 
 
 #define TA_CU(call, what) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return cuda_fail(e_, what); } while (0)
 
+// Whatever way fused_host() is left, nothing it enqueued may still be running: copies read and
+// write the caller's host buffers, and the next call reuses the device buffers without waiting.
+struct DrainPipe {
+    HostPipe &P;
+    explicit DrainPipe(HostPipe &p) : P(p) {}
+    ~DrainPipe()
+    {
+        if (P.up) cudaStreamSynchronize(P.up);
+        if (P.run) cudaStreamSynchronize(P.run);
+        if (P.down) cudaStreamSynchronize(P.down);
+    }
+};
+
 static int fused_host(const ta_b200_fused_params *hp)
 {
     // Validate with the device checks relaxed: gray_mean may be computed here.
@@ -98,6 +111,9 @@ static int fused_host(const ta_b200_fused_params *hp)
         }
         P.ready = true;
     }
+    rc = pending_timeout(*s);
+    if (rc != TA_B200_OK) return rc;
+    DrainPipe drain(P);          // every exit below, failures included, waits for the three streams
     const size_t es = ta::out_bytes(hp->dtype);          // output elements and factor vectors
     const size_t in_img = (size_t)hp->c * hp->h * hp->w * ta::in_bytes(hp->dtype), out_img = (size_t)hp->c * hp->oh * hp->ow * es;
     // Slice size: about 48 MiB of input per slice, at least 1 image, at least 4 slices when possible.
@@ -147,6 +163,10 @@ static int fused_host(const ta_b200_fused_params *hp)
         ta_b200_fused_params one = *hp;          // a slice: device input at a 256-byte aligned address
         one.n = slice;
         one.in = P.d_in[0];
+        // decided for the whole call before the first copy is enqueued
+        if (ta::in_bytes(hp->dtype) == 1 && !mean_staged_applicable(&one))
+            return fail(TA_B200_ERR_UNSUPPORTED, "the grayscale mean of a uint8 image needs rows of whole 16-byte units "
+                        "(width and plane size multiples of 16)");
         TA_CU(grow(&P.d_scratch, &P.scratch_cap, mean_scratch_need(&one)), "cudaMalloc(scratch)");
     }
 
@@ -248,6 +268,37 @@ static int fused_host(const ta_b200_fused_params *hp)
     }
     TA_CU(cudaStreamSynchronize(P.down), "cudaStreamSynchronize");
     TA_CU(cudaStreamSynchronize(P.run), "cudaStreamSynchronize");
+    TA_CU(cudaStreamSynchronize(P.up), "cudaStreamSynchronize");
+    return pending_timeout(*s);          // a slice whose kernel gave up left p->out incomplete
+}
+
+// Streams, events and device buffers of the host-buffer pipeline on the current device.
+static int host_release()
+{
+    int dev = -1;
+    TA_CU(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(TA_B200_ERR_DEVICE, "device index %d not supported", dev);
+    HostPipe &P = g_pipe[dev];
+    std::lock_guard<std::mutex> lock(P.mu);
+    { DrainPipe drain(P); }
+    for (int i = 0; i < 2; ++i) {
+        if (P.d_in[i]) TA_CU(cudaFree(P.d_in[i]), "cudaFree");
+        if (P.d_out[i]) TA_CU(cudaFree(P.d_out[i]), "cudaFree");
+        P.d_in[i] = P.d_out[i] = nullptr;
+        if (P.uploaded[i]) cudaEventDestroy(P.uploaded[i]);
+        if (P.computed[i]) cudaEventDestroy(P.computed[i]);
+        if (P.downloaded[i]) cudaEventDestroy(P.downloaded[i]);
+        P.uploaded[i] = P.computed[i] = P.downloaded[i] = nullptr;
+    }
+    if (P.d_params) TA_CU(cudaFree(P.d_params), "cudaFree");
+    if (P.d_scratch) TA_CU(cudaFree(P.d_scratch), "cudaFree");
+    P.d_params = P.d_scratch = nullptr;
+    P.in_cap = P.out_cap = P.params_cap = P.scratch_cap = 0;
+    if (P.up) cudaStreamDestroy(P.up);
+    if (P.run) cudaStreamDestroy(P.run);
+    if (P.down) cudaStreamDestroy(P.down);
+    P.up = P.run = P.down = nullptr;
+    P.ready = false;
     return TA_B200_OK;
 }
 
@@ -283,6 +334,25 @@ int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out, void *scra
 }
 
 int ta_b200_fused_augment_host(const ta_b200_fused_params *p) { return ta::fused_host(p); }
+
+int ta_b200_host_release(void) { return ta::host_release(); }
+
+int ta_b200_status(int acknowledge)
+{
+    ta::DeviceState *s = nullptr;
+    int rc = ta::current_device(&s, nullptr);
+    if (rc != TA_B200_OK) return rc;
+    rc = ta::pending_timeout(*s);
+    if (rc != TA_B200_OK && acknowledge) *(volatile unsigned *)s->status = 0u;
+    return rc;
+}
+
+int ta_b200_debug_wait(uint64_t limit_ns, int32_t skip_arrive_tile)
+{
+    ta::g_wait_ns.store(limit_ns ? (unsigned long long)limit_ns : ta::kDefaultWaitNs, std::memory_order_relaxed);
+    ta::g_skip_arrive_tile.store(skip_arrive_tile, std::memory_order_relaxed);
+    return TA_B200_OK;
+}
 
 int ta_b200_debug_host_upload(int32_t trimmed)
 {

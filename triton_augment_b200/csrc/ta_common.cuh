@@ -32,6 +32,9 @@ struct KArgs {
     const float *gray_mean;
     float *mean_partials;              // staged grayscale-mean pre-pass: [num_tiles][consumer warps] sums
     unsigned long long *counters;
+    unsigned *status;                  // host-mapped word: set to 1 when a bounded wait runs out (NULL: not reported)
+    unsigned long long wait_ns;        // limit of every barrier wait
+    int skip_arrive_tile;              // diagnostics: the producer of this tile leaves without its arrival (-1: never)
     int n, h, w, oh, ow;
     int tiles_x, tiles_y, num_tiles;
     int staged_ok;                     // source rows can be bulk-copied (16-byte aligned pitch and base)
@@ -85,40 +88,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 
 // ----------------------------------------------------------------------------- packed fp32
 // Two independent IEEE round-to-nearest operations per instruction on sm_100 (fma.rn.f32x2 and
-// friends).  -DTA_NO_PACKED builds the same arithmetic from scalar instructions.
-__device__ __forceinline__ float2 pk_fma(float2 a, float2 b, float2 c)
-{
-#ifdef TA_NO_PACKED
-    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
-#else
-    return __ffma2_rn(a, b, c);
-#endif
-}
-__device__ __forceinline__ float2 pk_mul(float2 a, float2 b)
-{
-#ifdef TA_NO_PACKED
-    return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y));
-#else
-    return __fmul2_rn(a, b);
-#endif
-}
-__device__ __forceinline__ float2 pk_add(float2 a, float2 b)
-{
-#ifdef TA_NO_PACKED
-    return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
-#else
-    return __fadd2_rn(a, b);
-#endif
-}
+// friends).
+__device__ __forceinline__ float2 pk_fma(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 pk_mul(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 pk_add(float2 a, float2 b) { return __fadd2_rn(a, b); }
 // Packed addition rounded towards minus infinity (the floor step of floor_magic, two at once).
-__device__ __forceinline__ float2 pk_add_rd(float2 a, float2 b)
-{
-#ifdef TA_NO_PACKED
-    return make_float2(__fadd_rd(a.x, b.x), __fadd_rd(a.y, b.y));
-#else
-    return __fadd2_rd(a, b);
-#endif
-}
+__device__ __forceinline__ float2 pk_add_rd(float2 a, float2 b) { return __fadd2_rd(a, b); }
 
 // ----------------------------------------------------------------------------- conversions without the XU pipe
 // float <-> int conversions issue at a quarter of the FMA rate.  For |v| < 2^22 the same
@@ -152,14 +127,8 @@ template <> struct Elem<float> {
         asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
         return v;
     }
-    static __device__ __forceinline__ void store(float *p, float v)
-    {
-#ifdef TA_STREAMING_STORES       // st.global.cs measured no better than plain stores (0-2 % worse)
-        __stcs(p, v);
-#else
-        *p = v;
-#endif
-    }
+    // plain store: st.global.cs measured no better for float (0-2 % worse)
+    static __device__ __forceinline__ void store(float *p, float v) { *p = v; }
 };
 template <> struct Elem<__half> {
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }

@@ -17,24 +17,15 @@
 
 namespace ta {
 
-#ifndef TA_VEC_ROWS
-#define TA_VEC_ROWS 2
-#endif
-#ifndef TA_VEC_BLOCKS_F32
-#define TA_VEC_BLOCKS_F32 3
-#endif
-#ifndef TA_VEC_BLOCKS_F16
-#define TA_VEC_BLOCKS_F16 2
-#endif
-constexpr int kVecRows = TA_VEC_ROWS;          // rows per warp strip
+constexpr int kVecRows = 2;                    // rows per warp strip
 
 // epv: elements per 16-byte vector.  blocks: resident CTAs per SM the register budget is set
 // for; the kernel waits on load latency, so fp32 gains from a third CTA (crop 112 of 224:
 // 248 -> 232 us for 4096 images; 256 -> 224: 242 -> 219 us for 1024 images), a fourth spills.
 // The fp16 kernel got slower with three (314 -> 329 us on 512 x 3 x 512^2 -> 448^2).
 template <typename T> struct VecTraits;
-template <> struct VecTraits<float> { static constexpr int epv = 4, blocks = TA_VEC_BLOCKS_F32; };
-template <> struct VecTraits<__half> { static constexpr int epv = 8, blocks = TA_VEC_BLOCKS_F16; };
+template <> struct VecTraits<float> { static constexpr int epv = 4, blocks = 3; };
+template <> struct VecTraits<__half> { static constexpr int epv = 8, blocks = 2; };
 
 // words[q .. q+4] of the 8 loaded words, shifted right by `sh` bits (0 or 16): the 4 output words.
 __device__ __forceinline__ void extract4(const uint32_t (&w)[8], int q, int sh, uint32_t (&o)[4])

@@ -27,10 +27,7 @@
 namespace ta {
 
 constexpr int kTileW = 64;       // output tile, pixels
-#ifndef TA_TILE_H
-#define TA_TILE_H 32
-#endif
-constexpr int kTileH = TA_TILE_H;
+constexpr int kTileH = 32;
 constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 groups of 8 rows)
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
 // Staged row pitch = width of every tensor-copy box, in elements.  A pitch that is a multiple

@@ -18,7 +18,29 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-__all__ = ["shard_bounds", "slice_params", "ShardedAugment"]
+import contextlib
+
+__all__ = ["shard_bounds", "slice_params", "ShardedAugment", "ShardError"]
+
+
+class ShardError(RuntimeError):
+    """One or more shards of a ``ShardedAugment`` call failed; the others ran to the end.
+
+    ``errors`` maps shard index -> the exception that shard raised, ``bounds`` holds every
+    shard's ``[start, stop)`` and ``outputs`` the per-shard results (None for failed shards),
+    so a caller can keep what succeeded and retry only the failed slices."""
+
+    def __init__(self, errors, bounds, outputs):
+        self.errors, self.bounds, self.outputs = dict(errors), list(bounds), list(outputs)
+        what = "; ".join(f"shard {i} (samples {bounds[i][0]}..{bounds[i][1]}): {type(e).__name__}: {e}"
+                         for i, e in sorted(self.errors.items()))
+        super().__init__(f"{len(self.errors)} of {len(bounds)} shards failed: {what}")
+
+
+def _on(device):
+    """Make ``device`` current for the block (nothing to do for a host 'device', which the
+    CPU tests of the sharding logic use)."""
+    return torch.cuda.device(device) if device.type == "cuda" else contextlib.nullcontext()
 
 
 def shard_bounds(total: int, parts: int, group: int = 1) -> List[Tuple[int, int]]:
@@ -110,15 +132,23 @@ class ShardedAugment:
             flat = local.reshape(-1, *local.shape[-3:]) if local.ndim != 4 else local
             if flat.shape[0] != stop - start:
                 raise ValueError(f"rank {self._rank} owns samples [{start}, {stop}) but got {flat.shape[0]}")
-            with torch.cuda.device(self.devices[0]):
+            with _on(self.devices[0]):
                 return self.transform._apply(flat.to(self.devices[0]), slice_params(spread, start, stop), first_image=start)
         lay, spread, bounds = self.plan(tuple(batch.shape), self.devices[0])
         flat = batch.reshape(-1, *batch.shape[-3:]) if batch.ndim != 4 else batch
-        outs = []
-        for dev, (start, stop) in zip(self.devices, bounds):
-            with torch.cuda.device(dev):
-                part = flat[start:stop].to(dev, non_blocking=True)
-                outs.append(self.transform._apply(part, slice_params(spread, start, stop, dev), first_image=start))
+        # Shards are independent: one that fails (a device out of memory, a bad device) is
+        # recorded and the loop goes on, so the other GPUs still deliver their slices.
+        outs, errors = [], {}
+        for i, (dev, (start, stop)) in enumerate(zip(self.devices, bounds)):
+            try:
+                with _on(dev):
+                    part = flat[start:stop].to(dev, non_blocking=True)
+                    outs.append(self.transform._apply(part, slice_params(spread, start, stop, dev), first_image=start))
+            except Exception as e:          # noqa: BLE001 - reported per shard below
+                outs.append(None)
+                errors[i] = e
+        if errors:
+            raise ShardError(errors, bounds, outs)
         if gather_to is None:
             return outs
         whole = torch.cat([o.to(gather_to) for o in outs], dim=0)
