@@ -46,7 +46,12 @@ CASES = [
     ("odd_sizes", 4, 517, 640, 401, 512, "float32"),
     ("c4_like_512_f16", 4, 512, 512, 448, 448, "float16"),
     ("scalar_stores", 3, 300, 340, 211, 203, "float32"),     # neither output dimension divisible by 16
+    ("variants_div16", 3, 272, 304, 208, 240, "float32"),    # both divisible by 16
 ]
+# Cases for which EVERY compiled fp32 variant of the reference kernel is pinned: 32 colour-flag
+# combinations x {nearest, bilinear}, the values at VARIANT_POINTS seeded pixel positions each.
+ALL_VARIANT_CASES = ("scalar_stores", "variants_div16")
+VARIANT_POINTS = 768
 # extra flag combinations (bit 0 brightness, 1 contrast, 2 saturation, 3 grayscale, 4 normalize) and
 # the subsampling stride per case
 EXTRA_FLAGS = {"scalar_stores": (5, 9, 14)}
@@ -80,6 +85,12 @@ def case_params(name, n, h, w, oh, ow):
                 flip=(np.arange(n) % 2 == 0), brightness=f(rng.uniform(0.8, 1.2, n)),
                 contrast=f(rng.uniform(0.8, 1.2, n)), saturation=f(rng.uniform(0.8, 1.2, n)),
                 gray=(np.arange(n) == 1))
+
+
+def variant_points(name, n, oh, ow):
+    """(image, row, column) of the pixels stored per variant of an ALL_VARIANT_CASES case."""
+    rng = np.random.default_rng(7 + sum(map(ord, name)))
+    return rng.integers(0, n, VARIANT_POINTS), rng.integers(0, oh, VARIANT_POINTS), rng.integers(0, ow, VARIANT_POINTS)
 
 
 def run(F, img, p, oh, ow, interp, colour, bits=31):
@@ -149,6 +160,19 @@ def main():
                 d = np.abs(res.cpu().numpy().astype(np.float32) - want.astype(np.float32))
                 print(f"{name}: oracle vs GPU reference, {interp} flags {bits}: max |diff| {d.max():.3e}, "
                       f"{int((d > 1e-5).sum())} of {d.size} above 1e-5")
+        if name in ALL_VARIANT_CASES:
+            pn, py, px = (torch.from_numpy(v).to(DEV) for v in variant_points(name, n, oh, ow))
+            worst = 0.0
+            for interp in ("nearest", "bilinear"):
+                vals = []
+                for bits in range(32):
+                    res = run(RF, img, p, oh, ow, interp, colour=True, bits=bits)
+                    vals.append(res[pn, :, py, px].cpu().numpy())                 # [points, 3]
+                    want = O.fused_augment(img.cpu().numpy(), p["top"], p["left"], oh, ow, p["flip"],
+                                           matrix=out[f"{name}|matrix"], interpolation=interp, **oracle_kwargs(p, bits, dtype))
+                    worst = max(worst, float(np.abs(res.cpu().numpy() - want).max()))
+                out[f"{name}|{interp}_variants"] = np.stack(vals)                 # [32, points, 3]
+            print(f"{name}: oracle vs GPU reference over all 64 fp32 variants: max |diff| {worst:.3e}")
     np.savez_compressed(args.out, **out)
     print("wrote", args.out, os.path.getsize(args.out) // 1024, "KiB")
 

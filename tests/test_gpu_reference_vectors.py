@@ -63,6 +63,30 @@ def test_nearest_geometry_hash(vectors):
 
 
 @pytest.mark.parametrize("interp", ["nearest", "bilinear"])
+def test_every_fp32_variant_against_stored_reference_values(vectors, interp):
+    """All 32 colour-flag combinations of either sampling mode, on one case whose output sizes are
+    multiples of 16 and one where neither is (the reference then compiles scalar stores and mixes
+    two coordinate contractions inside one launch): values of the reference's kernels at seeded
+    pixel positions.  Pins the per-variant contraction rule and the per-pixel one."""
+    import triton_augment_b200 as ta
+    import make_gpu_golden as G
+    for name in G.ALL_VARIANT_CASES:
+        if f"{name}|{interp}_variants" not in vectors.files:
+            pytest.fail(f"{name}: fixture has no per-variant values; regenerate with tests/golden/make_gpu_golden.py")
+        G_, (n, h, w, oh, ow), p, dtype = _inputs(vectors, name)
+        img = G.procedural_image(n, 3, h, w, dtype)
+        pn, py, px = (torch.from_numpy(v).to(G.DEV) for v in G.variant_points(name, n, oh, ow))
+        want_all = vectors[f"{name}|{interp}_variants"]
+        bad = []
+        for bits in range(32):
+            got = G.run(ta.functional, img, p, oh, ow, interp, colour=True, bits=bits)
+            err = float(np.abs(got[pn, :, py, px].cpu().numpy() - want_all[bits]).max())
+            if not err <= 1e-5:
+                bad.append((bits, err))
+        assert not bad, (name, interp, bad)
+
+
+@pytest.mark.parametrize("interp", ["nearest", "bilinear"])
 def test_full_pipeline_against_reference_output(vectors, interp):
     """All colour operations on; for the case whose output dimensions are not divisible by 16
     (the reference then mixes two coordinate contractions inside one launch) also three other

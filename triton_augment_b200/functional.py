@@ -65,7 +65,8 @@ def _convert_to_tensor(value, batch_size: int, dtype, device, name: str = "param
     if isinstance(value, torch.Tensor):
         if value.shape != (batch_size,):
             raise ValueError(f"{name} tensor must have shape ({batch_size},), got {value.shape}")
-        return value.to(device=device, dtype=dtype)
+        # dense: the library reads [n] vectors by pointer, so a strided view (params[:, 0], x[::2]) is copied
+        return value.to(device=device, dtype=dtype).contiguous()
     return torch.full((batch_size,), value, dtype=dtype, device=device)
 
 
@@ -85,7 +86,7 @@ def _pair_tensor(value, batch_size: int, device, name: str) -> torch.Tensor:
         if value.ndim == 1 and value.shape[0] == 2:
             return value.unsqueeze(0).repeat(batch_size, 1).to(device=device, dtype=torch.float32)
         if value.ndim == 2 and value.shape == (batch_size, 2):
-            return value.to(device=device, dtype=torch.float32)
+            return value.to(device=device, dtype=torch.float32).contiguous()
         raise ValueError(f"{name} tensor must be shape (2,) or ({batch_size}, 2), got {value.shape}")
     if len(value) != 2:
         raise ValueError(f"{name} must have 2 values, got {len(value)}")
