@@ -99,6 +99,13 @@ typedef struct ta_b200_fused_params {
                                  torchvision-exact formula of its stand-alone contrast kernel
                                  (kernels/color_normalize_kernel.py:37-77); needs gray_mean. */
     const float   *gray_mean; /* [n] per-image means written by ta_b200_gray_mean() */
+    /* -- fields below exist when struct_size == sizeof(ta_b200_fused_params); a caller built against
+     *    the layout that ended at gray_mean passes that smaller struct_size and they are not read -- */
+    float    fill_rgb[3];     /* with fill_per_channel != 0: value of out-of-image texels per channel
+                                 (torchvision's fill=[r, g, b]; the reference takes fill[0] for all
+                                 channels, triton_augment/functional.py:942-945, and notes per-channel
+                                 values as to do); 1-channel images use fill_rgb[0] */
+    uint32_t fill_per_channel;
 } ta_b200_fused_params;
 
 /* ABI version of the loaded library (TA_B200_ABI_VERSION it was built with). */
@@ -159,6 +166,28 @@ int ta_b200_fused_augment_at(const ta_b200_fused_params *p, uint32_t first_image
 int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out,
                       void *scratch, size_t scratch_bytes, void *stream);
 size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p);
+
+/*
+ * Mean-mode contrast (TA_B200_CONTRAST_MEAN) in one call: the grayscale-mean reduction of
+ * ta_b200_gray_mean() and the fused pass of ta_b200_fused_augment(), p->gray_mean not needed.
+ * Writes the means to mean_out[n] (device) on the way.  The result is bit-identical to
+ * ta_b200_gray_mean() followed by ta_b200_fused_augment().
+ * By default the call makes those two launches.  After ta_b200_mean_path(1) (or 2), float32
+ * images whose rows the staged kernels can read (16-byte aligned rows, see ta_b200_gray_mean) run
+ * both as ONE cooperative launch instead: every thread block alternates between reduction tiles of
+ * one image and fused-pass tiles of the image one (two) before it, so the second read of the source
+ * comes from the L2 cache and there is no launch in between; a block that needs a mean which is not
+ * final yet waits for it (bounded, see ta_b200_status()).  Same bits; on a B200 it measured slower
+ * than two launches on large batches (both passes are bound by instruction issue, not by HBM),
+ * which is why it is not the default.
+ * `scratch`: device memory, 256-byte aligned, ta_b200_fused_augment_mean_scratch_bytes(p) bytes,
+ * no initialisation needed, reusable by the next call on the same stream.
+ * Replaces: adjust_contrast's three passes inside a composed pipeline,
+ * triton_augment/functional.py:329-403 (the reference's fused kernel has the fast formula only).
+ */
+int ta_b200_fused_augment_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch,
+                               size_t scratch_bytes, void *stream);
+size_t ta_b200_fused_augment_mean_scratch_bytes(const ta_b200_fused_params *p);
 
 /*
  * ta_b200_gray_mean() for callers that cannot allocate device memory.  (No counterpart in
@@ -288,6 +317,10 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
  * thread block that owns the tile gives up after the limit, the launch completes, and
  * ta_b200_status() / ta_b200_debug_counters()[3] report it. */
 int ta_b200_debug_wait(uint64_t limit_ns, int32_t skip_arrive_tile);
+/* How ta_b200_fused_augment_mean() runs, process-wide: 0 = two launches (default), 1 / 2 = one
+ * cooperative launch where the images allow it, the fused pass one / two images behind the
+ * reduction.  Identical output. */
+int ta_b200_mean_path(int32_t one_launch);
 /* Which kernel runs calls without a matrix (crop / flip / colour), process-wide: 0 = chosen
  * by size (default: large fp32 batches go through the staged kernel, everything else through
  * the crop kernels), 1 = always the crop kernels, 2 = the staged kernel whenever the tensors
@@ -297,9 +330,9 @@ int ta_b200_debug_crop_path(int32_t path);
  * when the copy plan is cheaper than whole slices (default), 0 = upload every image whole, 2 =
  * boxes for every call on large images.  Identical output; for tests and measurements. */
 int ta_b200_debug_host_upload(int32_t trimmed);
-/* Tile shape of the staged affine kernel: out[0] = width, out[1] = height,
- * out[2] = row capacity, out[3] = row pitch in elements. */
-void ta_b200_debug_tile_shape(int32_t out[4]);
+/* Tile shape of the staged affine kernel: out[0] = width, out[1] = height, out[2] = row capacity,
+ * out[3], out[4], out[5] = staged row pitch in elements for 4-, 2- and 1-byte source elements. */
+void ta_b200_debug_tile_shape(int32_t out[6]);
 
 #ifdef __cplusplus
 }

@@ -80,8 +80,8 @@ def test_affine_and_rotate_vs_reference_vectors(functional_golden):
             assert (diff > 1e-6).mean() < 0.02, key
         else:
             assert diff.max() < 2e-4, (key, float(diff.max()))
-    with pytest.raises(NotImplementedError):
-        ta.rotate(img, 10.0, expand=True)
+    with pytest.raises(ValueError):                   # expand=True is built here (tests/test_gpu_extras.py); it needs the centre
+        ta.rotate(img, 10.0, expand=True, center=[3.0, 4.0])
     with pytest.raises(ValueError):
         ta.affine(img, 10.0, [0, 0], 1.0, [0, 0], interpolation="bicubic")
 

@@ -86,8 +86,11 @@ def test_constructor_validation_matches_reference():
         ta.TritonRandomAffine(degrees=10, scale=(1.2, 0.8))
     with pytest.raises(ValueError):
         ta.TritonRandomAffine(degrees=10, shear=(1, 2, 3))
-    with pytest.raises(NotImplementedError):
-        ta.TritonRandomRotation(10, expand=True)
+    assert ta.TritonRandomRotation(10, expand=True).expand          # built here; the reference raises NotImplementedError
+    with pytest.raises(ValueError):
+        ta.TritonRandomRotation(10, expand=True, center=(3, 4))
+    with pytest.raises(ValueError):
+        ta.TritonRandomCrop(8, padding=(1, 2, 3))
     with pytest.raises(ValueError):
         ta.TritonRandomHorizontalFlip(p=2)
     with pytest.raises(ValueError):
@@ -175,7 +178,8 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert _lib.load().ta_b200_abi_version() == _lib.ABI_VERSION
-    assert ctypes.sizeof(_lib.FusedParams) == 168       # sizeof(ta_b200_fused_params) on LP64
+    assert ctypes.sizeof(_lib.FusedParams) == 184       # sizeof(ta_b200_fused_params) on LP64 (168 before fill_rgb)
+    assert _lib.FusedParams.fill_rgb.offset == 168      # the older layout ends here and is still accepted
     assert ctypes.sizeof(_lib.SampleSpec) == 216        # sizeof(ta_b200_sample_spec) on LP64
 
 

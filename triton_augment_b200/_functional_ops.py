@@ -98,16 +98,28 @@ def rgb_to_grayscale(image, num_output_channels: int = 1, grayscale_mask=None):
     return out[:, 0:1, :, :] if num_output_channels == 1 else out
 
 
-def crop(image, top, left, height: int, width: int):
+def crop(image, top, left, height: int, width: int, fill=0.0):
     """Copy a window; ``top`` / ``left`` are ints or int tensors of shape ``(N,)``.
-    Reference: functional.py:610-690."""
+    Reference: functional.py:610-690.
+
+    The window may leave the image (negative offsets, or a window larger than the image): the
+    part outside reads ``fill`` (a number, or one value per channel; default 0, which is what
+    torchvision's ``crop`` pads with).  The reference notes this as future work
+    (functional.py:644-646) and reads out of bounds."""
     _F._validate_image_tensor(image, "image")
-    n = image.shape[0]
+    n, c, h, w = image.shape
     if height <= 0 or width <= 0:
         raise ValueError(f"Crop size must be positive, got height={height}, width={width}")
     top_t = _F._convert_to_tensor(top, n, torch.int32, image.device, "top").to(torch.float32)
     left_t = _F._convert_to_tensor(left, n, torch.int32, image.device, "left").to(torch.float32)
-    return _F._run_fused(image, height, width, top_t, left_t, None, None, False, 0.0, None, None, None, None,
+    fill = _F._fill_arg(fill, c)
+    if fill == 0.0 or fill == [0.0, 0.0, 0.0]:
+        return _F._run_fused(image, height, width, top_t, left_t, None, None, False, 0.0, None, None, None, None,
+                             None, None, 0)
+    # A fill value other than zero: the same window through the nearest-neighbour affine kernel with
+    # the identity matrix, which reads exactly the texels a crop reads and knows about fill values.
+    identity = torch.tensor([1.0, 0.0, 0.0, 0.0, 1.0, 0.0], device=image.device).repeat(n, 1)
+    return _F._run_fused(image, height, width, top_t, left_t, None, identity, False, fill, None, None, None, None,
                          None, None, 0)
 
 
@@ -151,10 +163,7 @@ def _apply_affine_matrix(image, matrix, interpolation="bilinear", fill=0.0):
     elif not (matrix.ndim == 2 and matrix.shape == (n, 6)):
         raise ValueError(f"matrix must be shape (6,) or ({n}, 6), got {matrix.shape}")
     matrix = matrix.to(dtype=torch.float32, device=image.device).contiguous()
-    if isinstance(fill, (list, tuple)):
-        fill_val = float(fill[0])      # the reference uses the first value only (functional.py:942-945)
-    else:
-        fill_val = 0.0 if fill is None else float(fill)
+    fill_val = _F._fill_arg(fill, image.shape[1])     # a sequence: one value per channel (the reference takes fill[0])
     return _F._run_fused(image, h, w, None, None, None, matrix, _F._is_bilinear(interpolation), fill_val, None,
                          None, None, None, None, None, 0)
 
@@ -168,12 +177,57 @@ def affine(image, angle, translate, scale, shear, interpolation=_F.Interpolation
     return _apply_affine_matrix(image, _F._get_inverse_affine_matrix(c, a, t, s, sh), interpolation, fill)
 
 
+def _expanded_size(matrix6, width: int, height: int):
+    """Size of the canvas that holds a whole ``width x height`` image after the transform whose
+    inverse is ``matrix6``: torchvision's rule (the corners' extent, snapped with a tolerance of
+    1e-4, evaluated in float32 like torchvision's _compute_affine_output_size)."""
+    m = torch.tensor(matrix6, dtype=torch.float32).view(2, 3)
+    half_w, half_h = 0.5 * width, 0.5 * height
+    pts = torch.tensor([[-half_w, -half_h, 1.0], [-half_w, half_h, 1.0], [half_w, half_h, 1.0], [half_w, -half_h, 1.0]])
+    new_pts = torch.matmul(pts, m.T)
+    half = torch.tensor([half_w, half_h])
+    lo, hi = new_pts.min(dim=0).values + half, new_pts.max(dim=0).values + half
+    tol = 1e-4
+    size = torch.ceil((hi / tol).trunc_() * tol) - torch.floor((lo / tol).trunc_() * tol)
+    return int(size[0]), int(size[1])
+
+
 def rotate(image, angle, interpolation=_F.InterpolationMode.NEAREST, expand: bool = False, center=None, fill=0.0):
-    """Rotate by ``angle`` degrees; ``expand=True`` is not supported.  Reference: functional.py:1117-1181."""
+    """Rotate by ``angle`` degrees about the image centre (or ``center``).  Reference:
+    functional.py:1117-1181, which raises NotImplementedError for ``expand=True``.
+
+    ``expand=True`` (built here): the result is large enough to hold the whole rotated image -
+    torchvision's size rule - and is the same resampling on that larger canvas: the kernel
+    already takes an output size and a (possibly negative, possibly half-pixel) window offset, so
+    the expanded image is the window centred on the input's centre.  One size per call, so the
+    angle must be a number (or a tensor holding one value for all images); ``center`` must be None."""
     _F._validate_image_tensor(image, "image")
-    if expand:
-        raise NotImplementedError("expand=True is not yet supported in Triton-Augment")
-    return affine(image, -angle, [0.0, 0.0], 1.0, [0.0, 0.0], interpolation, fill, center)
+    if not expand:
+        return affine(image, -angle, [0.0, 0.0], 1.0, [0.0, 0.0], interpolation, fill, center)
+    if center is not None:
+        raise ValueError("expand=True rotates about the image centre; center must be None")
+    if isinstance(angle, torch.Tensor):
+        if angle.numel() != 1 and not bool((angle == angle.reshape(-1)[0]).all()):
+            raise ValueError("expand=True needs one angle for the whole batch: every image gets the same output size")
+        angle = float(angle.reshape(-1)[0])
+    _F._check_interpolation(interpolation)
+    n, c, h, w = image.shape
+    # the matrix on the host for the size rule, in torchvision's float64 formula for a pure rotation
+    import math
+    rot = math.radians(-float(angle))
+    quarter = float(angle) % 360.0
+    if quarter in (0.0, 180.0):
+        ow, oh = w, h
+    elif quarter in (90.0, 270.0):               # exact quarter turns swap the sides (torchvision takes its rot90 path)
+        ow, oh = h, w
+    else:
+        ow, oh = _expanded_size([math.cos(rot), math.sin(rot), 0.0, -math.sin(rot), math.cos(rot), 0.0], w, h)
+    a, t, s, sh, ctr = _F._prepare_affine_params_to_tensor(-float(angle), [0.0, 0.0], 1.0, [0.0, 0.0], None, n, h, w, image.device)
+    matrix = _F._get_inverse_affine_matrix(ctr, a, t, s, sh).contiguous()
+    top = torch.full((n,), (h - oh) * 0.5, dtype=torch.float32, device=image.device)
+    left = torch.full((n,), (w - ow) * 0.5, dtype=torch.float32, device=image.device)
+    return _F._run_fused(image, oh, ow, top, left, None, matrix, _F._is_bilinear(interpolation), _F._fill_arg(fill, c),
+                         None, None, None, None, None, None, 0)
 
 
 apply_brightness = adjust_brightness

@@ -28,6 +28,7 @@ SYMBOLS = (
     "ta_b200_debug_counters", "ta_b200_debug_fused_checked", "ta_b200_debug_tile_footprint",
     "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
     "ta_b200_debug_tile_shape", "ta_b200_status", "ta_b200_host_release", "ta_b200_debug_wait",
+    "ta_b200_fused_augment_mean", "ta_b200_fused_augment_mean_scratch_bytes", "ta_b200_mean_path",
 )
 
 
@@ -42,6 +43,7 @@ class FusedParams(C.Structure):
         ("brightness", C.c_void_p), ("contrast", C.c_void_p), ("saturation", C.c_void_p), ("gray", C.c_void_p),
         ("mean", C.c_float * 3), ("std", C.c_float * 3),
         ("contrast_mode", C.c_int32), ("gray_mean", C.c_void_p),
+        ("fill_rgb", C.c_float * 3), ("fill_per_channel", C.c_uint32),
     ]
 
 
@@ -111,6 +113,12 @@ def load():
     lib.ta_b200_debug_tile_footprint.restype = C.c_int
     lib.ta_b200_debug_tile_shape.argtypes = [C.POINTER(C.c_int32)]
     lib.ta_b200_debug_tile_shape.restype = None
+    lib.ta_b200_fused_augment_mean.argtypes = [C.POINTER(FusedParams), C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.ta_b200_fused_augment_mean.restype = C.c_int
+    lib.ta_b200_fused_augment_mean_scratch_bytes.argtypes = [C.POINTER(FusedParams)]
+    lib.ta_b200_fused_augment_mean_scratch_bytes.restype = C.c_size_t
+    lib.ta_b200_mean_path.argtypes = [C.c_int32]
+    lib.ta_b200_mean_path.restype = C.c_int
     lib.ta_b200_status.argtypes = [C.c_int]
     lib.ta_b200_status.restype = C.c_int
     lib.ta_b200_host_release.argtypes = []
@@ -146,7 +154,17 @@ def make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits,
     p.oh, p.ow = out.shape[2], out.shape[3]
     p.inp, p.out = _ptr(image), _ptr(out)
     p.top, p.left, p.flip, p.matrix = _ptr(top), _ptr(left), _ptr(flip), _ptr(matrix)
-    p.fill = float(fill)
+    if isinstance(fill, (list, tuple)):               # per channel (1 value: all channels)
+        vals = [float(v) for v in fill]
+        if len(vals) not in (1, 3):
+            raise ValueError(f"fill must be a number or a sequence of 1 or 3 numbers, got {len(vals)} values")
+        vals = vals * 3 if len(vals) == 1 else vals
+        p.fill = vals[0]
+        p.fill_per_channel = 1
+        for i in range(3):
+            p.fill_rgb[i] = vals[i]
+    else:
+        p.fill = float(fill)
     p.interp = BILINEAR if bilinear else NEAREST
     p.apply = int(apply_bits)
     p.brightness, p.contrast, p.saturation, p.gray = _ptr(brightness), _ptr(contrast), _ptr(saturation), _ptr(gray)
@@ -191,6 +209,25 @@ def launch_gray_mean(params: FusedParams, device: torch.device) -> torch.Tensor:
         stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         check(lib.ta_b200_gray_mean(C.byref(params), _ptr(means), _ptr(scratch), need, stream), "ta_b200_gray_mean")
     return means
+
+
+def launch_fused_mean(params: FusedParams, device: torch.device) -> torch.Tensor:
+    """Mean-mode contrast in one library call (one cooperative launch where the images allow it):
+    reduction + fused pass; returns the fp32 ``[n]`` means it computed on the way."""
+    lib = load()
+    with torch.cuda.device(device):
+        need = int(lib.ta_b200_fused_augment_mean_scratch_bytes(C.byref(params)))
+        scratch = torch.empty(need, dtype=torch.uint8, device=device)
+        means = torch.empty(params.n, dtype=torch.float32, device=device)
+        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        check(lib.ta_b200_fused_augment_mean(C.byref(params), _ptr(means), _ptr(scratch), need, stream),
+              "ta_b200_fused_augment_mean")
+    return means
+
+
+def mean_path(one_launch) -> None:
+    """ta_b200_fused_augment_mean: 0 two launches (default), 1 / 2 one cooperative launch, the fused pass one / two images behind."""
+    check(load().ta_b200_mean_path(int(one_launch)), "ta_b200_mean_path")
 
 
 def inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.Tensor:
@@ -261,7 +298,8 @@ def debug_counters(reset: bool = False):
 
 
 def tile_shape():
-    buf = (C.c_int32 * 4)()
+    """(tile width, tile height, source-row capacity, staged row pitch for 4-, 2-, 1-byte elements)."""
+    buf = (C.c_int32 * 6)()
     load().ta_b200_debug_tile_shape(buf)
     return tuple(int(x) for x in buf)
 

@@ -22,22 +22,63 @@ def _draw_offsets(lay, h, w, th, tw, dtype):
     return top, left
 
 
-class TritonRandomCrop(T._BatchAware):
-    """Random ``size`` window per image.  Reference: transforms.py:899-989."""
+def _padding_ltrb(padding):
+    """torchvision's padding argument -> (left, top, right, bottom)."""
+    if padding is None:
+        return 0, 0, 0, 0
+    if isinstance(padding, int):
+        return padding, padding, padding, padding
+    p = [int(v) for v in padding]
+    if len(p) == 1:
+        return p[0], p[0], p[0], p[0]
+    if len(p) == 2:
+        return p[0], p[1], p[0], p[1]
+    if len(p) == 4:
+        return tuple(p)
+    raise ValueError(f"Padding must be an int or a 1, 2, or 4 element sequence, got {len(p)} elements")
 
-    def __init__(self, size, same_on_batch: bool = False, same_on_frame: bool = True):
+
+class TritonRandomCrop(T._BatchAware):
+    """Random ``size`` window per image.  Reference: transforms.py:899-989.
+
+    ``padding``, ``pad_if_needed`` and ``fill`` (keyword arguments after the reference's; constant
+    padding only) follow torchvision's RandomCrop: the window is drawn from the image padded by
+    ``padding`` (and, with ``pad_if_needed``, by whatever a too-small side lacks, on both ends),
+    and whatever part of it lies outside the image reads ``fill``.  Nothing is padded in memory:
+    the kernel takes the window's offset, which may be negative.  Without them an image smaller
+    than the window raises, as in the reference (which has no padding yet: functional.py:644-646)."""
+
+    def __init__(self, size, same_on_batch: bool = False, same_on_frame: bool = True, padding=None,
+                 pad_if_needed: bool = False, fill=0.0):
         super().__init__(same_on_batch, same_on_frame)
         self.size = T._size_pair(size)
+        self.padding = _padding_ltrb(padding)
+        if min(self.padding) < 0:
+            raise ValueError("padding must not be negative")
+        self.pad_if_needed = bool(pad_if_needed)
+        self.fill = fill
 
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         lay = self._layout(image)
         h, w = lay.image.shape[2:]
         th, tw = self.size
-        if h < th or w < tw:
+        left_pad, top_pad, right_pad, bottom_pad = self.padding
+        if self.pad_if_needed:                    # torchvision pads a short side by the missing amount at both ends
+            if h + top_pad + bottom_pad < th:
+                d = th - (h + top_pad + bottom_pad)
+                top_pad, bottom_pad = top_pad + d, bottom_pad + d
+            if w + left_pad + right_pad < tw:
+                d = tw - (w + left_pad + right_pad)
+                left_pad, right_pad = left_pad + d, right_pad + d
+        ph, pw = h + top_pad + bottom_pad, w + left_pad + right_pad
+        if ph < th or pw < tw:
             raise ValueError(f"Image size ({h}, {w}) is smaller than crop size ({th}, {tw}). "
-                             f"Padding not yet supported in MVP.")
-        top, left = _draw_offsets(lay, h, w, th, tw, torch.int32)
-        return lay.restore(F.crop(lay.image, lay.spread(top), lay.spread(left), th, tw))
+                             f"Padding not yet supported in MVP." if (ph, pw) == (h, w) else
+                             f"Padded image size ({ph}, {pw}) is smaller than crop size ({th}, {tw}).")
+        top, left = _draw_offsets(lay, ph, pw, th, tw, torch.int32)
+        if top_pad or left_pad:
+            top, left = top - top_pad, left - left_pad
+        return lay.restore(F.crop(lay.image, lay.spread(top), lay.spread(left), th, tw, fill=self.fill))
 
     def __repr__(self):
         return f"{self.__class__.__name__}(size={self.size}, " + self._tail()
@@ -156,7 +197,7 @@ class TritonRandomAffine(T._BatchAware):
             else:
                 raise ValueError("shear should be a single number or a sequence of length 2 or 4.")
         self.interpolation = interpolation
-        self.fill = float(fill)
+        self.fill = [float(v) for v in fill] if isinstance(fill, (list, tuple)) else float(fill)   # number, or one per channel
         self.center = center
 
     def _get_params(self, param_count: int, device, img_size):
@@ -195,14 +236,36 @@ class TritonRandomAffine(T._BatchAware):
 
 
 class TritonRandomRotation(TritonRandomAffine):
-    """Random rotation only.  Reference: transforms.py:1822-1902."""
+    """Random rotation only.  Reference: transforms.py:1822-1902.
+
+    ``expand=True`` (the reference raises NotImplementedError) enlarges the result to hold the
+    whole rotated image.  All images of a call then need one output size, i.e. one angle: it
+    works when a call draws a single parameter set (``same_on_batch=True`` with
+    ``same_on_frame=True``, or a single image) and raises ValueError otherwise.  The angle is read
+    back to the host to size the output (one device-to-host read per call)."""
 
     def __init__(self, degrees, interpolation=InterpolationMode.NEAREST, expand: bool = False, center=None,
                  fill: float = 0.0, same_on_batch: bool = False, same_on_frame: bool = True):
-        if expand:
-            raise NotImplementedError("expand=True is not yet supported in Triton-Augment")
+        if expand and center is not None:
+            raise ValueError("expand=True rotates about the image centre; center must be None")
+        self.expand = bool(expand)
         super().__init__(degrees=degrees, translate=None, scale=None, shear=None, interpolation=interpolation,
                          fill=fill, center=center, same_on_batch=same_on_batch, same_on_frame=same_on_frame)
+
+    def forward(self, img: torch.Tensor) -> torch.Tensor:
+        if not self.expand:
+            return super().forward(img)
+        lay = self._layout(img)
+        if lay.count != 1:
+            raise ValueError("expand=True gives every image of a call the same output size, so the call must draw ONE "
+                             f"angle (same_on_batch=True and same_on_frame=True, or a single image); this call draws {lay.count}")
+        h, w = lay.image.shape[2:]
+        angle = float(self._get_params(1, lay.param_device, (h, w))[0][0])
+        # affine(angle) is rotate(-angle): the class applies the drawn angle the way its parent does
+        out = F.rotate(lay.image, -angle, interpolation=self.interpolation, expand=True, fill=self.fill)
+        if lay.was_3d:
+            return out.squeeze(0)
+        return out.reshape(*lay.shape[:-2], *out.shape[-2:]) if len(lay.shape) == 5 else out
 
     def __repr__(self):
         return (f"{self.__class__.__name__}(degrees={self.degrees}, interpolation={self.interpolation}, "

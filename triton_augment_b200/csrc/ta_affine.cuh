@@ -44,6 +44,7 @@ namespace ta {
 //   64x36 tiles, 18 warps: 283 / 261 us; 64x28, 14 warps: 306 / 281 us
 //   64x48 tiles, 24 warps, 2 stages (what then fits): 389 us; 64x24, 24 warps, 4 stages: 350 us
 //   64x28 tiles, 28 warps with one row pair per thread (64 registers): 322 / 289 us
+//   64x32 tiles, 8 warps with four row pairs per thread: bilinear +2 %, half pixels +12 %
 constexpr int kRowsPerWarp = 4;                                // a thread's pixels: this many rows of one column
 constexpr int kConsumerWarps = 2 * kTileH / kRowsPerWarp;      // two warps side by side per strip of rows
 static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are handled in pairs");
@@ -54,7 +55,7 @@ constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one produce
 // images; S = uint8_t with T = float or half reads bytes and scales them by 1/255 (what ToTensor does
 // before the reference's pipeline) on the way from shared memory to registers.
 template <typename S> struct Src {
-    static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : kPitch;   // staged row pitch, elements
+    static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : sizeof(S) == 2 ? kPitchBytes2 : kPitch;   // staged row pitch, elements
     static constexpr int plane = kMaxRows * pitch;                         // elements per channel per stage
     static constexpr int chunk = 16 / (int)sizeof(S);                      // elements per 16 bytes
 };
@@ -64,6 +65,8 @@ constexpr float kInv255 = 1.0f / 255.0f;
 template <typename T, typename S> struct Px {
     static constexpr bool scaled = false;
     static __device__ __forceinline__ T from(S v) { return v; }
+    // two texels as a pixel pair
+    static __device__ __forceinline__ typename PairOf<T>::type pair(S a, S b) { return PairOf<T>::make(a, b); }
     // two texels as blend operands
     static __device__ __forceinline__ float2 raw_f2(S a, S b) { return make_float2(Elem<T>::to_f(a), Elem<T>::to_f(b)); }
     static __device__ __forceinline__ S lds(uint32_t addr) { return Elem<T>::lds(addr); }
@@ -76,6 +79,11 @@ template <> struct Px<float, uint8_t> {
     static constexpr bool scaled = true;        // blends run on the raw 0..255 values, scaled once afterwards
     static __device__ __forceinline__ float biased(uint8_t v) { return __uint_as_float(0x4B000000u | (uint32_t)v); }
     static __device__ __forceinline__ float from(uint8_t v) { return __fmaf_rn(biased(v), kInv255, -8388608.0f * kInv255); }
+    static __device__ __forceinline__ float2 pair(uint8_t a, uint8_t b)
+    {
+        return pk_fma(make_float2(biased(a), biased(b)), make_float2(kInv255, kInv255),
+                      make_float2(-8388608.0f * kInv255, -8388608.0f * kInv255));
+    }
     static __device__ __forceinline__ float2 raw_f2(uint8_t a, uint8_t b)
     {
         return pk_add(make_float2(biased(a), biased(b)), make_float2(-8388608.0f, -8388608.0f));
@@ -93,6 +101,7 @@ template <> struct Px<float, uint8_t> {
 template <> struct Px<__half, uint8_t> {
     static constexpr bool scaled = true;
     static __device__ __forceinline__ __half from(uint8_t v) { return __float2half_rn(Px<float, uint8_t>::from(v)); }
+    static __device__ __forceinline__ __half2 pair(uint8_t a, uint8_t b) { return PairOf<__half>::from_f2(Px<float, uint8_t>::pair(a, b)); }
     static __device__ __forceinline__ float2 raw_f2(uint8_t a, uint8_t b) { return Px<float, uint8_t>::raw_f2(a, b); }
     static __device__ __forceinline__ uint8_t lds(uint32_t addr) { return Px<float, uint8_t>::lds(addr); }
 };
@@ -110,9 +119,11 @@ struct alignas(64) TMaps {
 template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int n, x0, y0;        // image, first output column / row of the tile
     int rows, row0;       // staged source rows (rows == 0: gather this tile from global memory)
-    int window;           // every row starts at column xs0: texel (y, x) sits at element
-    int xs0;              //   (y - row0) * pitch + (x - xs0) of a channel plane
-    int pad;
+    int window;           // bit 0: every row starts at column xs0: texel (y, x) sits at element
+    int xs0;              //   (y - row0) * pitch + (x - xs0) of a channel plane.  window bit 1: a tile of the
+    int real_tile;        //   reduction phase (two-phase kernel).  real_tile = n * tiles per image + tile in image
+    int r_count;          // two-phase kernel: > 0 on this CTA's last reduction tile of an image = how many it had
+    int pad3[3];
     Geom g;
     Colour<T, C, F> col;
     int rowoff[kMaxRows + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
@@ -184,11 +195,13 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
     const S *img = (const S *)k.in + (size_t)n * C * k.h * k.w;
     T *out = (T *)k.out + (size_t)n * C * k.oh * k.ow;
     const size_t plane = (size_t)k.h * k.w, oplane = (size_t)k.oh * k.ow;
-    const T fillv = Elem<T>::from_f(MODE == 0 ? 0.0f : k.fill);
-    // texel (xx, yy) of a channel plane as a pixel value; outside the image: the fill value
-    auto tap = [&](const S *pl, int xx, int yy) -> T {
+    T fillv[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) fillv[c] = Elem<T>::from_f(MODE == 0 ? 0.0f : k.fill[c]);
+    // texel (xx, yy) of channel plane c as a pixel value; outside the image: the channel's fill value
+    auto tap = [&](const S *pl, int c, int xx, int yy) -> T {
         const bool ok = (unsigned)xx < (unsigned)k.w && (unsigned)yy < (unsigned)k.h;
-        return ok ? Px<T, S>::from(__ldg(pl + (size_t)yy * k.w + xx)) : fillv;
+        return ok ? Px<T, S>::from(__ldg(pl + (size_t)yy * k.w + xx)) : fillv[c];
     };
     const float xi = img_x(g, k.ow, x);
     const float xc = centred(xi, g.half_w);
@@ -197,25 +210,27 @@ __device__ __forceinline__ void affine_rows_direct(const KArgs &k, const Geom &g
         if (y >= k.oh) break;
         const float yi = img_y(g, y);
         const float yc = centred(yi, g.half_h);
-        float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, F>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
+        // (a reduction adds up the samples of its stand-alone kernel, compiled for brightness or nothing)
+        constexpr unsigned RF = REDUCE ? (F & kB) : F;
+        float sx = MODE == 0 ? truncf(xi) : src_coord_r<CoordRecipe<MODE, RF>::x>(xc, yc, g.a, g.b, g.c, g.half_w);
         if constexpr (MIX) {
             if (late_x(k, k.lin_base + (uint32_t)n * (uint32_t)oplane + (uint32_t)(y * k.ow + x)))
                 sx = src_coord_r<1>(xc, yc, g.a, g.b, g.c, g.half_w);
         }
-        const float sy = MODE == 0 ? truncf(yi) : src_coord_r<CoordRecipe<MODE, F>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
+        const float sy = MODE == 0 ? truncf(yi) : src_coord_r<CoordRecipe<MODE, RF>::y>(xc, yc, g.d, g.e, g.f, g.half_h);
         T s[C];
         if (MODE != 2) {
             const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
 #pragma unroll
-            for (int c = 0; c < C; ++c) s[c] = tap(img + c * plane, xn, yn);
+            for (int c = 0; c < C; ++c) s[c] = tap(img + c * plane, c, xn, yn);
         } else {
             const int x0 = __float2int_rd(sx), y0 = __float2int_rd(sy);
             const float dx = sx - (float)x0, dy = sy - (float)y0;
 #pragma unroll
             for (int c = 0; c < C; ++c) {
                 const S *pl = img + c * plane;
-                s[c] = Elem<T>::from_f(blend4(Elem<T>::to_f(tap(pl, x0, y0)), Elem<T>::to_f(tap(pl, x0 + 1, y0)),
-                                              Elem<T>::to_f(tap(pl, x0, y0 + 1)), Elem<T>::to_f(tap(pl, x0 + 1, y0 + 1)),
+                s[c] = Elem<T>::from_f(blend4(Elem<T>::to_f(tap(pl, c, x0, y0)), Elem<T>::to_f(tap(pl, c, x0 + 1, y0)),
+                                              Elem<T>::to_f(tap(pl, c, x0, y0 + 1)), Elem<T>::to_f(tap(pl, c, x0 + 1, y0 + 1)),
                                               dx, dy));
             }
         }

@@ -9,7 +9,30 @@
 
 namespace ta {
 
-template <typename T, int C, int MODE, unsigned F, typename S>
+// Two-phase kernel (TWO): the tile sequence of a launch interleaves, image by image, the tiles
+// of the grayscale-mean reduction (phase 1) with the tiles of the fused pass (phase 0) of the
+// image before: R(0) | R(1) F(0) | R(2) F(1) | ... | F(n-1).  An F tile needs its image's mean,
+// which the consumer warp that writes the image's last partial sum finishes; every CTA meets its
+// own R tiles of an image before its F tiles of that image, so with all CTAs resident (the
+// launch is cooperative) the wait below always ends - and it is bounded like every other wait.
+// lag: how many images the fused pass runs behind the reduction (<= the number of images).
+// r_start: where the reduction tiles of image n begin in the sequence (they are tpi consecutive numbers).
+__device__ __forceinline__ void two_phase_tile(int v, int n_images, int tpi, int lag, int &phase, int &n, int &t, int &r_start)
+{
+    const int head = lag * tpi, tail_start = head + (n_images - lag) * 2 * tpi;
+    if (v < head) { phase = 1; n = v / tpi; t = v - n * tpi; r_start = n * tpi; }
+    else if (v < tail_start) {
+        const int u = v - head, slot = u / (2 * tpi), w = u - slot * 2 * tpi;
+        if (w < tpi) { phase = 1; n = lag + slot; t = w; r_start = v - w; }
+        else         { phase = 0; n = slot; t = w - tpi; r_start = 0; }
+    } else {
+        const int u = v - tail_start, q = u / tpi;
+        phase = 0; n = n_images - lag + q; t = u - q * tpi; r_start = 0;
+    }
+}
+
+
+template <typename T, int C, int MODE, unsigned F, typename S, bool TWO>
 __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &maps, unsigned char *smem,
                                                 uint64_t *full, uint64_t *empty, volatile int *abort_flag, int p)
 {
@@ -36,7 +59,42 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
 
     int use = 0;
     for (int tile = first; tile < k.num_tiles; tile += step, ++use) {
-        if (n != cur_n) {                                   // per-image parameters: reload on change only
+        int phase = 0, real_tile = tile, r_count = 0;
+        if constexpr (TWO) {
+            int t, r_start;
+            two_phase_tile(tile, k.n, tiles_per_img, min(k.mean_lag, k.n), phase, n, t, r_start);
+            if (phase == 1 && tile + (int)gridDim.x >= r_start + tiles_per_img) {
+                // this CTA's last reduction tile of the image: tell the consumers, and how many there were
+                const int first_own = r_start + (((int)blockIdx.x - r_start) % (int)gridDim.x + (int)gridDim.x) % (int)gridDim.x;
+                r_count = (tile - first_own) / (int)gridDim.x + 1;
+            }
+            ty = t / k.tiles_x;
+            tx = t - ty * k.tiles_x;
+            real_tile = n * tiles_per_img + t;
+            if (2 * n + phase != cur_n) {
+                load_geom(g, k, n, MODE != 0);
+                if (phase == 0) {
+                    // the image's mean must be final (written by another SM: volatile flag, then a fence)
+                    int ok = 1;
+                    if (lane == 0) {
+                        const volatile unsigned *ready = k.mean_ready + n;
+                        ok = *ready != 0u;
+                        if (!ok) {
+                            const unsigned long long t0 = global_ns();
+                            for (int i = 0; i < (1 << 24) && !ok; ++i) {
+                                ok = *ready != 0u;
+                                if (!ok && (i & 63) == 63 && (*abort_flag || global_ns() - t0 > k.wait_ns)) break;
+                            }
+                        }
+                        __threadfence();
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) { *abort_flag = 1; return; }
+                }
+                col.init(k, n);             // (phase 1 reads no mean: brightness only)
+                cur_n = 2 * n + phase;
+            }
+        } else if (n != cur_n) {                            // per-image parameters: reload on change only
             load_geom(g, k, n, MODE != 0);
             col.init(k, n);
             cur_n = n;
@@ -89,7 +147,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             }
             // fill != 0 cannot rely on the copy's zero fill: stage only tiles that stay inside the image
             inside = inside && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
-            staged = staged && (MODE == 0 || k.fill == 0.0f || inside);
+            staged = staged && (MODE == 0 || (k.fill[0] == 0.0f && k.fill[1] == 0.0f && k.fill[2] == 0.0f) || inside);
         }
         if (lane == 0) {
             ti->g = g;
@@ -99,8 +157,10 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             ti->y0 = ty * kTileH;
             ti->rows = staged ? fp.rows : 0;
             ti->row0 = fp.row0;
-            ti->window = window ? 1 : 0;
+            ti->window = (window ? 1 : 0) | (phase << 1);
             ti->xs0 = gxs;
+            ti->real_tile = real_tile;
+            ti->r_count = r_count;
         }
         __syncwarp();
 
@@ -129,11 +189,13 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         if (lane == 0) mbar_arrive(&full[p]);
 
         // next tile of this warp
-        tx += step_tx;
-        if (tx >= k.tiles_x) { tx -= k.tiles_x; ++ty; }
-        ty += step_ty;
-        if (ty >= k.tiles_y) { ty -= k.tiles_y; ++n; }
-        n += step_n;
+        if constexpr (!TWO) {
+            tx += step_tx;
+            if (tx >= k.tiles_x) { tx -= k.tiles_x; ++ty; }
+            ty += step_ty;
+            if (ty >= k.tiles_y) { ty -= k.tiles_y; ++n; }
+            n += step_n;
+        }
     }
     if (lane == 0 && k.counters) {
         if (n_staged) atomicAdd(k.counters + kCntStaged, n_staged);

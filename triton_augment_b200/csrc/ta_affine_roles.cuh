@@ -69,26 +69,28 @@ template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSample
     static constexpr int PITCH = Src<S>::pitch, PLANE = Src<S>::plane;
     static constexpr uint32_t ES = sizeof(S), ROWB = ES * PITCH, PLANEB = ES * PLANE;
     using P = Px<T, S>;
+    using Pair = typename PairOf<T>::type;
 
-    // -> smp[j][c], j = 0 / 1 for the pair's first / second row
+    // -> smp[c] = (first pixel of the pair, second pixel)
     static __device__ __forceinline__ void window(const Const2 &k2, uint32_t stage_addr, uint32_t kb, int rows, int row0,
-                                                  int xs0, float2 sx, float2 sy, T (&smp)[2][C],
+                                                  int xs0, float2 sx, float2 sy, Pair (&smp)[C],
                                                   unsigned long long &n_viol)
     {
         const float2 magic = k2.magic, unmagic = k2.neg_magic;
         if (MODE != 2) {
             const float2 tx = pk_add(sx, magic), ty = pk_add(sy, magic);
+            uint32_t addr[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const uint32_t bx = __float_as_uint(j ? tx.y : tx.x), by = __float_as_uint(j ? ty.y : ty.x);
-                uint32_t addr = kb + by * ROWB + bx * ES;
+                addr[j] = kb + by * ROWB + bx * ES;
                 if (CHECK) {
                     const int r = (int)(by - (uint32_t)kMagicBits) - row0, x = (int)(bx - (uint32_t)kMagicBits) - xs0;
-                    if ((unsigned)r >= (unsigned)rows || (unsigned)x >= (unsigned)PITCH) { ++n_viol; addr = stage_addr; }
+                    if ((unsigned)r >= (unsigned)rows || (unsigned)x >= (unsigned)PITCH) { ++n_viol; addr[j] = stage_addr; }
                 }
-#pragma unroll
-                for (int c = 0; c < C; ++c) smp[j][c] = P::from(P::lds(addr + c * PLANEB));
             }
+#pragma unroll
+            for (int c = 0; c < C; ++c) smp[c] = P::pair(P::lds(addr[0] + c * PLANEB), P::lds(addr[1] + c * PLANEB));
         } else {
             const float2 tx = pk_add_rd(sx, magic), ty = pk_add_rd(sy, magic);
             const float2 neg = k2.neg_one, one = k2.one;
@@ -117,27 +119,27 @@ template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSample
                 acc = pk_fma(P::raw_f2(P::lds(a0 + ROWB), P::lds(a1 + ROWB)), w01, acc);
                 acc = pk_fma(P::raw_f2(P::lds(a0 + ROWB + ES), P::lds(a1 + ROWB + ES)), w11, acc);
                 if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
-                smp[0][c] = Elem<T>::from_f(acc.x);
-                smp[1][c] = Elem<T>::from_f(acc.y);
+                smp[c] = PairOf<T>::from_f2(acc);
             }
         }
     }
 
     static __device__ __forceinline__ void table(const Const2 &k2, const S *stage, const int *rowoff, int rows,
-                                                 int row0, float2 sx, float2 sy, T (&smp)[2][C],
+                                                 int row0, float2 sx, float2 sy, Pair (&smp)[C],
                                                  unsigned long long &n_viol)
     {
         if (MODE != 2) {
+            int idx[2];
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int xn = rint_magic(j ? sx.y : sx.x);
                 int r = rint_magic(j ? sy.y : sy.x) - row0;
                 if (CHECK && (unsigned)r >= (unsigned)rows) { ++n_viol; r = 0; }
-                int idx = rowoff[r] + xn;
-                if (CHECK && (unsigned)(idx - r * PITCH) >= (unsigned)PITCH) { ++n_viol; idx = 0; }
-#pragma unroll
-                for (int c = 0; c < C; ++c) smp[j][c] = P::from(stage[c * PLANE + idx]);
+                idx[j] = rowoff[r] + xn;
+                if (CHECK && (unsigned)(idx[j] - r * PITCH) >= (unsigned)PITCH) { ++n_viol; idx[j] = 0; }
             }
+#pragma unroll
+            for (int c = 0; c < C; ++c) smp[c] = P::pair(stage[c * PLANE + idx[0]], stage[c * PLANE + idx[1]]);
         } else {
             int i0[2], i1[2];
             float2 dx, dy;
@@ -168,57 +170,161 @@ template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSample
                 acc = pk_fma(P::raw_f2(pl[i1[0]], pl[i1[1]]), w01, acc);
                 acc = pk_fma(P::raw_f2(pl[i1[0] + 1], pl[i1[1] + 1]), w11, acc);
                 if (P::scaled) acc = pk_mul(acc, f2(kInv255, kInv255));
-                smp[0][c] = Elem<T>::from_f(acc.x);
-                smp[1][c] = Elem<T>::from_f(acc.y);
+                smp[c] = PairOf<T>::from_f2(acc);
             }
         }
     }
 };
 
-// Colour tier and stores of one pixel pair.  plane[c] points at the thread's pixel in the first
-// row of its tile strip, channel c; `row` (a compile-time constant after unrolling) is the
-// pair's first row within the strip and row_bytes the byte pitch of an output row, so every
-// store address is one multiply-add on a per-tile pointer.
-template <typename T, int C, unsigned F>
-__device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<T, C, F> &col, T (&smp)[2][C],
-                                            T *const (&plane)[C], int row, unsigned row_bytes, bool a_ok, bool b_ok)
+// Colour tier and stores of one pixel pair of a float image: two rows of one column.  plane[c]
+// points at the thread's pixel in the first row of its tile strip, channel c; `row` (a
+// compile-time constant after unrolling) is the pair's first row within the strip and row_bytes
+// the byte pitch of an output row, so every store address is one multiply-add on a per-tile
+// pointer.  Packed colour arithmetic measured 3 % faster than per-pixel scalar code, although
+// most of its operands are broadcast pairs.
+template <int C, unsigned F>
+__device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<float, C, F> &col, float2 (&v2)[C],
+                                            float *const (&plane)[C], int row, unsigned row_bytes, bool a_ok, bool b_ok)
 {
     auto at = [&](int c, int r) {
-        return reinterpret_cast<T *>(reinterpret_cast<char *>(plane[c]) + (size_t)row_bytes * (unsigned)r);
+        return reinterpret_cast<float *>(reinterpret_cast<char *>(plane[c]) + (size_t)row_bytes * (unsigned)r);
     };
-    // fp32: packed colour arithmetic (measured 3 % faster than per-pixel scalar code, although
-    // most of its operands are broadcast pairs); fp16 follows the reference's mixed-precision
-    // steps per pixel.
-    constexpr bool packed_colour = sizeof(T) == 4;
-    if constexpr (packed_colour) {
-        float2 v2[C];
+    col.apply2(k, v2);
 #pragma unroll
-        for (int c = 0; c < C; ++c) v2[c] = f2(smp[0][c], smp[1][c]);
-        col.apply2(k, v2);
+    for (int c = 0; c < C; ++c) {
+        if (a_ok) Elem<float>::store(at(c, row), v2[c].x);
+        if (b_ok) Elem<float>::store(at(c, row + 1), v2[c].y);
+    }
+}
+
+// The same for a half image, whose pair is two neighbouring columns of one row (the reference's
+// mixed half / float steps, two pixels at a time): one 32-bit store per channel when the pair
+// is whole and output rows keep pairs 4-byte aligned (vec), else element stores.
+// whole: every pair of the tile row is inside the image and aligned (uniform over the warp), so
+// the stores need no per-lane tests.
+template <int C, unsigned F>
+__device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__half, C, F> &col, const __half2 (&smp)[C],
+                                              __half *const (&plane)[C], int row, unsigned row_bytes, bool whole,
+                                              bool row_ok, bool pair_ok)
+{
+    float2 v2[C];
+    col.apply2(k, smp, v2);
+    unsigned h[C];
 #pragma unroll
-        for (int c = 0; c < C; ++c) {
-            if (a_ok) Elem<T>::store(at(c, row), v2[c].x);
-            if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
+    for (int c = 0; c < C; ++c) {
+        const __half2 p = __floats2half2_rn(v2[c].x, v2[c].y);       // one packed conversion
+        h[c] = *reinterpret_cast<const unsigned *>(&p);
+    }
+    auto at = [&](int c) { return reinterpret_cast<char *>(plane[c]) + (size_t)row_bytes * (unsigned)row; };
+    if (whole || (pair_ok && k.pair_store)) {
+        if (row_ok) {
+#pragma unroll
+            for (int c = 0; c < C; ++c) __stcs(reinterpret_cast<unsigned *>(at(c)), h[c]);
         }
-    } else {
-        float2 v2[C];
-        col.apply2(k, smp[0], smp[1], v2);
+    } else if (row_ok) {
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-            if (a_ok) Elem<T>::store(at(c, row), v2[c].x);
-            if (b_ok) Elem<T>::store(at(c, row + 1), v2[c].y);
+            __stcs(reinterpret_cast<unsigned short *>(at(c)), (unsigned short)(h[c] & 0xffffu));
+            if (pair_ok) __stcs(reinterpret_cast<unsigned short *>(at(c)) + 1, (unsigned short)(h[c] >> 16));
         }
     }
 }
 
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S, bool REDUCE>
+// A consumer warp's share of a tile.  Float pixels: 32 columns x kRowsPerWarp rows, a lane owns one
+// column and pairs the rows (full 128-byte lines per store instruction).  Half pixels: all 64
+// columns x kTileH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
+// so that a store is one 32-bit half2, a warp's store a full 128-byte line again, and shared
+// memory is read at 4-byte lane stride (no bank conflicts) as in the float case.
+// The mean of one image from its partial sums, by one warp.  The order of the additions is part
+// of the result, so it is fixed: 32 chains (one per lane) take the 16-byte groups of partials
+// round-robin and add their four values left to right, in double; a halving tree joins the chains.
+// Both users (mean_finish_kernel after the reduction launch, and the two-phase kernel's last
+// reducing warp) call this, so the one-launch and the two-launch path give the same bits.  All
+// loads of a lane are independent of its additions, so they overlap: ~3 us for 8192 partials.
+// per_image is a multiple of 4 (kConsumerWarps partials per tile), the base 16-byte aligned.
+__device__ __forceinline__ float mean_of_partials(const float *base, int per_image, int pixels, int lane)
+{
+    const float4 *v = reinterpret_cast<const float4 *>(base);
+    const int groups = per_image >> 2;
+    double s = 0.0;
+    int m = lane;
+    for (; m + 224 < groups; m += 256) {             // eight loads in flight per lane
+        float4 q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = __ldcg(v + m + 32 * j);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { s += (double)q[j].x; s += (double)q[j].y; s += (double)q[j].z; s += (double)q[j].w; }
+    }
+    for (; m < groups; m += 32) {
+        const float4 a = __ldcg(v + m);
+        s += (double)a.x; s += (double)a.y; s += (double)a.z; s += (double)a.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const double other = __shfl_down_sync(0xffffffffu, s, o);
+        if (lane < o) s += other;
+    }
+    return (float)(s / (double)pixels);               // valid in lane 0
+}
+
+__device__ __forceinline__ void finish_mean_by_warp(const KArgs &k, int n, int per_image, int lane)
+{
+    const float mean = mean_of_partials(k.mean_partials + (size_t)n * per_image, per_image, k.mean_pixels, lane);
+    if (lane == 0) {
+        k.mean_out[n] = mean;
+        __threadfence();
+        *(volatile unsigned *)(k.mean_ready + n) = 1u;
+    }
+}
+
+// The two-phase kernel's extra warp.  CTA b finishes the means of images b, b + grid, ...: it waits
+// until the image's counter says that every partial sum is out, adds them up (mean_of_partials,
+// ~10 us of latency that must not sit in any consumer's way: the consumer that happens to be
+// last is by definition the slowest, and making it do this work made it slower still, image after
+// image), and publishes the mean for the producers of the image's fused-pass tiles.  The wait has no
+// fixed limit of its own - the last image's count completes only near the end of the launch - but
+// it gives up when this CTA's consumers have made no progress for the wait limit (their heartbeat
+// stands still) while the count is incomplete, or when the CTA has aborted.
+__device__ __forceinline__ void two_phase_finisher(const KArgs &k, volatile int *abort_flag, volatile unsigned *heartbeat)
+{
+    const int lane = threadIdx.x & 31;
+    const int per_image = k.tiles_x * k.tiles_y * kConsumerWarps;
+    for (int n = blockIdx.x; n < k.n; n += gridDim.x) {
+        int ok = 1;
+        if (lane == 0) {
+            const volatile unsigned *done = k.mean_done + n;
+            unsigned beat = *heartbeat;
+            unsigned long long t0 = global_ns();
+            while (*done != (unsigned)per_image) {
+                __nanosleep(256);
+                if (*abort_flag) { ok = 0; break; }
+                const unsigned now = *heartbeat;
+                if (now != beat) { beat = now; t0 = global_ns(); }
+                else if (global_ns() - t0 > k.wait_ns) { ok = 0; break; }
+            }
+            __threadfence();
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { *abort_flag = 1; return; }
+        finish_mean_by_warp(k, n, per_image, lane);
+    }
+}
+
+// TWO: tiles of both phases of the two-phase kernel arrive through the same ring; the tile's
+// descriptor says which it is.
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S, bool REDUCE, bool TWO>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
-                                                volatile int *abort_flag)
+                                                volatile int *abort_flag, unsigned *two_phase_checkin)
 {
     using Info = TileInfo<T, C, F>;
     using Sampler = PairSampler<T, C, MODE, CHECK, S>;
     using Smem = AffineSmem<T, C, F, S>;
-    constexpr int ROWS_PER_WARP = kRowsPerWarp;
+    using Pair = typename PairOf<T>::type;
+    constexpr bool PAIR_X = sizeof(T) == 2;
+    static_assert(!PAIR_X || (!MIX && !REDUCE && !TWO), "the per-pixel recipe and the mean pre-pass exist for float pixels only");
+    static_assert(!TWO || (!REDUCE && !MIX && (F & kMean)), "the two-phase kernel is the mean-contrast pipeline");
+    constexpr int ROWS_PER_WARP = PAIR_X ? kTileH / kConsumerWarps : kRowsPerWarp;
+    static_assert(!PAIR_X || (kTileW == 64 && kTileH % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
@@ -229,86 +335,181 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     Const2 k2;
     k2.set();
     Colour<T, C, F> col;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x, ++it) {
-        const int s = it % kStages, use = it / kStages;
-        if (!mbar_wait_or_abort(&full[s], (uint32_t)use & 1u, abort_flag, k.wait_ns)) return;
+    // the CTA's tile number i uses stage i % kStages (for the (i / kStages)-th time) and descriptor i % kInfoSlots
+    int s = 0, slot = 0;
+    uint32_t phase = 0;
+    for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x) {
+        if (!mbar_wait_or_abort(&full[s], phase, abort_flag, k.wait_ns)) return;
         const S *stage = reinterpret_cast<const S *>(smem + s * Smem::stage);
-        const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)(it % kInfoSlots) * Smem::info);
+        const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)slot * Smem::info);
         const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
         const int4 h1 = *reinterpret_cast<const int4 *>(&ti->row0);    // row0, window, xs0, -
         const int n = h0.x, rows = h0.w, row0 = h1.x;
-        if (n != cur_n) {            // per-image parameters change only every few tiles (warp-uniform branch)
+        const bool reduce = REDUCE || (TWO && (h1.y & 2) != 0);          // this tile adds to its image's mean
+        const int key = TWO ? 2 * n + (reduce ? 1 : 0) : n;
+        if (key != cur_n) {          // per-image parameters change only every few tiles (warp-uniform branch)
             g = ti->g;
             g2.set(g);
             col = ti->col;
-            cur_n = n;
+            cur_n = key;
         }
-        const int x = h0.y + wx * 32 + lane;
-        const int y_first = h0.z + wy * ROWS_PER_WARP;
+        const int x = PAIR_X ? h0.y + 2 * lane : h0.y + wx * 32 + lane;
+        const int y_first = h0.z + (PAIR_X ? warp : wy) * ROWS_PER_WARP;
         float mean_acc = 0.0f;               // REDUCE: this lane's share of the tile's sum
 
         if (rows == 0) {
-            affine_rows_direct<T, C, MODE, F, MIX, S, REDUCE>(k, g, col, n, x, y_first, ROWS_PER_WARP, &mean_acc);
+            if constexpr (TWO) {
+                if (reduce) affine_rows_direct<T, C, MODE, F, MIX, S, true>(k, g, col, n, x, y_first, ROWS_PER_WARP, &mean_acc);
+                else        affine_rows_direct<T, C, MODE, F, MIX, S, false>(k, g, col, n, x, y_first, ROWS_PER_WARP, &mean_acc);
+            } else {
+                affine_rows_direct<T, C, MODE, F, MIX, S, REDUCE>(k, g, col, n, x, y_first, ROWS_PER_WARP, &mean_acc);
+                if (PAIR_X) affine_rows_direct<T, C, MODE, F, MIX, S, REDUCE>(k, g, col, n, x + 1, y_first, ROWS_PER_WARP, &mean_acc);
+            }
         } else if (x < k.ow) {
             T *plane[C];
             plane[0] = (T *)k.out + (size_t)n * C * oplane + (unsigned)(y_first * k.ow + x);
 #pragma unroll
             for (int c = 1; c < C; ++c) plane[c] = plane[c - 1] + oplane;
             const unsigned row_bytes = (unsigned)k.ow * (unsigned)sizeof(T);
-            // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
-            const float2 xc = bcast(MODE == 0 ? truncf(img_x(g, k.ow, x)) : centred(img_x(g, k.ow, x), g.half_w));
-            const bool window = h1.y != 0;
+            const bool window = (h1.y & 1) != 0;
             const int xs0 = h1.z;
             const uint32_t stage_addr = smem_u32(stage);
             const uint32_t kb = stage_addr - Sampler::ES * (uint32_t)(row0 * Sampler::PITCH + xs0)
                                 - Sampler::ES * (uint32_t)(Sampler::PITCH + 1) * (uint32_t)kMagicBits;
+            if constexpr (PAIR_X) {
+                // The pair: columns x and x + 1 of one row.  A pair cut by the image's right edge is
+                // computed on the last column twice (always staged) and stores one element.
+                const bool pair_ok = x + 1 < k.ow;
+                const float xi0 = img_x(g, k.ow, x), xi1 = img_x(g, k.ow, pair_ok ? x + 1 : x);
+                // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
+                const float2 xc = MODE == 0 ? f2(truncf(xi0), truncf(xi1)) : f2(centred(xi0, g.half_w), centred(xi1, g.half_w));
+                const bool whole = k.pair_store != 0 && h0.y + kTileW <= k.ow;       // the same for every lane
+                float2 ys_keep = f2(0.0f, 0.0f);
+                static_assert(ROWS_PER_WARP % 2 == 0, "the row coordinates are computed two rows at a time");
 #pragma unroll
-            for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
-                // No early exit: rows past the image's last row are computed on the last row's
-                // geometry (always staged) and only their stores are dropped, so the pairs stay
-                // independent and their instructions can interleave.
-                const int y_raw = y_first + 2 * pr;
-                const bool a_ok = y_raw < k.oh, b_ok = y_raw + 1 < k.oh;
-                const int ya = min(y_raw, k.oh - 1), yb = min(y_raw + 1, k.oh - 1);
-                // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred()
-                float2 yc = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
-                yc = pk_add(yc, g2.top);
-                float2 sx, sy;
-                if (MODE == 0) {
-                    sx = xc;
-                    sy = f2(truncf(yc.x), truncf(yc.y));
-                } else {
-                    yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
-                    sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                    sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
-                    if constexpr (MIX) {                  // see late_x()
-                        const float2 alt = src_coord2<1>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                        const uint32_t base = k.lin_base + (uint32_t)n * oplane + (uint32_t)x;
-                        if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
-                        if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
+                for (int r = 0; r < ROWS_PER_WARP; ++r) {
+                    // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred(); two rows at once
+                    float2 ys;
+                    if ((r & 1) == 0) {
+                        const int ya = min(y_first + r, k.oh - 1), yb = min(y_first + r + 1, k.oh - 1);
+                        ys = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
+                        ys = pk_add(ys, g2.top);
+                        if (MODE != 0) ys = pk_add(pk_add(ys, g2.neg_half_h), k2.half);
+                        ys_keep = ys;
+                    } else {
+                        ys = ys_keep;
                     }
+                    // no early exit: a row past the image's last row is computed on the last row's geometry
+                    const bool row_ok = y_first + r < k.oh;
+                    float2 sx, sy;
+                    if (MODE == 0) {
+                        sx = xc;
+                        sy = bcast(truncf((r & 1) ? ys.y : ys.x));
+                    } else {
+                        const float2 yc = bcast((r & 1) ? ys.y : ys.x);
+                        sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                        sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                    }
+                    Pair smp[C];
+                    if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
+                    else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
+                    if constexpr (!REDUCE) finish_pair_x<C, F>(k, col, smp, plane, r, row_bytes, whole, row_ok, pair_ok);
                 }
-                T smp[2][C];
-                if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
-                else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                if constexpr (REDUCE) {
-                    if (a_ok) mean_acc += mean_term<C, F>(col, smp[0]);
-                    if (b_ok) mean_acc += mean_term<C, F>(col, smp[1]);
-                } else {
-                    finish_pair<T, C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
-                }
+            } else {
+                // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
+                const float2 xc = bcast(MODE == 0 ? truncf(img_x(g, k.ow, x)) : centred(img_x(g, k.ow, x), g.half_w));
+                // The strip's row pairs, compiled three times: tiles that lie wholly above the image's
+                // last row (almost all) need no row clamps and no store predicates; the window /
+                // table choice is made once per tile instead of once per pair.
+                auto row_pairs = [&](auto inside_rows, auto use_window) {
+                    constexpr bool INSIDE = decltype(inside_rows)::value, WINDOW = decltype(use_window)::value;
+#pragma unroll
+                    for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
+                        // No early exit: rows past the image's last row are computed on the last row's
+                        // geometry (always staged) and only their stores are dropped, so the pairs stay
+                        // independent and their instructions can interleave.
+                        const int y_raw = y_first + 2 * pr;
+                        const bool a_ok = INSIDE || y_raw < k.oh, b_ok = INSIDE || y_raw + 1 < k.oh;
+                        const int ya = INSIDE ? y_raw : min(y_raw, k.oh - 1), yb = INSIDE ? y_raw + 1 : min(y_raw + 1, k.oh - 1);
+                        // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred()
+                        float2 yc = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
+                        yc = pk_add(yc, g2.top);
+                        float2 sx, sy;
+                        if (MODE == 0) {
+                            sx = xc;
+                            sy = f2(truncf(yc.x), truncf(yc.y));
+                        } else {
+                            yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
+                            // (the reduction uses the contraction of its own stand-alone kernel, whose
+                            // flags are brightness or nothing: the two paths must add up the same samples)
+                            if (TWO && CoordRecipe<MODE, F>::swapped && reduce) {
+                                sx = src_coord2<CoordRecipe<MODE, F & kB>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                                sy = src_coord2<CoordRecipe<MODE, F & kB>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                            } else {
+                                sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                                sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                            }
+                            if constexpr (MIX) {                  // see late_x()
+                                const float2 alt = src_coord2<1>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                                const uint32_t base = k.lin_base + (uint32_t)n * oplane + (uint32_t)x;
+                                if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
+                                if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
+                            }
+                        }
+                        Pair smp[C];
+                        if (WINDOW) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
+                        else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
+                        if constexpr (REDUCE || TWO) {
+                            if (reduce) {
+                                float pa[C], pb[C];
+#pragma unroll
+                                for (int c = 0; c < C; ++c) { pa[c] = smp[c].x; pb[c] = smp[c].y; }
+                                if (a_ok) mean_acc += mean_term<C, F>(col, pa);
+                                if (b_ok) mean_acc += mean_term<C, F>(col, pb);
+                            }
+                        }
+                        if constexpr (!REDUCE) {
+                            if (!reduce) finish_pair<C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
+                        }
+                    }
+                };
+                using yes = std::true_type;
+                using no = std::false_type;
+                if (!window) row_pairs(no{}, no{});
+                else if (y_first + ROWS_PER_WARP <= k.oh) row_pairs(yes{}, yes{});
+                else row_pairs(no{}, yes{});
             }
         }
         __syncwarp();
-        if constexpr (REDUCE) {
-            // one partial per (tile, warp), lanes added in a fixed order: the mean does not
-            // depend on which CTA ran the tile or when
+        if constexpr (REDUCE || TWO) {
+            if (reduce) {
+                // one partial per (tile, warp), lanes added in a fixed order: the mean does not
+                // depend on which CTA ran the tile or when
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) mean_acc += __shfl_xor_sync(0xffffffffu, mean_acc, o);
-            if (lane == 0) k.mean_partials[(size_t)tile * kConsumerWarps + warp] = mean_acc;
+                for (int o = 16; o > 0; o >>= 1) mean_acc += __shfl_xor_sync(0xffffffffu, mean_acc, o);
+                if (lane == 0) k.mean_partials[(size_t)h1.w * kConsumerWarps + warp] = mean_acc;
+                if constexpr (TWO) {
+                    // Counting the finished partials: once per image and CTA, not per tile - thousands
+                    // of additions to one address per image serialise in the L2.  On the CTA's last
+                    // reduction tile of the image every consumer warp checks in at a shared counter;
+                    // the last of them adds the CTA's share to the image's global counter.  Nobody
+                    // here waits for the count to complete: the image's finisher warp does (below).
+                    const int r_count = ti->r_count;
+                    if (r_count > 0 && lane == 0) {
+                        __threadfence();                                       // this warp's partials are out
+                        if (atomicAdd(&two_phase_checkin[n & 3], 1u) == (unsigned)(kConsumerWarps - 1)) {
+                            two_phase_checkin[n & 3] = 0u;                     // (no warp can be four images ahead)
+                            __threadfence();
+                            atomicAdd(k.mean_done + n, (unsigned)(r_count * kConsumerWarps));
+                        }
+                    }
+                }
+            }
         }
         if (lane == 0) mbar_arrive(&empty[s]);
+        if (TWO && threadIdx.x == 0) *(volatile unsigned *)&two_phase_checkin[4] += 1u;     // heartbeat for the finisher
+        if (++s == kStages) { s = 0; phase ^= 1u; }
+        if (++slot == kInfoSlots) slot = 0;
     }
     if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
 }
@@ -316,8 +517,10 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 // ----------------------------------------------------------------------------- kernel
 // MIX: the variant of a swapped bilinear kernel (CoordRecipe) that applies late_x() per pixel.
 // REDUCE: the grayscale-mean pre-pass on the same machinery (no colour tier, no image output).
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T, bool REDUCE = false>
-__global__ void __launch_bounds__(kAffineThreads, 1)
+// TWO: reduction and fused pass of the mean-contrast pipeline in one (cooperative) launch.
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T, bool REDUCE = false,
+          bool TWO = false>
+__global__ void __launch_bounds__(kAffineThreads + (TWO ? 32 : 0), 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
     // Used as declared (no pointer arithmetic through integers), so the compiler keeps every
@@ -326,6 +529,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     __shared__ __align__(8) uint64_t full[kStages];
     __shared__ __align__(8) uint64_t empty[kStages];
     __shared__ int abort_flag;
+    __shared__ unsigned two_phase_checkin[5];       // [0..3] consumer check-ins per image in flight, [4] consumer heartbeat
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kStages; ++i) {
@@ -333,14 +537,17 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
             mbar_init(&empty[i], kConsumerWarps);
         }
         abort_flag = 0;
+        two_phase_checkin[0] = two_phase_checkin[1] = two_phase_checkin[2] = two_phase_checkin[3] = two_phase_checkin[4] = 0u;
         mbar_fence_init();
     }
     __syncthreads();
 
-    if ((threadIdx.x >> 5) >= kConsumerWarps)
-        affine_producer<T, C, MODE, F, S>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
+    if (TWO && (threadIdx.x >> 5) >= kConsumerWarps + kStages)
+        two_phase_finisher(k, &abort_flag, &two_phase_checkin[4]);
+    else if ((threadIdx.x >> 5) >= kConsumerWarps)
+        affine_producer<T, C, MODE, F, S, TWO>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
     else
-        affine_consumer<T, C, MODE, F, CHECK, MIX, S, REDUCE>(k, smem, full, empty, &abort_flag);
+        affine_consumer<T, C, MODE, F, CHECK, MIX, S, REDUCE, TWO>(k, smem, full, empty, &abort_flag, two_phase_checkin);
 
     // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
     // memory: give each stage one more bounded chance to settle before the memory is released.

@@ -38,7 +38,7 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 7, kNumDtypes = 4;      // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed
+constexpr int kNumKinds = 10, kNumDtypes = 4;     // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed, mean pre-pass, two-phase x 3
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
@@ -49,6 +49,9 @@ static std::atomic<int> g_crop_path{0};
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;
 static std::atomic<unsigned long long> g_wait_ns{kDefaultWaitNs};
 static std::atomic<int> g_skip_arrive_tile{-1};
+// ta_b200_fused_augment_mean(): 0 = the two-launch sequence (default), 1 / 2 = one cooperative launch
+// where possible, with the fused pass one / two images behind the reduction (ta_b200_mean_path)
+static std::atomic<int> g_two_phase{0};
 
 struct DeviceState {
     std::mutex mu;
@@ -145,13 +148,31 @@ static int prepare_kernel(DeviceState &s, const KernelEntry &ke, int kind, int d
     return TA_B200_OK;
 }
 
+// ----------------------------------------------------------------------------- parameter block
+// The caller's block in the current layout.  Two layouts are accepted: the current one and the
+// one that ended before fill_rgb (its extra fields read as zero).  Any other struct_size is kept
+// as it is, for validate() to refuse.
+struct Imported {
+    ta_b200_fused_params full;
+    const ta_b200_fused_params *ptr;
+    explicit Imported(const ta_b200_fused_params *p) : ptr(p)
+    {
+        if (p && p->struct_size == offsetof(ta_b200_fused_params, fill_rgb)) {
+            memset(&full, 0, sizeof(full));
+            memcpy(&full, p, offsetof(ta_b200_fused_params, fill_rgb));
+            full.struct_size = sizeof(full);
+            ptr = &full;
+        }
+    }
+};
+
 // ----------------------------------------------------------------------------- validation
 static int validate(const ta_b200_fused_params *p, bool for_mean = false)
 {
     if (!p) return fail(TA_B200_ERR_NULL, "params is NULL");
     if (p->struct_size != sizeof(ta_b200_fused_params))
-        return fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", p->struct_size,
-                    sizeof(ta_b200_fused_params));
+        return fail(TA_B200_ERR_SHAPE, "struct_size %u is neither %zu nor %zu (ABI mismatch)", p->struct_size,
+                    sizeof(ta_b200_fused_params), offsetof(ta_b200_fused_params, fill_rgb));
     if (p->dtype != TA_B200_F32 && p->dtype != TA_B200_F16 && p->dtype != TA_B200_U8 && p->dtype != TA_B200_U8_F16)
         return fail(TA_B200_ERR_DTYPE, "dtype %d", p->dtype);
     if (p->c != 1 && p->c != 3)
@@ -183,6 +204,18 @@ static int validate(const ta_b200_fused_params *p, bool for_mean = false)
 
 static int validate_geometry_only(const ta_b200_fused_params *p) { return validate(p, true); }
 
+// How many of a reference thread's 8 pixels get the other x contraction, per colour-flag
+// combination (late_x() in ta_common.cuh; measured against the reference's kernels on a
+// B200, fp32, bilinear, neither output dimension divisible by 16; 0 elsewhere).
+static int late_count_of(const ta_b200_fused_params *p)
+{
+    static const unsigned char late_count[32] = {0, 0, 0, 0, 0, 1, 1, 3, 0, 2, 1, 3, 0, 2, 2, 3,
+                                                 0, 0, 0, 0, 0, 1, 2, 3, 0, 2, 1, 3, 0, 2, 2, 3};
+    if (p->matrix && p->interp == TA_B200_BILINEAR && out_bytes(p->dtype) == 4 && p->oh % 16 != 0 && p->ow % 16 != 0)
+        return late_count[p->apply & 31u];
+    return 0;
+}
+
 static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
 {
     memset(&k, 0, sizeof(k));
@@ -195,7 +228,7 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
     k.wait_ns = g_wait_ns.load(std::memory_order_relaxed);
     k.skip_arrive_tile = g_skip_arrive_tile.load(std::memory_order_relaxed);
     k.n = p->n; k.h = p->h; k.w = p->w; k.oh = p->oh; k.ow = p->ow;
-    k.fill = p->fill;
+    for (int i = 0; i < 3; ++i) k.fill[i] = p->fill_per_channel ? p->fill_rgb[i] : p->fill;
     for (int i = 0; i < 3; ++i) {
         const bool norm = (p->apply & TA_B200_APPLY_NORMALIZE) != 0;
         k.mean[i] = norm ? p->mean[i] : 0.0f;
@@ -203,14 +236,8 @@ static void fill_kargs(KArgs &k, const ta_b200_fused_params *p, DeviceState &s)
         k.inv_std[i] = 1.0f / k.stdv[i];
         k.nbias[i] = -k.mean[i] * k.inv_std[i];
     }
-    // How many of a reference thread's 8 pixels get the other x contraction, per colour-flag
-    // combination (late_x() in ta_common.cuh; measured against the reference's kernels on a
-    // B200, fp32, bilinear, neither output dimension divisible by 16; 0 elsewhere).
-    static const unsigned char late_count[32] = {0, 0, 0, 0, 0, 1, 1, 3, 0, 2, 1, 3, 0, 2, 2, 3,
-                                                 0, 0, 0, 0, 0, 1, 2, 3, 0, 2, 1, 3, 0, 2, 2, 3};
-    k.late_x_slot = 8;
-    if (p->matrix && p->interp == TA_B200_BILINEAR && out_bytes(p->dtype) == 4 && p->oh % 16 != 0 && p->ow % 16 != 0)
-        k.late_x_slot = 8 - late_count[p->apply & 31u];
+    k.late_x_slot = 8 - late_count_of(p);
+    k.pair_store = out_bytes(p->dtype) == 2 && p->ow % 2 == 0 && ((uintptr_t)p->out % 4) == 0;
     const size_t es = in_bytes(p->dtype);
     k.staged_ok = ((size_t)p->w * es) % 16 == 0 && ((uintptr_t)p->in % 16) == 0 &&
                   ((size_t)p->h * p->w * es) % 16 == 0 &&
@@ -291,12 +318,12 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         const bool large = p->ow >= 160 && (double)p->n * p->c * p->oh * p->ow * 4.0 >= 32.0 * 1024 * 1024;
         if (path == 2 || (path == 0 && large)) {
             kind = 3;
-            k.fill = 0.0f;
+            k.fill[0] = k.fill[1] = k.fill[2] = 0.0f;
         }
     }
     if (kind == 0 && in_bytes(p->dtype) == 1) {     // bytes are read by the staged kernels only
         kind = 3;
-        k.fill = 0.0f;
+        k.fill[0] = k.fill[1] = k.fill[2] = 0.0f;
     }
     unsigned f = template_flags(p);
     if (kind == 2 && k.late_x_slot < 8 && !checked) kind = 4;     // only swapped fp32 variants get here (fill_kargs)
@@ -446,5 +473,5 @@ static int gray_mean_static(const ta_b200_fused_params *p, float *mean_out, cuda
 
 extern "C" int ta_b200_gray_mean_static(const ta_b200_fused_params *p, float *mean_out, void *stream)
 {
-    return ta::gray_mean_static(p, mean_out, (cudaStream_t)stream);
+    return ta::gray_mean_static(ta::Imported(p).ptr, mean_out, (cudaStream_t)stream);
 }

@@ -34,7 +34,9 @@ __global__ void __launch_bounds__(kThreads) gray_mean_kernel(const __grid_consta
     load_geom(g, k, n, KIND != 0);
     const T *img = (const T *)k.in + (size_t)n * C * k.h * k.w;
     const size_t plane = (size_t)k.h * k.w;
-    const T fillv = Elem<T>::from_f(KIND != 0 ? k.fill : 0.0f);
+    T fillv[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) fillv[c] = Elem<T>::from_f(KIND != 0 ? k.fill[c] : 0.0f);
     float bf = 1.0f;
     __half bh = __float2half_rn(1.0f);
     if (BRIGHT) {
@@ -49,7 +51,7 @@ __global__ void __launch_bounds__(kThreads) gray_mean_kernel(const __grid_consta
         if (KIND == 0) {
             const int xin = (int)img_x(g, k.ow, x), yin = (int)img_y(g, y);
 #pragma unroll
-            for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xin, yin, fillv));
+            for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xin, yin, fillv[c]));
         } else {
             const float xc = centred(img_x(g, k.ow, x), g.half_w), yc = centred(img_y(g, y), g.half_h);
             // the common recipe of the sampling mode; the rarer swapped one moves a coordinate by
@@ -59,17 +61,17 @@ __global__ void __launch_bounds__(kThreads) gray_mean_kernel(const __grid_consta
             if (KIND == 1) {
                 const int xn = __float2int_rn(sx), yn = __float2int_rn(sy);
 #pragma unroll
-                for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xn, yn, fillv));
+                for (int c = 0; c < C; ++c) v[c] = Elem<T>::to_f(tap_global(img + c * plane, k.w, k.h, xn, yn, fillv[c]));
             } else {
                 const int x0 = __float2int_rd(sx), y0 = __float2int_rd(sy);
                 const float dx = sx - (float)x0, dy = sy - (float)y0;
 #pragma unroll
                 for (int c = 0; c < C; ++c) {
                     const T *pl = img + c * plane;
-                    const float b4 = blend4(Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0, fillv)),
-                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0, fillv)),
-                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0 + 1, fillv)),
-                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0 + 1, fillv)), dx, dy);
+                    const float b4 = blend4(Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0, fillv[c])),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0, fillv[c])),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0, y0 + 1, fillv[c])),
+                                            Elem<T>::to_f(tap_global(pl, k.w, k.h, x0 + 1, y0 + 1, fillv[c])), dx, dy);
                     v[c] = Elem<T>::to_f(Elem<T>::from_f(b4));
                 }
             }
@@ -137,19 +139,12 @@ static cudaError_t launch_gray_mean(const KArgs &k, int c, int kind, bool bright
 // order in double.  Measured on 64 x 3 x 1280^2 -> 1024^2: the pre-pass takes 0.24 ms (bilinear)
 // / 0.17 ms (nearest) instead of the gather kernel's 0.45 / 0.25 ms.  The gather kernel above
 // stays for fp16, unaligned rows and scratch buffers sized for it alone.
+// one warp per image; the order of the additions is mean_of_partials()'s
 __global__ void mean_finish_kernel(const float *partials, int per_image, int pixels, float *mean_out)
 {
-    __shared__ double sh[256];
-    const int n = blockIdx.x, t = threadIdx.x;
-    double s = 0.0;
-    for (int i = t; i < per_image; i += 256) s += (double)partials[(size_t)n * per_image + i];
-    sh[t] = s;
-    __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if (t < o) sh[t] += sh[t + o];
-        __syncthreads();
-    }
-    if (t == 0) mean_out[n] = (float)(sh[0] / (double)pixels);
+    const int n = blockIdx.x;
+    const float mean = mean_of_partials(partials + (size_t)n * per_image, per_image, pixels, (int)threadIdx.x);
+    if (threadIdx.x == 0) mean_out[n] = mean;
 }
 
 static long long mean_staged_tiles(const ta_b200_fused_params *p)
@@ -198,7 +193,7 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     k.out = nullptr;
     k.mean_partials = partials;
     k.late_x_slot = 8;
-    if (mode == 0) k.fill = 0.0f;
+    if (mode == 0) k.fill[0] = k.fill[1] = k.fill[2] = 0.0f;
     k.tiles_x = (p->ow + kTileW - 1) / kTileW;
     k.tiles_y = (p->oh + kTileH - 1) / kTileH;
     k.num_tiles = (int)mean_staged_tiles(p);
@@ -211,7 +206,7 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     void *args[] = {&k, &maps};
     cudaError_t e = cudaLaunchKernel(ke.fn, dim3((unsigned)grid), dim3(ke.threads), args, ke.smem, stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernel(gray_mean, staged)");
-    mean_finish_kernel<<<p->n, 256, 0, stream>>>(partials, k.tiles_x * k.tiles_y * kConsumerWarps, p->oh * p->ow, mean_out);
+    mean_finish_kernel<<<p->n, 32, 0, stream>>>(partials, k.tiles_x * k.tiles_y * kConsumerWarps, p->oh * p->ow, mean_out);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch(mean_finish)");
     return TA_B200_OK;
@@ -256,6 +251,100 @@ static int gray_mean_on(const ta_b200_fused_params *p, float *mean_out, void *sc
             ? launch_gray_mean<float>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream)
             : launch_gray_mean<__half>(k, p->c, kind, bright, mean_out, counters, partials, bpi, stream);
     if (e != cudaSuccess) return cuda_fail(e, "launch(gray_mean)");
+    return TA_B200_OK;
+}
+
+// ----------------------------------------------------------------------------- mean contrast in one call
+// ta_b200_fused_augment_mean(): grayscale-mean reduction + fused pass.  By default two launches
+// (reduction with its one-warp-per-image finish, then the fused kernel).  ta_b200_mean_path(1 or 2)
+// switches to ONE cooperative launch of the two-phase kernel (ta_affine_producer.cuh): the fused
+// pass of an image runs one or two images behind its reduction, so its read of the source comes
+// from L2 instead of HBM and nothing is launched in between.  Same partial sums, added in the same
+// order: identical output either way.  Measured on 64 x 3 x 1280^2 -> 1024^2, all colour
+// operations, medians of long runs (power-capped clocks): two launches 467 us nearest / 586 us
+// bilinear; one launch 547 / 640 us two images behind, 672 / 745 us one image behind.  Both passes
+// are bound by instruction issue, not by HBM, so reading from L2 buys little, while every
+// dependency between thread blocks costs: with the mean finished by the consumer warp that happened
+// to be last (always the slowest block, made slower still) it was 1100 us, counting partials per
+// tile instead of per block and image (8192 additions to one address per image) 2200 us.  Hence
+// the default.
+static bool two_phase_applicable(const ta_b200_fused_params *p)
+{
+    if (p->dtype != TA_B200_F32 || !mean_staged_applicable(p)) return false;
+    if (late_count_of(p) != 0) return false;                 // the per-pixel recipe has no two-phase build
+    return 2 * mean_staged_tiles(p) < 2147483647LL - (1 << 24);
+}
+static size_t two_phase_partials_offset(int n) { return ((size_t)n * 2 * sizeof(unsigned) + 255) / 256 * 256; }
+static size_t two_phase_need(const ta_b200_fused_params *p)
+{
+    return two_phase_partials_offset(p->n) + (size_t)mean_staged_tiles(p) * kConsumerWarps * sizeof(float);
+}
+
+static int fused_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,
+                      cudaStream_t stream)
+{
+    if (!p) return fail(TA_B200_ERR_NULL, "params is NULL");
+    const bool mean_mode = (p->apply & TA_B200_APPLY_CONTRAST) && p->contrast_mode == TA_B200_CONTRAST_MEAN;
+    if (!mean_mode) return launch_fused(p, stream, false);           // nothing to reduce
+    if (!mean_out) return fail(TA_B200_ERR_NULL, "mean_out is NULL");
+    ta_b200_fused_params q = *p;
+    q.gray_mean = mean_out;
+    int rc = validate(&q);
+    if (rc != TA_B200_OK) return rc;
+    if (p->n == 0) return TA_B200_OK;
+    DeviceState *s = nullptr;
+    int dev = 0;
+    rc = current_device(&s, &dev);
+    if (rc != TA_B200_OK) return rc;
+    static std::atomic<int> coop[kMaxDevices];                        // 0 unknown, 1 yes, 2 no
+    if (coop[dev].load() == 0) {
+        int v = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev);
+        coop[dev].store(e == cudaSuccess && v ? 1 : 2);
+    }
+    const bool one_launch = g_two_phase.load(std::memory_order_relaxed) != 0 && coop[dev].load() == 1 &&
+                            two_phase_applicable(p) && scratch && ((uintptr_t)scratch % 256) == 0 &&
+                            scratch_bytes >= two_phase_need(p);
+    if (!one_launch) {
+        rc = gray_mean_on(p, mean_out, scratch, scratch_bytes, stream, true);
+        if (rc != TA_B200_OK) return rc;
+        return launch_fused(&q, stream, false);
+    }
+    rc = pending_timeout(*s);
+    if (rc != TA_B200_OK) return rc;
+    KArgs k;
+    fill_kargs(k, &q, *s);
+    if (!k.staged_ok) return fail(TA_B200_ERR_UNSUPPORTED, "rows cannot be staged");
+    const int mode = p->matrix ? (p->interp == TA_B200_BILINEAR ? 2 : 1) : 0;
+    if (mode == 0) k.fill[0] = k.fill[1] = k.fill[2] = 0.0f;
+    const unsigned f = template_flags(&q);
+    const KernelTable &tab = table_f32_two_phase(mode);
+    const KernelEntry *ke = p->c == 3 ? &tab.c3[f] : &tab.c1[f];
+    if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no two-phase kernel for channels=%d flags=0x%x", p->c, f);
+    int blocks = 0;
+    rc = prepare_kernel(*s, *ke, 7 + mode, p->dtype, p->c, f, &blocks);
+    if (rc != TA_B200_OK) return rc;
+    k.tiles_x = (p->ow + kTileW - 1) / kTileW;
+    k.tiles_y = (p->oh + kTileH - 1) / kTileH;
+    k.num_tiles = (int)(2 * mean_staged_tiles(p));
+    k.mean_done = (unsigned *)scratch;
+    k.mean_ready = k.mean_done + p->n;
+    k.mean_partials = (float *)((char *)scratch + two_phase_partials_offset(p->n));
+    k.mean_out = mean_out;
+    k.mean_pixels = p->oh * p->ow;
+    k.mean_lag = g_two_phase.load(std::memory_order_relaxed) >= 2 ? 2 : 1;
+    // every CTA must be resident at once (CTAs wait for one another's partial sums): one wave at most
+    long long grid = (long long)s->sm_count * blocks;
+    if (grid > k.num_tiles) grid = k.num_tiles;
+    TMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    rc = build_tensor_maps(maps, p);
+    if (rc != TA_B200_OK) return rc;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, two_phase_partials_offset(p->n), stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(two-phase counters)");
+    void *args[] = {&k, &maps};
+    e = cudaLaunchCooperativeKernel(ke->fn, dim3((unsigned)grid), dim3(ke->threads), args, ke->smem, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchCooperativeKernel(two-phase)");
     return TA_B200_OK;
 }
 

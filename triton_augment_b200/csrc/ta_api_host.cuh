@@ -313,27 +313,49 @@ const char *ta_b200_last_error(void) { return ta::g_err; }
 
 int ta_b200_fused_augment(const ta_b200_fused_params *p, void *stream)
 {
-    return ta::launch_fused(p, (cudaStream_t)stream, false);
+    return ta::launch_fused(ta::Imported(p).ptr, (cudaStream_t)stream, false);
 }
 
 int ta_b200_fused_augment_at(const ta_b200_fused_params *p, uint32_t first_image, void *stream)
 {
-    return ta::launch_fused(p, (cudaStream_t)stream, false, first_image);
+    return ta::launch_fused(ta::Imported(p).ptr, (cudaStream_t)stream, false, first_image);
 }
 
 size_t ta_b200_gray_mean_scratch_bytes(const ta_b200_fused_params *p)
 {
     if (!p || p->n <= 0 || p->oh <= 0 || p->ow <= 0) return 256;
-    return ta::mean_scratch_need(p);
+    return ta::mean_scratch_need(ta::Imported(p).ptr);
 }
 
 int ta_b200_gray_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,
                       void *stream)
 {
-    return ta::gray_mean_on(p, mean_out, scratch, scratch_bytes, (cudaStream_t)stream, true);
+    return ta::gray_mean_on(ta::Imported(p).ptr, mean_out, scratch, scratch_bytes, (cudaStream_t)stream, true);
 }
 
-int ta_b200_fused_augment_host(const ta_b200_fused_params *p) { return ta::fused_host(p); }
+int ta_b200_fused_augment_mean(const ta_b200_fused_params *p, float *mean_out, void *scratch, size_t scratch_bytes,
+                               void *stream)
+{
+    return ta::fused_mean(ta::Imported(p).ptr, mean_out, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+size_t ta_b200_fused_augment_mean_scratch_bytes(const ta_b200_fused_params *p)
+{
+    if (!p || p->n <= 0 || p->oh <= 0 || p->ow <= 0) return 256;
+    ta::Imported imp(p);
+    const ta_b200_fused_params *q = imp.ptr;
+    size_t need = ta::mean_scratch_need(q);
+    if (ta::two_phase_applicable(q) && ta::two_phase_need(q) > need) need = ta::two_phase_need(q);
+    return need;
+}
+
+int ta_b200_mean_path(int32_t one_launch)
+{
+    ta::g_two_phase.store(one_launch < 0 ? 0 : one_launch > 2 ? 2 : one_launch, std::memory_order_relaxed);
+    return TA_B200_OK;
+}
+
+int ta_b200_fused_augment_host(const ta_b200_fused_params *p) { return p ? ta::fused_host(ta::Imported(p).ptr) : ta::fail(TA_B200_ERR_NULL, "params is NULL"); }
 
 int ta_b200_host_release(void) { return ta::host_release(); }
 
@@ -417,7 +439,7 @@ int ta_b200_debug_counters(uint64_t out[4], int reset)
 // Same as ta_b200_fused_augment but with the staging assertions compiled in (apply must be 0).
 int ta_b200_debug_fused_checked(const ta_b200_fused_params *p, void *stream)
 {
-    return ta::launch_fused(p, (cudaStream_t)stream, true);
+    return ta::launch_fused(ta::Imported(p).ptr, (cudaStream_t)stream, true);
 }
 
 int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, int32_t w, int32_t oh, int32_t ow,
@@ -446,9 +468,10 @@ int ta_b200_debug_crop_path(int32_t path)
     return TA_B200_OK;
 }
 
-void ta_b200_debug_tile_shape(int32_t out[4])
+void ta_b200_debug_tile_shape(int32_t out[6])
 {
-    out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows; out[3] = ta::kPitch;
+    out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows;
+    out[3] = ta::pitch_of(4); out[4] = ta::pitch_of(2); out[5] = ta::pitch_of(1);
 }
 
 }  // extern "C"

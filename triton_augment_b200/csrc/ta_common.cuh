@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda_fp16.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 #include <limits.h>
 #include <stdint.h>
@@ -30,7 +31,13 @@ struct KArgs {
     const void *bf, *cf, *sf;
     const uint8_t *gray;
     const float *gray_mean;
-    float *mean_partials;              // staged grayscale-mean pre-pass: [num_tiles][consumer warps] sums
+    float *mean_partials;              // staged grayscale-mean pre-pass: [image][tile][consumer warp] sums
+    // One-launch mean contrast (two-phase kernel): per image, how many partial sums have been
+    // written, whether the image's mean is final, and the means themselves (= gray_mean).
+    unsigned *mean_done, *mean_ready;
+    float *mean_out;
+    int mean_pixels;                   // pixels per output image (divisor of the mean)
+    int mean_lag;                      // the fused pass of an image runs this many images behind its reduction
     unsigned long long *counters;
     unsigned *status;                  // host-mapped word: set to 1 when a bounded wait runs out (NULL: not reported)
     unsigned long long wait_ns;        // limit of every barrier wait
@@ -39,8 +46,9 @@ struct KArgs {
     int tiles_x, tiles_y, num_tiles;
     int staged_ok;                     // source rows can be bulk-copied (16-byte aligned pitch and base)
     int late_x_slot;                   // see late_x(): 8 = never
+    int pair_store;                    // half output: pairs of columns (x even) are 4-byte aligned in every row
     unsigned lin_base;                 // linear index of this launch's first output element within the caller's batch (late_x())
-    float fill;
+    float fill[3];                     // per channel: value of texels outside the image (affine only)
     float mean[3], stdv[3];            // image-dtype-rounded values
     float inv_std[3], nbias[3];        // 1/std and -mean/std (fp32 path)
 };
@@ -145,6 +153,24 @@ template <> struct Elem<__half> {
     }
 };
 
+// Two pixels that go through the pipeline together (two rows of one column for float images,
+// two neighbouring columns of one row for half images): float2 / __half2.
+template <typename T> struct PairOf;
+template <> struct PairOf<float> {
+    using type = float2;
+    static __device__ __forceinline__ float2 make(float a, float b) { return make_float2(a, b); }
+    static __device__ __forceinline__ float2 from_f2(float2 v) { return v; }
+    static __device__ __forceinline__ float first(float2 v) { return v.x; }
+    static __device__ __forceinline__ float second(float2 v) { return v.y; }
+};
+template <> struct PairOf<__half> {
+    using type = __half2;
+    static __device__ __forceinline__ __half2 make(__half a, __half b) { return __halves2half2(a, b); }
+    static __device__ __forceinline__ __half2 from_f2(float2 v) { return __floats2half2_rn(v.x, v.y); }   // one packed conversion
+    static __device__ __forceinline__ __half first(__half2 v) { return __low2half(v); }
+    static __device__ __forceinline__ __half second(__half2 v) { return __high2half(v); }
+};
+
 // ----------------------------------------------------------------------------- geometry
 // Per-image geometry, loaded once per tile.
 struct Geom {
@@ -232,7 +258,7 @@ template <int C, unsigned F> struct Colour<float, C, F> {
         if (F & kB) bf = __ldg((const float *)k.bf + n);
         if (F & kC) {
             cf = __ldg((const float *)k.cf + n);
-            if (F & kMean) gmt = __ldg(k.gray_mean + n) * (1.0f - cf);
+            if (F & kMean) gmt = __ldcg(k.gray_mean + n) * (1.0f - cf);     // (may have been written by this very launch)
         }
         if (F & kS) { sf = __ldg((const float *)k.sf + n); oms = 1.0f - sf; }
         if (F & kG) gray = __ldg(k.gray + n) != 0;
@@ -333,7 +359,7 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
             cf = __half2float(ch);
             if (F & kMean) {
                 const __half omc = __hsub(one, ch);
-                const float m = __ldg(k.gray_mean + n);
+                const float m = __ldcg(k.gray_mean + n);
                 gmth = __hmul(__float2half_rn(m), omc);
                 gmt = m * __half2float(omc);
             }
@@ -405,7 +431,7 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
 #pragma unroll
             for (int i = 0; i < C; ++i) {
                 if (wide_after_s)
-                    v[i] = (v[i] - k.mean[i]) * k.inv_std[i];
+                    v[i] = __fmaf_rn(v[i], k.inv_std[i], k.nbias[i]);      // fp32 from the first clamp on, as for float images
                 else
                     v[i] = __half2float(__hdiv(__hsub(hv[i], __float2half_rn(k.mean[i])),
                                                __float2half_rn(k.stdv[i])));
@@ -430,18 +456,27 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
         g = pk_fma(make_float2(0.587f, 0.587f), v[C > 1 ? 1 : 0], g);
         return pk_fma(make_float2(0.114f, 0.114f), v[C - 1], g);
     }
-    __device__ __forceinline__ void apply2(const KArgs &k, const __half (&a)[C], const __half (&b)[C], float2 (&v)[C]) const
+    // half2 product clamped to [0, 1] in one instruction; the clamp of a half value is the same
+    // in half and in float (0 and 1 are exact), NaN -> 0 like __saturatef
+    static __device__ __forceinline__ __half2 hmul2_sat(__half2 a, __half2 b)
+    {
+        __half2 r;
+        asm("mul.rn.sat.f16x2 %0, %1, %2;" : "=r"(*reinterpret_cast<unsigned *>(&r))
+            : "r"(*reinterpret_cast<const unsigned *>(&a)), "r"(*reinterpret_cast<const unsigned *>(&b)));
+        return r;
+    }
+    __device__ __forceinline__ void apply2(const KArgs &k, const __half2 (&in)[C], float2 (&v)[C]) const
     {
         __half2 hv[C];
 #pragma unroll
-        for (int i = 0; i < C; ++i) hv[i] = __halves2half2(a[i], b[i]);
+        for (int i = 0; i < C; ++i) hv[i] = in[i];
         constexpr bool wide_after_b = (F & kB) != 0;
         constexpr bool wide_after_c = wide_after_b || (F & kC) != 0;
         constexpr bool wide_after_s = wide_after_c || (C == 3 && (F & kS) != 0);
         if (F & kB) {
             const __half2 bh2 = __half2half2(bh);
 #pragma unroll
-            for (int i = 0; i < C; ++i) v[i] = sat2(__half22float2(__hmul2(hv[i], bh2)));
+            for (int i = 0; i < C; ++i) v[i] = __half22float2(hmul2_sat(hv[i], bh2));
         }
         if (F & kC) {
 #pragma unroll
@@ -490,7 +525,7 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
 #pragma unroll
             for (int i = 0; i < C; ++i) {
                 if (wide_after_s)
-                    v[i] = pk_mul(pk_add(v[i], make_float2(-k.mean[i], -k.mean[i])), make_float2(k.inv_std[i], k.inv_std[i]));
+                    v[i] = pk_fma(v[i], make_float2(k.inv_std[i], k.inv_std[i]), make_float2(k.nbias[i], k.nbias[i]));
                 else
                     v[i] = __half22float2(__h2div(__hsub2(hv[i], __float2half2_rn(k.mean[i])), __float2half2_rn(k.stdv[i])));
             }

@@ -145,11 +145,11 @@ __global__ void __launch_bounds__(kThreads, VecTraits<T>::blocks) direct_vec_ker
                     // fp16: element pairs through the packed colour tier, results packed as half2 words
 #pragma unroll
                     for (int e = 0; e < EPV; e += 2) {
-                        T sa[C], sb[C];
+                        __half2 pk[C];
                         float2 v2[C];
 #pragma unroll
-                        for (int c = 0; c < C; ++c) { sa[c] = elem_of<T>(o[c], e); sb[c] = elem_of<T>(o[c], e + 1); }
-                        col.apply2(k, sa, sb, v2);
+                        for (int c = 0; c < C; ++c) pk[c] = *reinterpret_cast<const __half2 *>(&o[c][e >> 1]);   // elements e, e + 1
+                        col.apply2(k, pk, v2);
 #pragma unroll
                         for (int c = 0; c < C; ++c) {
                             const __half2 h = __floats2half2_rn(v2[c].x, v2[c].y);

@@ -33,13 +33,16 @@ constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
 // Staged row pitch = width of every tensor-copy box, in elements.  A pitch that is a multiple
 // of 32 words keeps lanes of one warp that sit in different source rows on different banks
 // (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but 2-way bank conflicts cost
-// more than they saved).  One-byte elements need 128: a copy starts on a 16-byte boundary, i.e.
+// more than they saved).  Two-byte elements: 128 (64 words); with 96 (48 words) the lanes of a
+// warp, which cover 64 neighbouring columns in pairs, met 2-way conflicts on a third of their
+// loads under rotation.  One-byte elements need 128: a copy starts on a 16-byte boundary, i.e.
 // up to 15 columns left of the footprint, and a 64-pixel tile under +-15 degrees and scale 1.1
 // already spans ~85 columns.  (144 was tried for bytes, to spread rows over the banks: fewer
 // conflicts, no gain - the byte kernels are bound by instruction issue.)
 constexpr int kPitch = 96;
+constexpr int kPitchBytes2 = 128;
 constexpr int kPitchBytes1 = 128;
-TA_HD int pitch_of(int elem_bytes) { return elem_bytes == 1 ? kPitchBytes1 : kPitch; }
+TA_HD int pitch_of(int elem_bytes) { return elem_bytes == 1 ? kPitchBytes1 : elem_bytes == 2 ? kPitchBytes2 : kPitch; }
 constexpr float kEps = 1.0f / 64.0f;   // slack (pixels) for the fp32 evaluation of coordinates
 constexpr float kCoordLimit = 1.0e6f;  // tiles whose source coordinates exceed this are not staged
 

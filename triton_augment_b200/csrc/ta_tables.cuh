@@ -37,12 +37,20 @@ constexpr bool flags_valid(int channels, unsigned f)
 }
 
 // KIND 0 crop/flip, 1 affine nearest, 2 affine bilinear, 3 crop/flip through the staged kernel,
-// 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only).
+// 4 affine bilinear with the per-pixel x contraction of late_x() (swapped variants only),
+// 5 / 6 / 7 the two-phase kernel (mean reduction + fused pass in one launch) without a matrix /
+// nearest / bilinear: exists for the flag combinations with mean-mode contrast.
 // S: source element type (uint8_t with T = float or half: bytes scaled by 1/255; staged kernels only).
 template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename S = T> KernelEntry kernel_entry()
 {
     if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
     else if constexpr (KIND == 0) return KernelEntry{(const void *)&direct_kernel<T, C, F>, 0, kThreads};
+    else if constexpr (KIND >= 5) {
+        if constexpr ((F & kMean) != 0 && !CHECK)
+            return KernelEntry{(const void *)&affine_kernel<T, C, KIND - 5, F, false, false, S, false, true>,
+                               AffineSmem<T, C, F, S>::total, kAffineThreads + 32};      // + the finisher warp
+        else return KernelEntry{nullptr, 0, 0};
+    }
     else if constexpr (KIND == 4) {
         if constexpr (CoordRecipe<2, F>::swapped && !CHECK)
             return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true, S>, AffineSmem<T, C, F, S>::total,
@@ -63,7 +71,9 @@ void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
 {
     ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs, false, S>()), ...);
     ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs, false, S>()), ...);
-    if constexpr (KIND != 0) {
+    if constexpr (KIND >= 5) {
+        t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
+    } else if constexpr (KIND != 0) {
         t.c3_checked = kernel_entry<T, 3, KIND, 0u, true, S>();
         t.c1_checked = kernel_entry<T, 1, KIND, 0u, true, S>();
     } else {
@@ -97,6 +107,7 @@ template <int C, int MODE, unsigned F, typename S> KernelEntry mean_entry()
 const KernelTable &table_f32_direct();
 const KernelTable &table_f32_crop_staged();
 const KernelTable &table_f32_bilinear_mix();
+const KernelTable &table_f32_two_phase(int mode);    // mode 0 no matrix, 1 nearest, 2 bilinear
 const KernelTable &table_u8_crop_staged();
 const KernelTable &table_u8_nearest();
 const KernelTable &table_u8_bilinear();

@@ -145,6 +145,24 @@ def _prepare_affine_matrix_only(batch_size, device, img_height, img_width, angle
     return _get_inverse_affine_matrix(c, a, t, s, sh)
 
 
+def _fill_arg(fill, channels: int = 3):
+    """``fill`` as the library takes it: a float, or a list of per-channel floats.
+
+    A number or None (= 0) fills every channel alike.  A sequence gives one value per channel,
+    as in torchvision (one value: all channels); the reference reads only the first value of a
+    sequence and marks per-channel values as to do (functional.py:942-945)."""
+    if fill is None:
+        return 0.0
+    if isinstance(fill, (list, tuple)):
+        vals = [float(v) for v in fill]
+        if len(vals) == 1:
+            return vals[0]
+        if len(vals) != channels:
+            raise ValueError(f"fill has {len(vals)} values but the image has {channels} channels")
+        return vals if channels == 3 else vals[0]
+    return float(fill)
+
+
 def _is_bilinear(interpolation) -> bool:
     return str(interpolation).lower() == "bilinear"
 
@@ -194,6 +212,9 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
         return out
     params = _lib.make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness,
                               contrast, saturation, gray, mean, std, contrast_mode)
+    if mean_mode and not first_image:
+        _lib.launch_fused_mean(params, image.device)      # reduction + fused pass, one launch where possible
+        return out
     keep = None
     if mean_mode:
         keep = _lib.launch_gray_mean(params, image.device)
@@ -203,7 +224,7 @@ def _run_fused(image, height, width, top, left, flip, matrix, bilinear, fill, br
 
 
 def fused_augment(image, top, left, height: int, width: int, flip_horizontal=False, angle=0.0,
-                  translate=[0.0, 0.0], scale=1.0, shear=[0.0, 0.0], interpolation="nearest", fill: float = 0.0,
+                  translate=[0.0, 0.0], scale=1.0, shear=[0.0, 0.0], interpolation="nearest", fill=0.0,
                   center=None, brightness_factor=1.0, contrast_factor=1.0, saturation_factor=1.0,
                   grayscale=False, mean=None, std=None, *, contrast_mode="fast", out_dtype=None, _flags=None,
                   _matrix=None, _first_image=0) -> torch.Tensor:
@@ -213,6 +234,9 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     arguments are Python scalars or ``(N,)`` tensors (translate/shear: 2-lists, ``(2,)`` or
     ``(N, 2)``), operations whose arguments are all neutral are skipped, any non-identity
     affine argument selects the affine path.  Returns a new ``(N, C, height, width)`` tensor.
+
+    Extra: ``fill`` may be a sequence of one value per channel (torchvision's meaning; the
+    reference uses the first value for every channel).
 
     Extra, keyword only: ``contrast_mode="torchvision"`` blends towards the per-image
     grayscale mean (torchvision's adjust_contrast) instead of 0.5; ``_flags`` lets the
@@ -262,7 +286,7 @@ def fused_augment(image, top, left, height: int, width: int, flip_horizontal=Fal
     elif _flags["affine"]:
         matrix = _prepare_affine_matrix_only(n, dev, img_h, img_w, angle, translate, scale, shear, center).contiguous()
     return _run_fused(image, height, width, top_t, left_t, flip_t, matrix, _flags["affine"] and _is_bilinear(interpolation),
-                      float(fill), brightness, contrast, saturation, gray,
+                      _fill_arg(fill, image.shape[1]), brightness, contrast, saturation, gray,
                       _rounded_triple(mean, dt) if apply_norm else None, _rounded_triple(std, dt) if apply_norm else None,
                       bits, _contrast_mode(contrast_mode), out_dtype, _first_image)
 
