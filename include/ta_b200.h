@@ -284,9 +284,41 @@ typedef struct ta_b200_sample_spec {
     float   *matrix;            /* [total, 6] */
     void    *brightness_out, *contrast_out, *saturation_out;   /* [total] factor_dtype */
     float   *angle_out, *translate_out, *scale_out, *shear_out; /* [total], [total,2], [total], [total,2]: the draws behind matrix */
+    /* -- fields below exist when struct_size == sizeof(ta_b200_sample_spec); the layout that ended at
+     *    shear_out is still accepted (torch_compat reads as 0) -- */
+    /*
+     * torch_compat != 0: reproduce the parameters that the reference's own sequence of draws
+     * (one `uniform_` / `randint` / `rand` call of [parameter sets] values per parameter,
+     * triton_augment/transforms.py:1431-1481, 1712-1751, 637-668) takes from PyTorch's CUDA
+     * generator, in this one launch.  PyTorch's generator is Philox4x32-10 keyed by its seed; a
+     * draw of up to (SM count x resident threads) values gives value i the first output word of
+     * counter (offset / 4, i) and advances the offset by 4.  draw[j] says which draw of the call
+     * (0, 1, 2 ... in the reference's order) parameter j comes from, or -1 for a parameter the
+     * configuration does not draw (it gets its neutral value: angle 0, translation 0, scale 1,
+     * shear 0, offsets 0, no flip, factors 1, no grayscale).  j: 0 angle, 1 tx, 2 ty, 3 scale,
+     * 4 shear x, 5 shear y, 6 top, 7 left, 8 flip, 9 brightness, 10 contrast, 11 saturation,
+     * 12 grayscale.  In this mode translate[] holds the translation ranges in PIXELS (the reference
+     * multiplies fraction and image size in double precision before the draw).  The generator's (seed, offset) at the start of the call come from
+     * torch_state (device, two 64-bit words: a captured graph can be replayed with new values) or,
+     * if that is NULL, from torch_seed / torch_offset.  The caller advances PyTorch's offset by
+     * 4 x (number of draws) afterwards.  Bits of torch_compat above bit 0 select how two float
+     * roundings are done, which is a property of the PyTorch build: bit 1 = the conversion of a
+     * random word to (0, 1] is a fused multiply-add, bit 2 = `rand * range + from` is.  seed is
+     * not read in this mode.
+     */
+    int32_t  torch_compat;
+    int8_t   draw[13];
+    int8_t   pad_[3];
+    uint64_t torch_seed, torch_offset;
+    const uint64_t *torch_state;
 } ta_b200_sample_spec;
 
 int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream);
+
+/* dst[0] = a, dst[1] = b on `stream` (device memory): how a caller refreshes the torch_state of a
+ * captured ta_b200_sample_params launch before replaying the graph - the values travel as
+ * kernel arguments, so no host buffer has to outlive the call. */
+int ta_b200_store_words(uint64_t *dst, uint64_t a, uint64_t b, void *stream);
 
 /*
  * Diagnostics.  ta_b200_debug_counters copies {tiles staged through shared memory,

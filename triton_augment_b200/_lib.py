@@ -29,6 +29,7 @@ SYMBOLS = (
     "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
     "ta_b200_debug_tile_shape", "ta_b200_status", "ta_b200_host_release", "ta_b200_debug_wait",
     "ta_b200_fused_augment_mean", "ta_b200_fused_augment_mean_scratch_bytes", "ta_b200_mean_path",
+    "ta_b200_store_words",
 )
 
 
@@ -61,6 +62,8 @@ class SampleSpec(C.Structure):
         ("matrix", C.c_void_p), ("brightness_out", C.c_void_p), ("contrast_out", C.c_void_p),
         ("saturation_out", C.c_void_p), ("angle_out", C.c_void_p), ("translate_out", C.c_void_p),
         ("scale_out", C.c_void_p), ("shear_out", C.c_void_p),
+        ("torch_compat", C.c_int32), ("draw", C.c_int8 * 13), ("pad_", C.c_int8 * 3),
+        ("torch_seed", C.c_uint64), ("torch_offset", C.c_uint64), ("torch_state", C.c_void_p),
     ]
 
 
@@ -119,6 +122,8 @@ def load():
     lib.ta_b200_fused_augment_mean_scratch_bytes.restype = C.c_size_t
     lib.ta_b200_mean_path.argtypes = [C.c_int32]
     lib.ta_b200_mean_path.restype = C.c_int
+    lib.ta_b200_store_words.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]
+    lib.ta_b200_store_words.restype = C.c_int
     lib.ta_b200_status.argtypes = [C.c_int]
     lib.ta_b200_status.restype = C.c_int
     lib.ta_b200_host_release.argtypes = []
@@ -248,6 +253,13 @@ def launch_sample_params(spec: SampleSpec, device: torch.device) -> None:
     with torch.cuda.device(device):
         stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         check(load().ta_b200_sample_params(C.byref(spec), stream), "ta_b200_sample_params")
+
+
+def store_words(dst: torch.Tensor, a: int, b: int) -> None:
+    """dst[0], dst[1] = a, b (a 2-element int64 device tensor) on torch's current stream."""
+    with torch.cuda.device(dst.device):
+        stream = C.c_void_p(torch.cuda.current_stream(dst.device).cuda_stream)
+        check(load().ta_b200_store_words(_ptr(dst), int(a) & (2 ** 64 - 1), int(b) & (2 ** 64 - 1), stream), "ta_b200_store_words")
 
 
 def crop_path(path: int) -> None:

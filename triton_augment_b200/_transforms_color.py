@@ -54,7 +54,18 @@ class TritonColorJitter(_JitterBase):
     def _get_params(self, param_count: int, device):
         return self._draw_jitter(param_count, device)
 
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        t = TritonFusedAugment(brightness=self.brightness or 0, contrast=self.contrast or 0, saturation=self.saturation or 0,
+                               same_on_batch=self.same_on_batch, same_on_frame=self.same_on_frame,
+                               contrast_mode=self.contrast_mode)
+        t._draw_gray = False                     # this class draws brightness, contrast, saturation only
+        return t
+
     def forward(self, img: torch.Tensor) -> torch.Tensor:
+        out = self._through_fused(img, self._twin)
+        if out is not None:
+            return out
         lay = self._layout(img)
         b, c, s = (lay.spread(p) for p in self._get_params(lay.count, lay.param_device))
         h, w = lay.image.shape[2:]
@@ -117,7 +128,16 @@ class TritonColorJitterNormalize(_JitterBase):
         flags.update(affine=affine, grayscale=self.grayscale_p > 0)
         return flags
 
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        return TritonFusedAugment(brightness=self.brightness or 0, contrast=self.contrast or 0, saturation=self.saturation or 0,
+                                  grayscale_p=self.grayscale_p, mean=self.mean, std=self.std, same_on_batch=self.same_on_batch,
+                                  same_on_frame=self.same_on_frame, contrast_mode=self.contrast_mode)
+
     def forward(self, img: torch.Tensor) -> torch.Tensor:
+        out = self._through_fused(img, self._twin)
+        if out is not None:
+            return out
         lay = self._layout(img)
         b, c, s, g = (lay.spread(p) for p in self._get_params(lay.count, lay.param_device))
         h, w = lay.image.shape[2:]

@@ -125,16 +125,67 @@ class TritonFusedAugment(T._BatchAware):
             out_dtype=self.out_dtype if image4d.dtype == torch.uint8 else None, _first_image=first_image,
             _flags=self.color_helper._colour_flags(affine=self.has_affine))
 
-    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None):
+    # True: when PyTorch's CUDA generator can be reproduced inside the sampler kernel (checked per
+    # device, see _torch_rng), forward() draws all parameters with ONE launch and advances the
+    # generator as the reference's separate draws would - same parameters for a seed, a dozen
+    # launches fewer.  False: always draw with PyTorch itself.
+    one_launch_draws = True
+    # The reference's TritonFusedAugment draws the flip mask only for horizontal_flip_p > 0 and the
+    # grayscale mask always; classes that borrow this sampler (TritonRandomCropFlip: flip always;
+    # TritonColorJitter, TritonRandomCropFlip: no grayscale draw) say so here.
+    _draw_flip_always = False
+    _draw_gray = True
+
+    def _draw_plan(self):
+        """Which draw of a call (0, 1, ... in the reference's order, transforms.py:1431-1481) each
+        parameter comes from; -1 = not drawn.  Returns (13 indices, number of draws)."""
+        ch, k, plan = self.color_helper, 0, {}
+        def take(name, drawn):
+            nonlocal k
+            plan[name] = k if drawn else -1
+            k += 1 if drawn else 0
+        ah = self.affine_helper if self.has_affine else None
+        take("angle", ah is not None)
+        take("tx", ah is not None and ah.translate is not None)
+        take("ty", ah is not None and ah.translate is not None)
+        take("scale", ah is not None and ah.scale is not None)
+        take("shear_x", ah is not None and ah.shear is not None)
+        take("shear_y", ah is not None and ah.shear is not None)
+        take("top", self.crop_height is not None)
+        take("left", self.crop_height is not None)
+        take("flip", self.horizontal_flip_p > 0 or self._draw_flip_always)
+        take("brightness", ch.brightness is not None)
+        take("contrast", ch.contrast is not None)
+        take("saturation", ch.saturation is not None)
+        take("gray", self._draw_gray)
+        from ._torch_rng import DRAW_SLOTS
+        return [plan[s] for s in DRAW_SLOTS], k
+
+    def _torch_flags(self, lay, dev) -> int:
+        """Non-zero: this call's parameters can come from the sampler kernel in PyTorch-compatible mode."""
+        from . import _torch_rng
+        if not self.one_launch_draws or self._param_device is not None or dev.type != "cuda":
+            return 0
+        if lay.count > _torch_rng.max_values_per_draw(dev):
+            return 0
+        if torch.cuda.is_current_stream_capturing() and getattr(self, "_torch_state", None) is None:
+            return 0                      # the replay state must exist before the capture starts
+        return _torch_rng.flags_for(dev)
+
+    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None, torch_flags: int = 0):
         """Every per-sample parameter of one call from the library's sampler kernel: dict of
         device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
         (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
-        scale, shear``, the draws behind the matrix)."""
+        scale, shear``, the draws behind the matrix).  ``torch_flags`` != 0: the values PyTorch's
+        generator would give the reference's separate draws (and the generator is advanced
+        accordingly); 0: the library's own random stream, seeded by one PyTorch draw."""
         from . import _lib
         dev = lay.image.device if device is None else torch.device(device)     # host batches: where to sample
         h, w = lay.image.shape[2:]
         total = lay.total
-        seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
+        seed = None
+        if not torch_flags:
+            seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
         words = 8 + 3 + (6 if want_draws else 0)                 # fp32 slots per sample: top, left, matrix(6), 3 factors, draws
         buf = torch.empty(total * words * 4 + total * 2, dtype=torch.uint8, device=dev)
         f32 = buf[: total * words * 4].view(torch.float32)
@@ -161,7 +212,25 @@ class TritonFusedAugment(T._BatchAware):
         sp.brightness[:] = ch.brightness or (1.0, 1.0)
         sp.contrast[:] = ch.contrast or (1.0, 1.0)
         sp.saturation[:] = ch.saturation or (1.0, 1.0)
-        sp.seed = seed.data_ptr()
+        if torch_flags:
+            from . import _torch_rng
+            plan, draws = self._draw_plan()
+            sp.torch_compat = torch_flags
+            sp.draw[:] = plan
+            if ah and ah.translate is not None:           # pixels, multiplied in double like the reference
+                sp.translate[:] = (float(ah.translate[0] * w), float(ah.translate[1] * h))
+            gen = _torch_rng.generator_of(dev)
+            if getattr(self, "_torch_state", None) is None or self._torch_state.device != dev:
+                self._torch_state = torch.zeros(2, dtype=torch.int64, device=dev)      # (seed, offset) for graph replays
+            if torch.cuda.is_current_stream_capturing():
+                sp.torch_state = self._torch_state.data_ptr()      # refreshed before every replay (GraphedTransform)
+                _torch_rng.CAPTURED.append((self._torch_state, draws))
+            else:
+                offset = gen.get_offset()
+                sp.torch_seed, sp.torch_offset = gen.initial_seed(), offset
+                gen.set_offset(offset + 4 * draws)                 # what the separate draws would have consumed
+        else:
+            sp.seed = seed.data_ptr()
         sp.top, sp.left, sp.flip, sp.gray = top.data_ptr(), left.data_ptr(), flip.data_ptr(), gray.data_ptr()
         sp.matrix = matrix.data_ptr() if self.has_affine else None
         sp.brightness_out, sp.contrast_out, sp.saturation_out = (f.data_ptr() for f in factors)
@@ -176,7 +245,7 @@ class TritonFusedAugment(T._BatchAware):
         _lib.launch_sample_params(sp, dev)
         return out
 
-    def _forward_fast(self, lay):
+    def _forward_fast(self, lay, torch_flags: int = 0):
         from . import _lib
         img = lay.image
         h, w = img.shape[2:]
@@ -184,7 +253,7 @@ class TritonFusedAugment(T._BatchAware):
             raise ValueError(f"Crop size ({self.crop_height}, {self.crop_width}) is larger than the image ({h}, {w})")
         out_dtype = self.out_dtype if img.dtype == torch.uint8 else None
         work = F._work_dtype(img, out_dtype)
-        p = self._sample_fast(lay, work)
+        p = self._sample_fast(lay, work, torch_flags=torch_flags)
         flags = self.color_helper._colour_flags(affine=self.has_affine)
         mean, std = self.color_helper.mean, self.color_helper.std
         bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
@@ -202,6 +271,9 @@ class TritonFusedAugment(T._BatchAware):
         lay = self._layout(image)
         if self.fast_rng:
             return lay.restore(self._forward_fast(lay))
+        torch_flags = self._torch_flags(lay, lay.param_device)
+        if torch_flags:
+            return lay.restore(self._forward_fast(lay, torch_flags))
         h, w = lay.image.shape[2:]
         # (Drawing the parameters on a side stream so that they overlap the previous call's
         # kernel was tried and measured slower: 0.66 ms instead of 0.41 ms per 64-image call.)

@@ -137,6 +137,9 @@ class TritonRandomCropFlip(T._BatchAware):
         th, tw = self.size
         if th > h or tw > w:
             raise ValueError(f"Crop size ({th}, {tw}) is larger than image size ({h}, {w})")
+        out = self._through_fused(image, self._twin)
+        if out is not None:
+            return out
         top, left = _draw_offsets(lay, h, w, th, tw, torch.int32)
         flip = F._sample_bernoulli_tensor(lay.count, self.horizontal_flip_p, lay.param_device)
         out = F.fused_augment(lay.image, top=lay.spread(top), left=lay.spread(left), height=th, width=tw,
@@ -144,6 +147,13 @@ class TritonRandomCropFlip(T._BatchAware):
                               saturation_factor=1.0, grayscale=False, mean=None, std=None,
                               _flags=dict(affine=False, **_NO_COLOUR))
         return lay.restore(out)
+
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        t = TritonFusedAugment(crop_size=self.size, horizontal_flip_p=self.horizontal_flip_p,
+                               same_on_batch=self.same_on_batch, same_on_frame=self.same_on_frame)
+        t._draw_flip_always, t._draw_gray = True, False      # this class draws top, left and - always - the flip mask
+        return t
 
     def __repr__(self):
         return (f"{self.__class__.__name__}(size={self.size}, horizontal_flip_p={self.horizontal_flip_p}, "

@@ -402,6 +402,33 @@ __device__ __forceinline__ uint4 philox4x32_10(uint2 key, uint4 ctr)
 __device__ __forceinline__ float unit_float(uint32_t bits) { return (float)(bits >> 8) * (1.0f / 16777216.0f); }   // [0, 1)
 __device__ __forceinline__ float uniform_in(uint32_t bits, const float (&r)[2]) { return r[0] == r[1] ? r[0] : r[0] + unit_float(bits) * (r[1] - r[0]); }
 
+__global__ void store_words_kernel(uint64_t *dst, uint64_t a, uint64_t b) { dst[0] = a; dst[1] = b; }
+
+// ---- PyTorch's CUDA generator, restated (ATen/native/cuda/DistributionTemplates.h, curand's Philox
+// state: curand_philox4x32_x.h).  A draw of `numel` values launches ceil(numel / 256) blocks of 256
+// threads (at most SM count x resident blocks); thread t starts curand at (seed, subsequence t,
+// offset) and, while numel <= the thread count, value t is made from the first word of its first
+// four-word block, i.e. Philox(key = seed, counter = (offset / 4 lo, hi, t lo, t hi)).x.
+__device__ __forceinline__ uint32_t torch_word(uint64_t seed, uint64_t offset4, uint32_t draw, uint32_t index)
+{
+    const uint64_t c = offset4 + draw;
+    return philox4x32_10(make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)),
+                         make_uint4((uint32_t)c, (uint32_t)(c >> 32), index, 0u)).x;
+}
+// curand_uniform: word -> (0, 1]
+__device__ __forceinline__ float torch_unit(uint32_t w, bool fused)
+{
+    const float x = __uint2float_rn(w), k = 2.3283064e-10f, h = 2.3283064e-10f / 2.0f;
+    return fused ? __fmaf_rn(x, k, h) : __fadd_rn(__fmul_rn(x, k), h);
+}
+// tensor.uniform_(from, to): rand * (to - from) + from, the value `to` folded back to `from`
+__device__ __forceinline__ float torch_uniform(uint32_t w, float from, float to, int flags)
+{
+    const float r = torch_unit(w, (flags & 2) != 0), range = __fsub_rn(to, from);
+    const float v = (flags & 4) ? __fmaf_rn(r, range, from) : __fadd_rn(__fmul_rn(r, range), from);
+    return v == to ? from : v;
+}
+
 template <typename FT>
 __global__ void sample_params_kernel(const __grid_constant__ ta_b200_sample_spec s)
 {
@@ -410,6 +437,34 @@ __global__ void sample_params_kernel(const __grid_constant__ ta_b200_sample_spec
     int p;
     if (s.frames <= 1) p = s.same_on_batch ? 0 : i;
     else p = (s.same_on_batch ? 0 : i / s.frames) * (s.same_on_frame ? 1 : s.frames) + (s.same_on_frame ? 0 : i % s.frames);
+    if (s.torch_compat) {
+        const uint64_t seed = s.torch_state ? s.torch_state[0] : s.torch_seed;
+        const uint64_t off4 = (s.torch_state ? s.torch_state[1] : s.torch_offset) >> 2;
+        const int fl = s.torch_compat;
+        auto word = [&](int j) { return torch_word(seed, off4, (uint32_t)s.draw[j], (uint32_t)p); };
+        auto uni = [&](int j, float lo, float hi, float neutral) { return s.draw[j] < 0 ? neutral : torch_uniform(word(j), lo, hi, fl); };
+        const float max_dx = s.translate[0], max_dy = s.translate[1];        // pixels in this mode
+        const float angle = uni(0, s.degrees[0], s.degrees[1], 0.0f);
+        const float tx = uni(1, -max_dx, max_dx, 0.0f), ty = uni(2, -max_dy, max_dy, 0.0f);
+        const float sc = uni(3, s.scale[0], s.scale[1], 1.0f);
+        const float shx = uni(4, s.shear[0], s.shear[1], 0.0f), shy = uni(5, s.shear[2], s.shear[3], 0.0f);
+        if (s.matrix) inverse_matrix_of(angle, tx, ty, sc, shx, shy, 0.0f, 0.0f, s.matrix + 6 * (size_t)i);
+        if (s.angle_out) s.angle_out[i] = angle;
+        if (s.translate_out) { s.translate_out[2 * i] = tx; s.translate_out[2 * i + 1] = ty; }
+        if (s.scale_out) s.scale_out[i] = sc;
+        if (s.shear_out) { s.shear_out[2 * i] = shx; s.shear_out[2 * i + 1] = shy; }
+        // randint(0, size - crop + 1): word % range (ATen/core/TransformationHelper.h, uniform_int_from_to)
+        const uint32_t span_y = (uint32_t)(s.img_h - s.crop_h + 1), span_x = (uint32_t)(s.img_w - s.crop_w + 1);
+        if (s.top) s.top[i] = s.draw[6] < 0 ? 0.0f : (float)(word(6) % span_y);
+        if (s.left) s.left[i] = s.draw[7] < 0 ? 0.0f : (float)(word(7) % span_x);
+        // rand(n) < p
+        if (s.flip) s.flip[i] = s.draw[8] >= 0 && torch_uniform(word(8), 0.0f, 1.0f, fl) < s.flip_p ? 1 : 0;
+        if (s.brightness_out) ((FT *)s.brightness_out)[i] = (FT)uni(9, s.brightness[0], s.brightness[1], 1.0f);
+        if (s.contrast_out) ((FT *)s.contrast_out)[i] = (FT)uni(10, s.contrast[0], s.contrast[1], 1.0f);
+        if (s.saturation_out) ((FT *)s.saturation_out)[i] = (FT)uni(11, s.saturation[0], s.saturation[1], 1.0f);
+        if (s.gray) s.gray[i] = s.draw[12] >= 0 && torch_uniform(word(12), 0.0f, 1.0f, fl) < s.grayscale_p ? 1 : 0;
+        return;
+    }
     const uint64_t seed = *s.seed;
     const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
     uint32_t u[16];

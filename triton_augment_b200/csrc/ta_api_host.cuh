@@ -399,8 +399,26 @@ int ta_b200_inverse_affine_matrix(int32_t n, const float *center, const float *a
 int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream)
 {
     if (!spec) return ta::fail(TA_B200_ERR_NULL, "spec is NULL");
+    ta_b200_sample_spec full;
+    if (spec->struct_size == offsetof(ta_b200_sample_spec, torch_compat)) {      // the layout before torch_compat
+        memset(&full, 0, sizeof(full));
+        memcpy(&full, spec, offsetof(ta_b200_sample_spec, torch_compat));
+        full.struct_size = sizeof(full);
+        spec = &full;
+    }
     if (spec->struct_size != sizeof(ta_b200_sample_spec))
         return ta::fail(TA_B200_ERR_SHAPE, "struct_size %u != %zu (ABI mismatch)", spec->struct_size, sizeof(ta_b200_sample_spec));
+    if (spec->torch_compat) {
+        int max_draw = -1;
+        for (int j = 0; j < 13; ++j) {
+            if (spec->draw[j] >= 13) return ta::fail(TA_B200_ERR_SHAPE, "draw[%d] = %d", j, (int)spec->draw[j]);
+            if (spec->draw[j] > max_draw) max_draw = spec->draw[j];
+        }
+        if ((spec->draw[6] >= 0 || spec->draw[7] >= 0) && (spec->crop_h <= 0 || spec->crop_w <= 0))
+            return ta::fail(TA_B200_ERR_SHAPE, "crop offsets are drawn but there is no crop size");
+        const uint64_t off = spec->torch_state ? 0 : spec->torch_offset;
+        if (off % 4 != 0) return ta::fail(TA_B200_ERR_UNSUPPORTED, "PyTorch generator offset %llu is not a multiple of 4", (unsigned long long)off);
+    }
     if (spec->total < 0 || spec->frames < 1 || spec->total % spec->frames != 0)
         return ta::fail(TA_B200_ERR_SHAPE, "total = %d, frames = %d", spec->total, spec->frames);
     if (spec->img_h <= 0 || spec->img_w <= 0 || spec->crop_h < 0 || spec->crop_w < 0 || spec->crop_h > spec->img_h ||
@@ -408,13 +426,22 @@ int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream)
         return ta::fail(TA_B200_ERR_SHAPE, "image %dx%d, crop %dx%d", spec->img_h, spec->img_w, spec->crop_h, spec->crop_w);
     if (spec->factor_dtype != TA_B200_F32 && spec->factor_dtype != TA_B200_F16)
         return ta::fail(TA_B200_ERR_DTYPE, "factor_dtype %d", spec->factor_dtype);
-    if (!spec->seed) return ta::fail(TA_B200_ERR_NULL, "seed is NULL");
+    if (!spec->seed && !spec->torch_compat) return ta::fail(TA_B200_ERR_NULL, "seed is NULL");
     if (spec->total == 0) return TA_B200_OK;
     const int threads = 128, blocks = (spec->total + threads - 1) / threads;
     if (spec->factor_dtype == TA_B200_F32) ta::sample_params_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>(*spec);
     else ta::sample_params_kernel<__half><<<blocks, threads, 0, (cudaStream_t)stream>>>(*spec);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return ta::cuda_fail(e, "launch(sample_params)");
+    return TA_B200_OK;
+}
+
+int ta_b200_store_words(uint64_t *dst, uint64_t a, uint64_t b, void *stream)
+{
+    if (!dst) return ta::fail(TA_B200_ERR_NULL, "dst is NULL");
+    ta::store_words_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(dst, a, b);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return ta::cuda_fail(e, "launch(store_words)");
     return TA_B200_OK;
 }
 

@@ -53,8 +53,19 @@ class GraphedTransform:
                 transform(example)
         torch.cuda.current_stream(device).wait_stream(side)
         self.graph = torch.cuda.CUDAGraph()
+        from . import _torch_rng
+        del _torch_rng.CAPTURED[:]
         with torch.cuda.device(device), torch.cuda.graph(self.graph):
             self.static_output = transform(example)
+        # A transform that draws its parameters inside the library in PyTorch-compatible mode has
+        # captured a launch that reads the generator's (seed, offset) from device memory: every
+        # replay is preceded by a refresh of those two words (per captured sampler launch, each
+        # starting where the one before stops) and followed by the same advance of PyTorch's
+        # generator that eager calls make.
+        self._samplers = list(_torch_rng.CAPTURED)
+        del _torch_rng.CAPTURED[:]
+        self._draws = sum(d for _, d in self._samplers)
+        self._device = device
 
     def __call__(self, image: Optional[torch.Tensor] = None) -> torch.Tensor:
         if image is not None and image is not self.static_input:
@@ -63,6 +74,14 @@ class GraphedTransform:
                                  f"got {tuple(image.shape)} {image.dtype}")
             if not image.is_cuda or image.data_ptr() != self.static_input.data_ptr():
                 self.static_input.copy_(image, non_blocking=True)
+        if self._samplers:
+            from . import _lib, _torch_rng
+            gen = _torch_rng.generator_of(self._device)
+            seed, offset = gen.initial_seed(), gen.get_offset()
+            for state, draws in self._samplers:
+                _lib.store_words(state, seed, offset)
+                offset += 4 * draws
+            gen.set_offset(offset)
         self.graph.replay()
         return self.static_output
 

@@ -170,6 +170,27 @@ class _BatchAware(nn.Module):
     def _layout(self, image, upload=True) -> _Layout:
         return _Layout(image, self.same_on_batch, self.same_on_frame, upload, self._param_device)
 
+    # True (default): where PyTorch's CUDA generator can be reproduced inside the library's sampler
+    # kernel, a forward draws all its parameters with one launch - the same values, the generator
+    # left where the reference's separate draws would leave it.  False: draw with PyTorch itself.
+    one_launch_draws = True
+
+    def _through_fused(self, image, make):
+        """forward() of a class whose draws are a subset of TritonFusedAugment's, through a private
+        TritonFusedAugment (built once by ``make``) and its one-launch sampler.  Returns None when
+        that path is not available for this call (the caller then draws with PyTorch)."""
+        if not self.one_launch_draws or self._param_device is not None:
+            return None
+        d = self.__dict__.get("_fused_twin")
+        if d is None:
+            d = make()
+            self.__dict__["_fused_twin"] = d          # (not a registered sub-module: it has no state of its own)
+        lay = d._layout(image)
+        flags = d._torch_flags(lay, lay.param_device)
+        if not flags:
+            return None
+        return lay.restore(d._forward_fast(lay, flags))
+
     def _tail(self):
         return f"same_on_batch={self.same_on_batch}, same_on_frame={self.same_on_frame})"
 
