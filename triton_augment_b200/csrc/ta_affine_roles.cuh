@@ -235,41 +235,55 @@ __device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__hal
 // columns x kTileH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
 // so that a store is one 32-bit half2, a warp's store a full 128-byte line again, and shared
 // memory is read at 4-byte lane stride (no bank conflicts) as in the float case.
-// The mean of one image from its partial sums, by one warp.  The order of the additions is part
-// of the result, so it is fixed: 32 chains (one per lane) take the 16-byte groups of partials
-// round-robin and add their four values left to right, in double; a halving tree joins the chains.
-// Both users (mean_finish_kernel after the reduction launch, and the two-phase kernel's last
-// reducing warp) call this, so the one-launch and the two-launch path give the same bits.  All
-// loads of a lane are independent of its additions, so they overlap: ~3 us for 8192 partials.
-// per_image is a multiple of 4 (kConsumerWarps partials per tile), the base 16-byte aligned.
-__device__ __forceinline__ float mean_of_partials(const float *base, int per_image, int pixels, int lane)
+// The mean of one image from its partial sums.  The order of the additions is part of the result,
+// so it is fixed: 256 chains take the 16-byte groups of partials round-robin (chain t: groups t,
+// t + 256, ...) and add each group's four values left to right, in double; a halving tree joins
+// the chains (chain t += chain t + 128, then + 64, ... + 1).  Two implementations with the same
+// order, hence the same bits: mean_finish_kernel (256 threads, one chain each, after the reduction
+// launch) and mean_of_partials_by_warp (one warp, lane l running chains l, l + 32, ... l + 224: the
+// two-phase kernel's finisher).  per_image is a multiple of 4 (kConsumerWarps partials per tile),
+// the base 16-byte aligned.
+__device__ __forceinline__ double chain_sum(const float4 *v, int groups, int chain)
 {
-    const float4 *v = reinterpret_cast<const float4 *>(base);
-    const int groups = per_image >> 2;
     double s = 0.0;
-    int m = lane;
-    for (; m + 224 < groups; m += 256) {             // eight loads in flight per lane
-        float4 q[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = __ldcg(v + m + 32 * j);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { s += (double)q[j].x; s += (double)q[j].y; s += (double)q[j].z; s += (double)q[j].w; }
+    int m = chain;
+    for (; m + 768 < groups; m += 1024) {            // four loads in flight
+        const float4 a = __ldcg(v + m), b = __ldcg(v + m + 256), c = __ldcg(v + m + 512), d = __ldcg(v + m + 768);
+        s += (double)a.x; s += (double)a.y; s += (double)a.z; s += (double)a.w;
+        s += (double)b.x; s += (double)b.y; s += (double)b.z; s += (double)b.w;
+        s += (double)c.x; s += (double)c.y; s += (double)c.z; s += (double)c.w;
+        s += (double)d.x; s += (double)d.y; s += (double)d.z; s += (double)d.w;
     }
-    for (; m < groups; m += 32) {
+    for (; m < groups; m += 256) {
         const float4 a = __ldcg(v + m);
         s += (double)a.x; s += (double)a.y; s += (double)a.z; s += (double)a.w;
     }
+    return s;
+}
+
+__device__ __forceinline__ float mean_of_partials_by_warp(const float *base, int per_image, int pixels, int lane)
+{
+    const float4 *v = reinterpret_cast<const float4 *>(base);
+    const int groups = per_image >> 2;
+    double a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = chain_sum(v, groups, lane + 32 * j);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a[j] += a[j + 4];          // + 128
+    a[0] += a[2];                                           // + 64
+    a[1] += a[3];
+    a[0] += a[1];                                           // + 32
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const double other = __shfl_down_sync(0xffffffffu, s, o);
-        if (lane < o) s += other;
+        const double other = __shfl_down_sync(0xffffffffu, a[0], o);
+        if (lane < o) a[0] += other;
     }
-    return (float)(s / (double)pixels);               // valid in lane 0
+    return (float)(a[0] / (double)pixels);            // valid in lane 0
 }
 
 __device__ __forceinline__ void finish_mean_by_warp(const KArgs &k, int n, int per_image, int lane)
 {
-    const float mean = mean_of_partials(k.mean_partials + (size_t)n * per_image, per_image, k.mean_pixels, lane);
+    const float mean = mean_of_partials_by_warp(k.mean_partials + (size_t)n * per_image, per_image, k.mean_pixels, lane);
     if (lane == 0) {
         k.mean_out[n] = mean;
         __threadfence();

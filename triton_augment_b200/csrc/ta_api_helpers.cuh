@@ -139,12 +139,19 @@ static cudaError_t launch_gray_mean(const KArgs &k, int c, int kind, bool bright
 // order in double.  Measured on 64 x 3 x 1280^2 -> 1024^2: the pre-pass takes 0.24 ms (bilinear)
 // / 0.17 ms (nearest) instead of the gather kernel's 0.45 / 0.25 ms.  The gather kernel above
 // stays for fp16, unaligned rows and scratch buffers sized for it alone.
-// one warp per image; the order of the additions is mean_of_partials()'s
-__global__ void mean_finish_kernel(const float *partials, int per_image, int pixels, float *mean_out)
+// one block of 256 threads per image, one chain each; the order of the additions is chain_sum()'s
+// and the tree's, as in mean_of_partials_by_warp()
+__global__ void __launch_bounds__(256) mean_finish_kernel(const float *partials, int per_image, int pixels, float *mean_out)
 {
-    const int n = blockIdx.x;
-    const float mean = mean_of_partials(partials + (size_t)n * per_image, per_image, pixels, (int)threadIdx.x);
-    if (threadIdx.x == 0) mean_out[n] = mean;
+    __shared__ double sh[256];
+    const int n = blockIdx.x, t = threadIdx.x;
+    sh[t] = chain_sum(reinterpret_cast<const float4 *>(partials + (size_t)n * per_image), per_image >> 2, t);
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (t < o) sh[t] += sh[t + o];
+        __syncthreads();
+    }
+    if (t == 0) mean_out[n] = (float)(sh[0] / (double)pixels);
 }
 
 static long long mean_staged_tiles(const ta_b200_fused_params *p)
@@ -206,7 +213,7 @@ static int gray_mean_staged(const ta_b200_fused_params *p, float *mean_out, floa
     void *args[] = {&k, &maps};
     cudaError_t e = cudaLaunchKernel(ke.fn, dim3((unsigned)grid), dim3(ke.threads), args, ke.smem, stream);
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernel(gray_mean, staged)");
-    mean_finish_kernel<<<p->n, 32, 0, stream>>>(partials, k.tiles_x * k.tiles_y * kConsumerWarps, p->oh * p->ow, mean_out);
+    mean_finish_kernel<<<p->n, 256, 0, stream>>>(partials, k.tiles_x * k.tiles_y * kConsumerWarps, p->oh * p->ow, mean_out);
     e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch(mean_finish)");
     return TA_B200_OK;
