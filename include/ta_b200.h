@@ -311,6 +311,9 @@ typedef struct ta_b200_sample_spec {
     int8_t   pad_[3];
     uint64_t torch_seed, torch_offset;
     const uint64_t *torch_state;
+    int32_t  first_sample;      /* the launch covers samples first_sample .. first_sample + total - 1 of a larger
+                                   batch (a shard): entry i of every output belongs to sample first_sample + i */
+    int32_t  pad2_;
 } ta_b200_sample_spec;
 
 int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream);

@@ -143,3 +143,24 @@ def test_other_classes_through_the_one_launch_sampler(name, kw, ndim):
     for want in outs[False]:
         assert torch.equal(g(), want)
     assert _gen().get_offset() == offsets[False]
+
+
+def test_a_rank_draws_only_its_own_slice():
+    """Per-rank sharding: every rank seeds alike, samples just its slice (the sampler computes
+    value i of a draw from the seed, the offset and i) and leaves its generator where the
+    whole-batch call leaves it; the slices tile the single-GPU result."""
+    import triton_augment_b200 as ta
+    aug = ta.TritonFusedAugment(**CONFIGS[0])
+    for shape, world in (((10, 3, 128, 144), 3), ((4, 3, 3, 128, 144), 2)):
+        x = torch.rand(shape, device=DEV)
+        torch.manual_seed(31)
+        want = aug(x)
+        end = _gen().get_offset()
+        flat_want = want.reshape(-1, *want.shape[-3:])
+        group = shape[1] if len(shape) == 5 else 1
+        flat = x.reshape(-1, *x.shape[-3:])
+        for rank, (a, b) in enumerate(ta.shard_bounds(flat.shape[0], world, group)):
+            torch.manual_seed(31)
+            got = ta.ShardedAugment.for_rank(aug, rank, world, device=DEV)((flat[a:b], shape))
+            assert _gen().get_offset() == end
+            assert torch.equal(got, flat_want[a:b]), (shape, rank)

@@ -180,7 +180,7 @@ def test_library_exports_every_declared_symbol():
     assert _lib.load().ta_b200_abi_version() == _lib.ABI_VERSION
     assert ctypes.sizeof(_lib.FusedParams) == 184       # sizeof(ta_b200_fused_params) on LP64 (168 before fill_rgb)
     assert _lib.FusedParams.fill_rgb.offset == 168      # the older layout ends here and is still accepted
-    assert ctypes.sizeof(_lib.SampleSpec) == 264 and _lib.SampleSpec.torch_compat.offset == 216     # the older layout ends at 216        # sizeof(ta_b200_sample_spec) on LP64
+    assert ctypes.sizeof(_lib.SampleSpec) == 272 and _lib.SampleSpec.torch_compat.offset == 216     # the older layout ends at 216        # sizeof(ta_b200_sample_spec) on LP64
 
 
 def test_a_failing_shard_does_not_stop_the_others():

@@ -64,6 +64,7 @@ class SampleSpec(C.Structure):
         ("scale_out", C.c_void_p), ("shear_out", C.c_void_p),
         ("torch_compat", C.c_int32), ("draw", C.c_int8 * 13), ("pad_", C.c_int8 * 3),
         ("torch_seed", C.c_uint64), ("torch_offset", C.c_uint64), ("torch_state", C.c_void_p),
+        ("first_sample", C.c_int32), ("pad2_", C.c_int32),
     ]
 
 

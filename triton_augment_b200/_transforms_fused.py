@@ -172,17 +172,19 @@ class TritonFusedAugment(T._BatchAware):
             return 0                      # the replay state must exist before the capture starts
         return _torch_rng.flags_for(dev)
 
-    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None, torch_flags: int = 0):
+    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None, torch_flags: int = 0, part=None):
         """Every per-sample parameter of one call from the library's sampler kernel: dict of
         device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
         (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
         scale, shear``, the draws behind the matrix).  ``torch_flags`` != 0: the values PyTorch's
         generator would give the reference's separate draws (and the generator is advanced
-        accordingly); 0: the library's own random stream, seeded by one PyTorch draw."""
+        accordingly); 0: the library's own random stream, seeded by one PyTorch draw.  ``part =
+        (start, stop)``: only the samples of that slice of the batch ``lay`` describes (a shard);
+        the values are those the whole-batch call gives these samples."""
         from . import _lib
         dev = lay.image.device if device is None else torch.device(device)     # host batches: where to sample
         h, w = lay.image.shape[2:]
-        total = lay.total
+        first, total = (0, lay.total) if part is None else (part[0], part[1] - part[0])
         seed = None
         if not torch_flags:
             seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
@@ -198,7 +200,7 @@ class TritonFusedAugment(T._BatchAware):
         ch = self.color_helper
         sp = _lib.SampleSpec()
         sp.struct_size = _lib.C.sizeof(_lib.SampleSpec)
-        sp.total, sp.frames = total, (lay.frames or 1)
+        sp.total, sp.frames, sp.first_sample = total, (lay.frames or 1), first
         sp.same_on_batch, sp.same_on_frame = int(self.same_on_batch), int(self.same_on_frame)
         sp.img_h, sp.img_w = h, w
         sp.crop_h, sp.crop_w = (self.crop_height or 0), (self.crop_width or 0)
@@ -245,15 +247,17 @@ class TritonFusedAugment(T._BatchAware):
         _lib.launch_sample_params(sp, dev)
         return out
 
-    def _forward_fast(self, lay, torch_flags: int = 0):
+    def _forward_fast(self, lay, torch_flags: int = 0, part=None, image=None):
+        """Sampler launch + fused kernel.  ``part`` / ``image``: run only the slice ``part`` of the
+        batch that ``lay`` describes, ``image`` holding that slice's samples."""
         from . import _lib
-        img = lay.image
+        img = lay.image if image is None else image
         h, w = img.shape[2:]
         if self.crop_height is not None and (self.crop_height > h or self.crop_width > w):
             raise ValueError(f"Crop size ({self.crop_height}, {self.crop_width}) is larger than the image ({h}, {w})")
         out_dtype = self.out_dtype if img.dtype == torch.uint8 else None
         work = F._work_dtype(img, out_dtype)
-        p = self._sample_fast(lay, work, torch_flags=torch_flags)
+        p = self._sample_fast(lay, work, torch_flags=torch_flags, part=part, device=img.device)
         flags = self.color_helper._colour_flags(affine=self.has_affine)
         mean, std = self.color_helper.mean, self.color_helper.std
         bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
@@ -265,7 +269,7 @@ class TritonFusedAugment(T._BatchAware):
                             p["brightness"], p["contrast"], p["saturation"], p["gray"],
                             F._rounded_triple(mean, work) if mean is not None else None,
                             F._rounded_triple(std, work) if std is not None else None, bits,
-                            F._contrast_mode(self.contrast_mode), out_dtype)
+                            F._contrast_mode(self.contrast_mode), out_dtype, first_image=part[0] if part else 0)
 
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         lay = self._layout(image)

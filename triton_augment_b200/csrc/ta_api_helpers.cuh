@@ -441,9 +441,10 @@ __global__ void sample_params_kernel(const __grid_constant__ ta_b200_sample_spec
 {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= s.total) return;
+    const int gi = s.first_sample + i;                   // the sample's index in the whole batch
     int p;
-    if (s.frames <= 1) p = s.same_on_batch ? 0 : i;
-    else p = (s.same_on_batch ? 0 : i / s.frames) * (s.same_on_frame ? 1 : s.frames) + (s.same_on_frame ? 0 : i % s.frames);
+    if (s.frames <= 1) p = s.same_on_batch ? 0 : gi;
+    else p = (s.same_on_batch ? 0 : gi / s.frames) * (s.same_on_frame ? 1 : s.frames) + (s.same_on_frame ? 0 : gi % s.frames);
     if (s.torch_compat) {
         const uint64_t seed = s.torch_state ? s.torch_state[0] : s.torch_seed;
         const uint64_t off4 = (s.torch_state ? s.torch_state[1] : s.torch_offset) >> 2;

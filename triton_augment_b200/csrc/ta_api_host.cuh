@@ -419,8 +419,9 @@ int ta_b200_sample_params(const ta_b200_sample_spec *spec, void *stream)
         const uint64_t off = spec->torch_state ? 0 : spec->torch_offset;
         if (off % 4 != 0) return ta::fail(TA_B200_ERR_UNSUPPORTED, "PyTorch generator offset %llu is not a multiple of 4", (unsigned long long)off);
     }
-    if (spec->total < 0 || spec->frames < 1 || spec->total % spec->frames != 0)
-        return ta::fail(TA_B200_ERR_SHAPE, "total = %d, frames = %d", spec->total, spec->frames);
+    if (spec->total < 0 || spec->frames < 1 || spec->first_sample < 0 ||
+        (spec->first_sample == 0 && spec->total % spec->frames != 0))
+        return ta::fail(TA_B200_ERR_SHAPE, "total = %d, frames = %d, first_sample = %d", spec->total, spec->frames, spec->first_sample);
     if (spec->img_h <= 0 || spec->img_w <= 0 || spec->crop_h < 0 || spec->crop_w < 0 || spec->crop_h > spec->img_h ||
         spec->crop_w > spec->img_w)
         return ta::fail(TA_B200_ERR_SHAPE, "image %dx%d, crop %dx%d", spec->img_h, spec->img_w, spec->crop_h, spec->crop_w);

@@ -120,6 +120,41 @@ class ShardedAugment:
         bounds = shard_bounds(lay.total, parts, lay.frames or 1)
         return lay, spread, bounds
 
+    def _one_launch_slice(self, flat, full_shape):
+        """Per-rank flavour, fast path: where the transform can draw its parameters with the
+        library's sampler in PyTorch-compatible mode, the rank draws ONLY its own slice - the
+        sampler computes value i of a draw from (seed, offset, i), so no rank needs the rest -
+        and advances its generator as the whole-batch draw would.  Same bits as plan() + _apply().
+        None when that path is not available."""
+        t = self.transform
+        if not (hasattr(t, "_torch_flags") and hasattr(t, "_forward_fast")) or getattr(t, "fast_rng", False):
+            return None
+        dev = self.devices[0]
+        if dev.type != "cuda":
+            return None
+        lay = self._meta_layout(full_shape, dev)
+        flags = t._torch_flags(lay, dev)
+        if not flags:
+            return None
+        start, stop = shard_bounds(lay.total, self._world, lay.frames or 1)[self._rank]
+        if flat.shape[0] != stop - start:
+            raise ValueError(f"rank {self._rank} owns samples [{start}, {stop}) but got {flat.shape[0]}")
+        with _on(dev):
+            return t._forward_fast(lay, flags, part=(start, stop), image=flat.to(dev))
+
+    def _meta_layout(self, batch_shape, param_device):
+        """Shape bookkeeping of a batch of ``batch_shape`` without any data."""
+        from .transforms import _Layout, _compute_param_count
+        meta = torch.empty(batch_shape, device="meta")
+        lay = _Layout.__new__(_Layout)
+        flat_shape, lay.batch, lay.frames, lay.shape, lay.was_3d = _meta_layout(meta)
+        lay.sob, lay.sof = self.transform.same_on_batch, self.transform.same_on_frame
+        lay.total = flat_shape[0]
+        lay.count = _compute_param_count(lay.batch, lay.frames, lay.sob, lay.sof)
+        lay.image = torch.empty(flat_shape, device="meta")
+        lay.param_device = torch.device(param_device)
+        return lay
+
     # ------------------------------------------------------------------ execution
     def __call__(self, batch, gather_to=None):
         """``batch``: one tensor holding the whole batch (host or any GPU; slices are copied to
@@ -127,9 +162,12 @@ class ShardedAugment:
         list of per-device outputs, or one tensor on ``gather_to`` if given."""
         if self._world is not None:
             local, full_shape = batch
+            flat = local.reshape(-1, *local.shape[-3:]) if local.ndim != 4 else local
+            fast = self._one_launch_slice(flat, full_shape)
+            if fast is not None:
+                return fast
             lay, spread, bounds = self.plan(full_shape, self.devices[0])
             start, stop = bounds[self._rank]
-            flat = local.reshape(-1, *local.shape[-3:]) if local.ndim != 4 else local
             if flat.shape[0] != stop - start:
                 raise ValueError(f"rank {self._rank} owns samples [{start}, {stop}) but got {flat.shape[0]}")
             with _on(self.devices[0]):
