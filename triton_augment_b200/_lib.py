@@ -147,6 +147,60 @@ def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+class RawPointer:
+    """A device address that quacks like a tensor for make_params() (`data_ptr()`): lets a caller
+    carve one allocation into many vectors without creating a tensor view per vector."""
+    __slots__ = ("address",)
+
+    def __init__(self, address: int):
+        self.address = address
+
+    def data_ptr(self) -> int:
+        return self.address
+
+
+def _index_of(device):
+    """Device index of a torch.device / "cuda:1" / 1 / None (None: whichever device is current)."""
+    if device is None or isinstance(device, int):
+        return device
+    if not isinstance(device, torch.device):
+        device = torch.device(device)
+    return device.index
+
+
+class _OnDevice:
+    """`with torch.cuda.device(d)` only when d is not current already (the switch costs microseconds)."""
+    __slots__ = ("guard",)
+
+    def __init__(self, device):
+        idx = _index_of(device)
+        self.guard = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(idx)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *a):
+        if self.guard is not None:
+            self.guard.__exit__(*a)
+
+
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream          # the current stream's handle without a Stream object
+except AttributeError:                                        # pragma: no cover - older or newer torch
+    _raw_stream = None
+
+
+def _stream(device) -> "C.c_void_p":
+    """torch's current stream on `device` as a cudaStream_t."""
+    idx = _index_of(device)
+    if idx is None:
+        idx = torch.cuda.current_device()
+    if _raw_stream is not None:
+        return C.c_void_p(_raw_stream(idx))
+    return C.c_void_p(torch.cuda.current_stream(idx).cuda_stream)
+
+
 def make_params(image, out, top, left, flip, matrix, fill, bilinear, apply_bits, brightness, contrast,
                 saturation, gray, mean, std, contrast_mode=CONTRAST_FAST, gray_mean=None) -> FusedParams:
     """Fill a FusedParams from tensors (device or host; the caller picks the entry point)."""
@@ -188,8 +242,8 @@ def launch_fused(params: FusedParams, device: torch.device, checked: bool = Fals
     """``first_image``: index of the first image within the batch this call is a piece of (see
     ta_b200_fused_augment_at in the header)."""
     lib = load()
-    with torch.cuda.device(device):
-        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    with _OnDevice(device):
+        stream = _stream(device)
         if checked:
             check(lib.ta_b200_debug_fused_checked(C.byref(params), stream), "ta_b200_fused_augment")
         elif first_image:
@@ -251,9 +305,8 @@ def inverse_affine_matrix(center, angle, translate, scale, shear) -> torch.Tenso
 
 def launch_sample_params(spec: SampleSpec, device: torch.device) -> None:
     """Enqueue the fused parameter sampler on torch's current stream of ``device``."""
-    with torch.cuda.device(device):
-        stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-        check(load().ta_b200_sample_params(C.byref(spec), stream), "ta_b200_sample_params")
+    with _OnDevice(device):
+        check(load().ta_b200_sample_params(C.byref(spec), _stream(device)), "ta_b200_sample_params")
 
 
 def store_words(dst: torch.Tensor, a: int, b: int) -> None:

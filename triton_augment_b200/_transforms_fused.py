@@ -172,40 +172,26 @@ class TritonFusedAugment(T._BatchAware):
             return 0                      # the replay state must exist before the capture starts
         return _torch_rng.flags_for(dev)
 
-    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None, torch_flags: int = 0, part=None):
-        """Every per-sample parameter of one call from the library's sampler kernel: dict of
-        device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
-        (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
-        scale, shear``, the draws behind the matrix).  ``torch_flags`` != 0: the values PyTorch's
-        generator would give the reference's separate draws (and the generator is advanced
-        accordingly); 0: the library's own random stream, seeded by one PyTorch draw.  ``part =
-        (start, stop)``: only the samples of that slice of the batch ``lay`` describes (a shard);
-        the values are those the whole-batch call gives these samples."""
+    def _static_spec(self, work_dtype, h, w, frames, torch_flags):
+        """The part of a sampler call that depends on the configuration and the image size only,
+        as a filled ta_b200_sample_spec (cached; the per-call fields are set by _sample_fast)."""
         from . import _lib
-        dev = lay.image.device if device is None else torch.device(device)     # host batches: where to sample
-        h, w = lay.image.shape[2:]
-        first, total = (0, lay.total) if part is None else (part[0], part[1] - part[0])
-        seed = None
-        if not torch_flags:
-            seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
-        words = 8 + 3 + (6 if want_draws else 0)                 # fp32 slots per sample: top, left, matrix(6), 3 factors, draws
-        buf = torch.empty(total * words * 4 + total * 2, dtype=torch.uint8, device=dev)
-        f32 = buf[: total * words * 4].view(torch.float32)
-        u8 = buf[total * words * 4:]
-        top, left, matrix = f32[:total], f32[total: 2 * total], f32[2 * total: 8 * total].view(total, 6)
-        factors = [f32[(8 + i) * total: (9 + i) * total] for i in range(3)]
-        if work_dtype == torch.float16:
-            factors = [f.view(torch.float16)[:total] for f in factors]
-        flip, gray = u8[:total], u8[total:]
         ch = self.color_helper
+        ah = self.affine_helper if self.has_affine else None
+        key = (work_dtype, h, w, frames, torch_flags, self.same_on_batch, self.same_on_frame, self.crop_height,
+               self.crop_width, self.horizontal_flip_p, ch.grayscale_p, ch.brightness, ch.contrast, ch.saturation,
+               (ah.degrees, ah.translate, ah.scale, ah.shear) if ah else None, self._draw_flip_always, self._draw_gray)
+        cache = self.__dict__.setdefault("_spec_cache", {})
+        hit = cache.get(key)
+        if hit is not None:
+            return hit
         sp = _lib.SampleSpec()
         sp.struct_size = _lib.C.sizeof(_lib.SampleSpec)
-        sp.total, sp.frames, sp.first_sample = total, (lay.frames or 1), first
+        sp.frames = frames
         sp.same_on_batch, sp.same_on_frame = int(self.same_on_batch), int(self.same_on_frame)
         sp.img_h, sp.img_w = h, w
         sp.crop_h, sp.crop_w = (self.crop_height or 0), (self.crop_width or 0)
         sp.factor_dtype = _lib.F16 if work_dtype == torch.float16 else _lib.F32
-        ah = self.affine_helper if self.has_affine else None
         sp.degrees[:] = ah.degrees if ah else (0.0, 0.0)
         sp.translate[:] = ah.translate if ah and ah.translate is not None else (0.0, 0.0)
         sp.scale[:] = ah.scale if ah and ah.scale is not None else (1.0, 1.0)
@@ -214,13 +200,39 @@ class TritonFusedAugment(T._BatchAware):
         sp.brightness[:] = ch.brightness or (1.0, 1.0)
         sp.contrast[:] = ch.contrast or (1.0, 1.0)
         sp.saturation[:] = ch.saturation or (1.0, 1.0)
+        draws = 0
         if torch_flags:
-            from . import _torch_rng
             plan, draws = self._draw_plan()
             sp.torch_compat = torch_flags
             sp.draw[:] = plan
             if ah and ah.translate is not None:           # pixels, multiplied in double like the reference
                 sp.translate[:] = (float(ah.translate[0] * w), float(ah.translate[1] * h))
+        if len(cache) > 32:
+            cache.clear()
+        cache[key] = (sp, draws)
+        return sp, draws
+
+    def _sample_fast(self, lay, work_dtype, want_draws: bool = False, device=None, torch_flags: int = 0, part=None,
+                     views: bool = True):
+        """Every per-sample parameter of one call from the library's sampler kernel: dict of
+        device tensors ``top, left, flip, gray, matrix, brightness, contrast, saturation``
+        (``matrix`` None without affine arguments; with ``want_draws`` also ``angle, translate,
+        scale, shear``, the draws behind the matrix).  ``torch_flags`` != 0: the values PyTorch's
+        generator would give the reference's separate draws (and the generator is advanced
+        accordingly); 0: the library's own random stream, seeded by one PyTorch draw.  ``part =
+        (start, stop)``: only the samples of that slice of the batch ``lay`` describes (a shard);
+        the values are those the whole-batch call gives these samples.  ``views=False``: the
+        entries are bare device addresses into one buffer (kept alive under ``"buffer"``) instead of
+        tensor views - all the fused launch needs, and a dozen tensor objects fewer per call."""
+        from . import _lib
+        dev = lay.image.device if device is None else torch.device(device)     # host batches: where to sample
+        h, w = lay.image.shape[2:]
+        first, total = (0, lay.total) if part is None else (part[0], part[1] - part[0])
+        sp, draws = self._static_spec(work_dtype, h, w, lay.frames or 1, torch_flags)
+        sp.total, sp.first_sample = total, first
+        seed = None
+        if torch_flags:
+            from . import _torch_rng
             gen = _torch_rng.generator_of(dev)
             if getattr(self, "_torch_state", None) is None or self._torch_state.device != dev:
                 self._torch_state = torch.zeros(2, dtype=torch.int64, device=dev)      # (seed, offset) for graph replays
@@ -229,22 +241,41 @@ class TritonFusedAugment(T._BatchAware):
                 _torch_rng.CAPTURED.append((self._torch_state, draws))
             else:
                 offset = gen.get_offset()
+                sp.torch_state = None
                 sp.torch_seed, sp.torch_offset = gen.initial_seed(), offset
                 gen.set_offset(offset + 4 * draws)                 # what the separate draws would have consumed
         else:
+            seed = torch.randint(-2 ** 63, 2 ** 63 - 1, (1,), dtype=torch.int64, device=dev)    # one draw from torch's generator
             sp.seed = seed.data_ptr()
-        sp.top, sp.left, sp.flip, sp.gray = top.data_ptr(), left.data_ptr(), flip.data_ptr(), gray.data_ptr()
-        sp.matrix = matrix.data_ptr() if self.has_affine else None
-        sp.brightness_out, sp.contrast_out, sp.saturation_out = (f.data_ptr() for f in factors)
-        out = dict(top=top, left=left, flip=flip, gray=gray, matrix=matrix if self.has_affine else None,
+        words = 8 + 3 + (6 if want_draws else 0)                 # fp32 slots per sample: top, left, matrix(6), 3 factors, draws
+        buf = torch.empty(total * words * 4 + total * 2, dtype=torch.uint8, device=dev)
+        base = buf.data_ptr()
+        at = lambda slot: base + 4 * total * slot                # address of fp32 slot `slot`
+        sp.top, sp.left, sp.matrix = at(0), at(1), (at(2) if self.has_affine else None)
+        sp.brightness_out, sp.contrast_out, sp.saturation_out = at(8), at(9), at(10)
+        sp.flip, sp.gray = at(words), at(words) + total
+        if want_draws:
+            sp.angle_out, sp.translate_out, sp.scale_out, sp.shear_out = at(11), at(12), at(14), at(15)
+        else:
+            sp.angle_out = sp.translate_out = sp.scale_out = sp.shear_out = None
+        _lib.launch_sample_params(sp, dev)
+        if not views:
+            R = _lib.RawPointer
+            return dict(top=R(at(0)), left=R(at(1)), flip=R(at(words)), gray=R(at(words) + total),
+                        matrix=R(at(2)) if self.has_affine else None, brightness=R(at(8)), contrast=R(at(9)),
+                        saturation=R(at(10)), buffer=buf, seed=seed)
+        f32 = buf[: total * words * 4].view(torch.float32)
+        u8 = buf[total * words * 4:]
+        factors = [f32[(8 + i) * total: (9 + i) * total] for i in range(3)]
+        if work_dtype == torch.float16:
+            factors = [f.view(torch.float16)[:total] for f in factors]
+        out = dict(top=f32[:total], left=f32[total: 2 * total], flip=u8[:total], gray=u8[total:],
+                   matrix=f32[2 * total: 8 * total].view(total, 6) if self.has_affine else None,
                    brightness=factors[0], contrast=factors[1], saturation=factors[2])
         if want_draws:
             d = f32[11 * total:]
             out.update(angle=d[:total], translate=d[total: 3 * total].view(total, 2), scale=d[3 * total: 4 * total],
                        shear=d[4 * total: 6 * total].view(total, 2))
-            sp.angle_out, sp.translate_out = out["angle"].data_ptr(), out["translate"].data_ptr()
-            sp.scale_out, sp.shear_out = out["scale"].data_ptr(), out["shear"].data_ptr()
-        _lib.launch_sample_params(sp, dev)
         return out
 
     def _forward_fast(self, lay, torch_flags: int = 0, part=None, image=None):
@@ -257,7 +288,7 @@ class TritonFusedAugment(T._BatchAware):
             raise ValueError(f"Crop size ({self.crop_height}, {self.crop_width}) is larger than the image ({h}, {w})")
         out_dtype = self.out_dtype if img.dtype == torch.uint8 else None
         work = F._work_dtype(img, out_dtype)
-        p = self._sample_fast(lay, work, torch_flags=torch_flags, part=part, device=img.device)
+        p = self._sample_fast(lay, work, torch_flags=torch_flags, part=part, device=img.device, views=False)
         flags = self.color_helper._colour_flags(affine=self.has_affine)
         mean, std = self.color_helper.mean, self.color_helper.std
         bits = ((_lib.APPLY_BRIGHTNESS if flags["brightness"] else 0) | (_lib.APPLY_CONTRAST if flags["contrast"] else 0)
