@@ -119,6 +119,11 @@ def test_graph_replays_follow_the_eager_sequence():
     ("TritonColorJitterNormalize", dict(contrast=0.5, contrast_mode="torchvision")),
     ("TritonRandomCropFlip", dict(size=(90, 70), horizontal_flip_p=0.5)),
     ("TritonRandomCropFlip", dict(size=64, horizontal_flip_p=0.0)),          # the flip draw happens even for p = 0
+    ("TritonRandomCrop", dict(size=(100, 77))),
+    ("TritonRandomHorizontalFlip", dict(p=0.5)),
+    ("TritonRandomAffine", dict(degrees=25, translate=(0.1, 0.2), scale=(0.8, 1.2), shear=(-5, 5, -3, 3), interpolation="bilinear", fill=0.25)),
+    ("TritonRandomAffine", dict(degrees=(-10, 40), interpolation="nearest")),
+    ("TritonRandomRotation", dict(degrees=30, interpolation="bilinear")),
 ])
 @pytest.mark.parametrize("ndim", [4, 5])
 def test_other_classes_through_the_one_launch_sampler(name, kw, ndim):

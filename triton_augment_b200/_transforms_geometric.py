@@ -75,10 +75,20 @@ class TritonRandomCrop(T._BatchAware):
             raise ValueError(f"Image size ({h}, {w}) is smaller than crop size ({th}, {tw}). "
                              f"Padding not yet supported in MVP." if (ph, pw) == (h, w) else
                              f"Padded image size ({ph}, {pw}) is smaller than crop size ({th}, {tw}).")
+        if (ph, pw) == (h, w) and self.fill in (0, 0.0):
+            out = self._through_fused(image, self._twin)           # top and left from the one-launch sampler
+            if out is not None:
+                return out
         top, left = _draw_offsets(lay, ph, pw, th, tw, torch.int32)
         if top_pad or left_pad:
             top, left = top - top_pad, left - left_pad
         return lay.restore(F.crop(lay.image, lay.spread(top), lay.spread(left), th, tw, fill=self.fill))
+
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        t = TritonFusedAugment(crop_size=self.size, same_on_batch=self.same_on_batch, same_on_frame=self.same_on_frame)
+        t._draw_gray = False                     # this class draws top and left only
+        return t
 
     def __repr__(self):
         return f"{self.__class__.__name__}(size={self.size}, " + self._tail()
@@ -112,9 +122,18 @@ class TritonRandomHorizontalFlip(T._BatchAware):
     def forward(self, image: torch.Tensor) -> torch.Tensor:
         if self.p == 0:
             return image
+        out = self._through_fused(image, self._twin)
+        if out is not None:
+            return out
         lay = self._layout(image)
         mask = lay.spread(F._sample_bernoulli_tensor(lay.count, self.p, lay.param_device))
         return lay.restore(F.horizontal_flip(lay.image, flip_mask=mask))
+
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        t = TritonFusedAugment(horizontal_flip_p=self.p, same_on_batch=self.same_on_batch, same_on_frame=self.same_on_frame)
+        t._draw_gray = False                     # this class draws the flip mask only
+        return t
 
     def __repr__(self):
         return f"{self.__class__.__name__}(p={self.p}, " + self._tail()
@@ -231,7 +250,25 @@ class TritonRandomAffine(T._BatchAware):
             shear = torch.zeros((param_count, 2), device=device)
         return angle, translate, scale, shear
 
+    def _twin(self):
+        from ._transforms_fused import TritonFusedAugment
+        t = TritonFusedAugment(degrees=self.degrees, translate=self.translate, scale=self.scale, shear=self.shear,
+                               interpolation=self.interpolation, fill=self.fill, same_on_batch=self.same_on_batch,
+                               same_on_frame=self.same_on_frame)
+        t._draw_gray = False                     # this class draws the affine parameters only
+        return t
+
     def forward(self, img: torch.Tensor) -> torch.Tensor:
+        # (a rotation centre other than the image's goes into the matrix, which the sampler builds for the
+        #  image centre; a zero-width angle range with nothing else set would make the twin skip the angle draw)
+        if self.center is None and (self.degrees != (0.0, 0.0) or self.translate is not None or self.scale is not None
+                                    or self.shear is not None):
+            twin = self.__dict__.get("_fused_twin")
+            if twin is not None:                 # attributes that tests and users change after construction
+                twin.interpolation, twin.fill = self.interpolation, self.fill
+            out = self._through_fused(img, self._twin)
+            if out is not None:
+                return out
         lay = self._layout(img)
         h, w = lay.image.shape[2:]
         angle, translate, scale, shear = self._get_params(lay.count, lay.param_device, (h, w))
