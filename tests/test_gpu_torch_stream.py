@@ -169,3 +169,24 @@ def test_a_rank_draws_only_its_own_slice():
             got = ta.ShardedAugment.for_rank(aug, rank, world, device=DEV)((flat[a:b], shape))
             assert _gen().get_offset() == end
             assert torch.equal(got, flat_want[a:b]), (shape, rank)
+
+
+def test_a_capture_by_someone_else_keeps_pytorch_draws():
+    """Only GraphedTransform refreshes the sampler's generator state before a replay; a graph that
+    the user captures directly must therefore fall back to PyTorch's own (graph-safe) draws, so
+    that its replays keep producing fresh parameters."""
+    import triton_augment_b200 as ta
+    aug = ta.TritonFusedAugment(**CONFIGS[1])
+    x = torch.rand(6, 3, 128, 144, device=DEV)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            aug(x)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = aug(x)
+    g.replay(); a = out.clone()
+    g.replay(); b = out.clone()
+    assert not torch.equal(a, b)                                  # fresh parameters on every replay

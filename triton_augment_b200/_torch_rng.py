@@ -25,6 +25,10 @@ _FLAGS = {}            # device index -> torch_compat value (0: unavailable)
 # Sampler launches recorded while a CUDA graph is being captured: (state tensor, draws), in launch
 # order.  GraphedTransform empties it before a capture and keeps what the capture added.
 CAPTURED = []
+# True only while GraphedTransform captures: it is the one that refreshes the captured launches'
+# generator state before every replay.  A capture started by anyone else keeps PyTorch's own
+# draws (whose graph-safe generator advances by itself on replay).
+REPLAY_MANAGED = False
 DRAW_SLOTS = ("angle", "tx", "ty", "scale", "shear_x", "shear_y", "top", "left", "flip", "brightness", "contrast",
               "saturation", "gray")
 

@@ -168,8 +168,13 @@ class TritonFusedAugment(T._BatchAware):
             return 0
         if lay.count > _torch_rng.max_values_per_draw(dev):
             return 0
-        if torch.cuda.is_current_stream_capturing() and getattr(self, "_torch_state", None) is None:
-            return 0                      # the replay state must exist before the capture starts
+        if torch.cuda.is_current_stream_capturing():
+            # only under GraphedTransform, which refreshes the state before each replay, and only if the
+            # state words exist already (nothing may be allocated and zeroed inside the capture)
+            if not _torch_rng.REPLAY_MANAGED or getattr(self, "_torch_state", None) is None:
+                return 0
+        elif _torch_rng.generator_of(dev).get_offset() % 4:
+            return 0                      # PyTorch itself only ever leaves multiples of 4
         return _torch_rng.flags_for(dev)
 
     def _static_spec(self, work_dtype, h, w, frames, torch_flags):

@@ -55,8 +55,12 @@ class GraphedTransform:
         self.graph = torch.cuda.CUDAGraph()
         from . import _torch_rng
         del _torch_rng.CAPTURED[:]
-        with torch.cuda.device(device), torch.cuda.graph(self.graph):
-            self.static_output = transform(example)
+        _torch_rng.REPLAY_MANAGED = True
+        try:
+            with torch.cuda.device(device), torch.cuda.graph(self.graph):
+                self.static_output = transform(example)
+        finally:
+            _torch_rng.REPLAY_MANAGED = False
         # A transform that draws its parameters inside the library in PyTorch-compatible mode has
         # captured a launch that reads the generator's (seed, offset) from device memory: every
         # replay is preceded by a refresh of those two words (per captured sampler launch, each
