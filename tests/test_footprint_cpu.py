@@ -42,8 +42,9 @@ def _matrix(rng, deg, tr, sc, sh, h, w):
 
 
 def _check_image(bilinear, elem_bytes, h, w, oh, ow, top, left, flip, m):
-    tw, th, max_rows = _lib.tile_shape()[:3]
-    pitch = _lib.tile_shape()[{4: 3, 2: 4, 1: 5}[elem_bytes]]
+    shape = _lib.tile_shape()
+    tw, th, max_rows = (shape[0], shape[6], shape[7]) if elem_bytes == 2 else shape[:3]      # half pixels: taller tiles
+    pitch = shape[{4: 3, 2: 4, 1: 5}[elem_bytes]]
     chunk = 16 // elem_bytes
     staged = 0
     for ty in range((oh + th - 1) // th):
@@ -109,3 +110,21 @@ def test_degenerate_matrices_are_not_staged():
         rows, *_ = _lib.tile_footprint(True, 4, 64, 64, 64, 64, 0.0, 0.0, False, np.array(m, f32), 0, 0)
         if rows:   # the all-zero matrix maps the tile to one point, which does fit
             assert np.allclose(m, 0)
+
+
+def test_half_pixel_benchmark_geometry_is_always_staged():
+    """512x512 -> 448x448 half images with the benchmark's parameter ranges: the taller tiles of
+    the half-pixel kernels (64 x 64, up to 96 source rows) must all fit the staging buffer."""
+    rng = np.random.default_rng(2)
+    shape = _lib.tile_shape()
+    tw, th = shape[0], shape[6]
+    assert th == 64 and shape[7] == 96
+    for _ in range(40):
+        m = _matrix(rng, 15, 0.1, (0.9, 1.1), 5, 512, 512)
+        top, left = float(rng.integers(0, 65)), float(rng.integers(0, 65))
+        nx, ny = (448 + tw - 1) // tw, (448 + th - 1) // th
+        for tx in range(nx):
+            for ty in range(ny):
+                for flip in (False, True):
+                    rows, *_ = _lib.tile_footprint(True, 2, 512, 512, 448, 448, top, left, flip, m, tx, ty)
+                    assert 0 < rows <= 96

@@ -364,15 +364,16 @@ def debug_counters(reset: bool = False):
 
 
 def tile_shape():
-    """(tile width, tile height, source-row capacity, staged row pitch for 4-, 2-, 1-byte elements)."""
-    buf = (C.c_int32 * 6)()
+    """(tile width, tile height and source-row capacity for float pixels, staged row pitch for 4-, 2-,
+    1-byte elements, tile height and source-row capacity for half pixels)."""
+    buf = (C.c_int32 * 8)()
     load().ta_b200_debug_tile_shape(buf)
     return tuple(int(x) for x in buf)
 
 
 def tile_footprint(bilinear, elem_bytes, h, w, oh, ow, top, left, flip, matrix, tile_x, tile_y):
     """Host-side evaluation of the staged kernel's footprint for one tile (tests)."""
-    cap = tile_shape()[2]
+    cap = max(tile_shape()[2], tile_shape()[7])
     row0 = C.c_int32(0)
     xs = (C.c_int32 * cap)()
     xe = (C.c_int32 * cap)()

@@ -56,9 +56,16 @@ constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one produce
 // before the reference's pipeline) on the way from shared memory to registers.
 template <typename S> struct Src {
     static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : sizeof(S) == 2 ? kPitchBytes2 : kPitch;   // staged row pitch, elements
-    static constexpr int plane = kMaxRows * pitch;                         // elements per channel per stage
     static constexpr int chunk = 16 / (int)sizeof(S);                      // elements per 16 bytes
 };
+// Tile height, source-row capacity and row groups of a kernel whose OUTPUT pixels are T (ta_footprint.h).
+template <typename T> struct Tile {
+    static constexpr int H = sizeof(T) == 2 ? kTileHHalf : kTileH;
+    static constexpr int ROWS = sizeof(T) == 2 ? kMaxRowsHalf : kMaxRows;
+    static constexpr int GROUPS = ROWS / kGroupRows;
+};
+// Elements per channel per stage.
+template <typename T, typename S> struct Stage { static constexpr int plane = Tile<T>::ROWS * Src<S>::pitch; };
 constexpr float kInv255 = 1.0f / 255.0f;
 
 // Texel of type S -> pixel of type T.
@@ -106,7 +113,7 @@ template <> struct Px<__half, uint8_t> {
     static __device__ __forceinline__ uint8_t lds(uint32_t addr) { return Px<float, uint8_t>::lds(addr); }
 };
 
-constexpr int kNumGroups = kMaxRows / kGroupRows;
+constexpr int kNumGroups = kMaxRowsAny / kGroupRows;      // tensor maps built per launch (a kernel uses its first Tile<T>::GROUPS)
 constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
 
 // The input seen as [N*C, H, W].  rows[g] copies a box of Src::pitch columns x (g + 1) * kGroupRows
@@ -126,7 +133,7 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int pad3[3];
     Geom g;
     Colour<T, C, F> col;
-    int rowoff[kMaxRows + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
+    int rowoff[Tile<T>::ROWS + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
 };
 
 // Shared memory: kStages pixel stages, then kInfoSlots tile descriptors.  Tile number i of a CTA
@@ -134,7 +141,7 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
 // of the stage's next tile while the consumers still read the current one, and only the copy
 // itself has to wait for the stage to be released.
 template <typename T, int C, unsigned F, typename S = T> struct AffineSmem {
-    static constexpr size_t stage = ((size_t)C * Src<S>::plane * sizeof(S) + 1023) / 1024 * 1024;
+    static constexpr size_t stage = ((size_t)C * Stage<T, S>::plane * sizeof(S) + 1023) / 1024 * 1024;
     static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
     static constexpr size_t total = kStages * stage + kInfoSlots * info;
 };

@@ -66,7 +66,7 @@ namespace ta {
 //
 // Table path: each row group has its own first column; rowoff[] translates.
 template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSampler {
-    static constexpr int PITCH = Src<S>::pitch, PLANE = Src<S>::plane;
+    static constexpr int PITCH = Src<S>::pitch, PLANE = Stage<T, S>::plane;
     static constexpr uint32_t ES = sizeof(S), ROWB = ES * PITCH, PLANEB = ES * PLANE;
     using P = Px<T, S>;
     using Pair = typename PairOf<T>::type;
@@ -232,7 +232,7 @@ __device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__hal
 
 // A consumer warp's share of a tile.  Float pixels: 32 columns x kRowsPerWarp rows, a lane owns one
 // column and pairs the rows (full 128-byte lines per store instruction).  Half pixels: all 64
-// columns x kTileH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
+// columns x Tile<T>::H / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
 // so that a store is one 32-bit half2, a warp's store a full 128-byte line again, and shared
 // memory is read at 4-byte lane stride (no bank conflicts) as in the float case.
 // The mean of one image from its partial sums.  The order of the additions is part of the result,
@@ -337,8 +337,9 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     constexpr bool PAIR_X = sizeof(T) == 2;
     static_assert(!PAIR_X || (!MIX && !REDUCE && !TWO), "the per-pixel recipe and the mean pre-pass exist for float pixels only");
     static_assert(!TWO || (!REDUCE && !MIX && (F & kMean)), "the two-phase kernel is the mean-contrast pipeline");
-    constexpr int ROWS_PER_WARP = PAIR_X ? kTileH / kConsumerWarps : kRowsPerWarp;
-    static_assert(!PAIR_X || (kTileW == 64 && kTileH % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
+    constexpr int ROWS_PER_WARP = PAIR_X ? Tile<T>::H / kConsumerWarps : kRowsPerWarp;
+    static_assert(!PAIR_X || (kTileW == 64 && Tile<T>::H % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
+    static_assert(PAIR_X || Tile<T>::H == 2 * kRowsPerWarp * kConsumerWarps / 4, "two warps side by side per strip of rows");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);

@@ -26,10 +26,19 @@
 
 namespace ta {
 
-constexpr int kTileW = 64;       // output tile, pixels
-constexpr int kTileH = 32;
-constexpr int kMaxRows = 64;     // source rows one staged tile may span (8 groups of 8 rows)
+constexpr int kTileW = 64;       // output tile width, pixels
+// Tile height and the number of source rows one staged tile may span depend on the size of an
+// OUTPUT pixel.  Float pixels: 64 x 32 tiles, 64 rows (8 groups of 8).  Half pixels move half the
+// bytes per pixel, so a stage of the same size holds a 64 x 64 tile's footprint (96 rows): a
+// consumer thread then handles eight pixels per tile instead of four, which halves what the
+// per-tile bookkeeping (barrier wait, descriptor, pointers, coordinates of the column) costs per
+// pixel - and that bookkeeping is about half of all instructions of these kernels.
+constexpr int kTileH = 32, kMaxRows = 64;
+constexpr int kTileHHalf = 64, kMaxRowsHalf = 96;
+constexpr int kMaxRowsAny = kMaxRowsHalf;
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
+TA_HD int tile_h_of(int out_bytes) { return out_bytes == 2 ? kTileHHalf : kTileH; }
+TA_HD int max_rows_of(int out_bytes) { return out_bytes == 2 ? kMaxRowsHalf : kMaxRows; }
 // Staged row pitch = width of every tensor-copy box, in elements.  A pitch that is a multiple
 // of 32 words keeps lanes of one warp that sit in different source rows on different banks
 // (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but 2-way bank conflicts cost
@@ -58,11 +67,12 @@ struct TileFootprint {
 // Corners, rows and bounding box.  mode: 0 nearest (reads row rint(sy)), 1 bilinear (reads rows
 // floor(sy), floor(sy)+1).  rows == 0 on return: the tile is not staged.
 TA_HD void tile_footprint(TileFootprint &t, int mode, int h, int w, int oh, int ow,
-                          float top, float left, bool flip, const float *m, int tile_x, int tile_y)
+                          float top, float left, bool flip, const float *m, int tile_x, int tile_y,
+                          int tile_h = kTileH, int max_rows = kMaxRows)
 {
-    const int x_first = tile_x * kTileW, y_first = tile_y * kTileH;
+    const int x_first = tile_x * kTileW, y_first = tile_y * tile_h;
     const int x_last = (x_first + kTileW < ow ? x_first + kTileW : ow) - 1;
-    const int y_last = (y_first + kTileH < oh ? y_first + kTileH : oh) - 1;
+    const int y_last = (y_first + tile_h < oh ? y_first + tile_h : oh) - 1;
     const float half_w = 0.5f * (float)w, half_h = 0.5f * (float)h;
     const float xi0 = (float)(flip ? ow - 1 - x_last : x_first) + left;
     const float xi1 = (float)(flip ? ow - 1 - x_first : x_last) + left;
@@ -89,7 +99,7 @@ TA_HD void tile_footprint(TileFootprint &t, int mode, int h, int w, int oh, int 
     if (mode == 0) { r0 = (int)ceilf(ymin - kEps - 0.5f); r1 = (int)floorf(ymax + kEps + 0.5f); }
     else           { r0 = (int)floorf(ymin - kEps);       r1 = (int)floorf(ymax + kEps) + 1; }
     const int rows = r1 - r0 + 1;
-    if (rows < 1 || rows > kMaxRows) return;
+    if (rows < 1 || rows > max_rows) return;
     t.row0 = r0;
     t.rows = rows;
 }
@@ -118,11 +128,12 @@ TA_HD bool tile_window(const TileFootprint &t, int mode, int chunk, int pitch, i
 // Crop / flip without a matrix: source pixel = (int)(x_img), (int)(y_img) (truncation, as the
 // crop kernels do), monotone in x and y, so the tile's first and last pixel give the exact
 // range.  Fills xmin / xmax / row0 / rows only; the window always exists (a tile is kTileW wide).
-TA_HD void tile_footprint_crop(TileFootprint &t, int oh, int ow, float top, float left, bool flip, int tile_x, int tile_y)
+TA_HD void tile_footprint_crop(TileFootprint &t, int oh, int ow, float top, float left, bool flip, int tile_x, int tile_y,
+                               int tile_h = kTileH, int max_rows = kMaxRows)
 {
-    const int x_first = tile_x * kTileW, y_first = tile_y * kTileH;
+    const int x_first = tile_x * kTileW, y_first = tile_y * tile_h;
     const int x_last = (x_first + kTileW < ow ? x_first + kTileW : ow) - 1;
-    const int y_last = (y_first + kTileH < oh ? y_first + kTileH : oh) - 1;
+    const int y_last = (y_first + tile_h < oh ? y_first + tile_h : oh) - 1;
     const float xa = (float)(flip ? ow - 1 - x_last : x_first) + left;
     const float xb = (float)(flip ? ow - 1 - x_first : x_last) + left;
     const float ya = (float)y_first + top, yb = (float)y_last + top;
@@ -133,7 +144,7 @@ TA_HD void tile_footprint_crop(TileFootprint &t, int oh, int ow, float top, floa
     t.xmin = (float)(int)xa;
     t.xmax = (float)(int)xb;
     const int r0 = (int)ya, r1 = (int)yb;
-    if (r1 - r0 + 1 > kMaxRows) return;
+    if (r1 - r0 + 1 > max_rows) return;
     t.row0 = r0;
     t.rows = r1 - r0 + 1;
 }
@@ -200,19 +211,20 @@ TA_HD bool tile_rows_range(const TileFootprint &t, int mode, int chunk, int r_fi
 
 // What is actually fetched.  Window case: all rows, `pitch` columns from *group_xs.  Otherwise
 // rows in groups of kGroupRows, every group `pitch` columns from the smallest xs of its rows
-// (group_xs has kMaxRows / kGroupRows entries).  Scalar restatement of the producer warp's
+// (group_xs has max_rows / kGroupRows entries).  Scalar restatement of the producer warp's
 // decisions; returns false when the tile is not staged.
-TA_HD bool tile_plan(TileFootprint &t, int mode, int chunk, int pitch, const float *m, int *group_xs, bool *window)
+TA_HD bool tile_plan(TileFootprint &t, int mode, int chunk, int pitch, const float *m, int *group_xs, bool *window,
+                     int max_rows = kMaxRows)
 {
     if (t.rows == 0) return false;
     int xs;
     *window = tile_window(t, mode, chunk, pitch, xs);
     if (*window) {
-        for (int g = 0; g < kMaxRows / kGroupRows; ++g) group_xs[g] = xs;
+        for (int g = 0; g < max_rows / kGroupRows; ++g) group_xs[g] = xs;
         return true;
     }
     if (!tile_edges(t, mode, chunk, pitch, m)) return false;
-    for (int g = 0; g < kMaxRows / kGroupRows; ++g) {
+    for (int g = 0; g < max_rows / kGroupRows; ++g) {
         int lo = 0, hi = chunk;
         const int r_first = g * kGroupRows;
         const int r_last = r_first + kGroupRows - 1 < t.rows - 1 ? r_first + kGroupRows - 1 : t.rows - 1;
