@@ -365,9 +365,9 @@ int ta_b200_debug_crop_path(int32_t path);
  * when the copy plan is cheaper than whole slices (default), 0 = upload every image whole, 2 =
  * boxes for every call on large images.  Identical output; for tests and measurements. */
 int ta_b200_debug_host_upload(int32_t trimmed);
-/* Tile shape of the staged affine kernel: out[0] = width, out[1] = height and out[2] = source-row
- * capacity for float output pixels, out[3], out[4], out[5] = staged row pitch in elements for 4-, 2-
- * and 1-byte source elements, out[6] = height and out[7] = row capacity for half output pixels. */
+/* Tile shape of the staged affine kernel: out[0] = width, out[1] = height, out[2] = source-row
+ * capacity, out[3], out[4], out[5] = staged row pitch in elements for 4-, 2- and 1-byte source
+ * elements; out[6], out[7] repeat height and row capacity (half output pixels once had their own). */
 void ta_b200_debug_tile_shape(int32_t out[8]);
 
 #ifdef __cplusplus

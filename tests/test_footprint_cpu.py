@@ -43,7 +43,7 @@ def _matrix(rng, deg, tr, sc, sh, h, w):
 
 def _check_image(bilinear, elem_bytes, h, w, oh, ow, top, left, flip, m):
     shape = _lib.tile_shape()
-    tw, th, max_rows = (shape[0], shape[6], shape[7]) if elem_bytes == 2 else shape[:3]      # half pixels: taller tiles
+    tw, th, max_rows = shape[:3]
     pitch = shape[{4: 3, 2: 4, 1: 5}[elem_bytes]]
     chunk = 16 // elem_bytes
     staged = 0
@@ -113,12 +113,12 @@ def test_degenerate_matrices_are_not_staged():
 
 
 def test_half_pixel_benchmark_geometry_is_always_staged():
-    """512x512 -> 448x448 half images with the benchmark's parameter ranges: the taller tiles of
-    the half-pixel kernels (64 x 64, up to 96 source rows) must all fit the staging buffer."""
+    """512x512 -> 448x448 half images with the benchmark's parameter ranges: every 64 x 64 tile
+    (up to 96 source rows) must fit the staging buffer."""
     rng = np.random.default_rng(2)
     shape = _lib.tile_shape()
-    tw, th = shape[0], shape[6]
-    assert th == 64 and shape[7] == 96
+    tw, th = shape[:2]
+    assert th == 64 and shape[2] == 96 and tuple(shape[6:8]) == (64, 96)
     for _ in range(40):
         m = _matrix(rng, 15, 0.1, (0.9, 1.1), 5, 512, 512)
         top, left = float(rng.integers(0, 65)), float(rng.integers(0, 65))

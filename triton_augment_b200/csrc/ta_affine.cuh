@@ -3,7 +3,7 @@
 //
 // Persistent, warp-specialised, one CTA per SM.  The CTA walks output tiles of
 // kTileW x kTileH pixels (grid-stride).  PRODUCER warps (one per stage) work ahead of the
-// CONSUMER warps through a ring of kStages shared-memory stages:
+// CONSUMER warps through a ring of shared-memory stages (Src<S>::stages of them):
 //
 //   producer  for each tile: map the tile's corners to the source (ta_footprint.h).  When
 //             their bounding box fits one window of columns - the usual case - plan one TMA
@@ -34,22 +34,20 @@
 
 namespace ta {
 
-// Launch shape, chosen by measurement on the 1280x1280 -> 1024x1024 workload.  Two consumer
-// warps side by side per strip of four tile rows, so the tile height sets the warp count:
-//   64x32 tiles, 16 consumer warps, 3 stages: bilinear 283 us, nearest 262 us, and the light
-//                variants (no colour work, matrix-free) 258-265 us                     <- built
-//   64x40 tiles, 20 warps: bilinear 273 us, nearest 256 us, but the light variants 305-332 us,
-//                and a tile needs up to 64 source rows already at 15 degrees / scale 1.1, so
-//                larger rotations would leave the staged path
-//   64x36 tiles, 18 warps: 283 / 261 us; 64x28, 14 warps: 306 / 281 us
-//   64x48 tiles, 24 warps, 2 stages (what then fits): 389 us; 64x24, 24 warps, 4 stages: 350 us
-//   64x28 tiles, 28 warps with one row pair per thread (64 registers): 322 / 289 us
-//   64x32 tiles, 8 warps with four row pairs per thread: bilinear +2 %, half pixels +12 %
-constexpr int kRowsPerWarp = 4;                                // a thread's pixels: this many rows of one column
+// Launch shape, chosen by measurement on the 1280x1280 -> 1024x1024 workload (times: bilinear /
+// nearest, power-capped clocks).  About half of a consumer thread's instructions are per-tile
+// bookkeeping (barrier wait, descriptor, pointers, the column's coordinates), so the pixels a
+// thread handles per tile matter more than the depth of the ring:
+//   64x64 tiles, 16 consumer warps x 8 pixels per thread, 96 source rows; float sources fit two
+//                such stages in shared memory, half and byte sources three: 298 / 269 us  <- built
+//   64x32 tiles, 16 warps x 4 pixels, 64 rows, 3 stages: 322 / 275 us (half pixels: +14 %)
+//   64x48 tiles, 16 warps x 6 pixels, 80 rows, 2 stages: 322 / 290 us (48 does not divide 1024)
+//   64x40 tiles, 20 warps x 4 pixels, 3 stages: 3 % faster than 64x32, light variants 20 % slower
+//   64x36 / 64x28 / 64x24 tiles with 18 / 14 / 24 warps x 4 pixels: equal or slower than 64x32
+//   64x32 tiles, 8 warps x 8 pixels: bilinear +2 %, half pixels +12 % (too few warps to hide latency)
+constexpr int kRowsPerWarp = 8;                                // float pixels: a thread's pixels are this many rows of one column
 constexpr int kConsumerWarps = 2 * kTileH / kRowsPerWarp;      // two warps side by side per strip of rows
 static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are handled in pairs");
-constexpr int kStages = 3;
-constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one producer warp per stage
 
 // Source element type S of a staged kernel whose pixels are T: S = T for float and half
 // images; S = uint8_t with T = float or half reads bytes and scales them by 1/255 (what ToTensor does
@@ -57,15 +55,12 @@ constexpr int kAffineThreads = (kConsumerWarps + kStages) * 32;   // one produce
 template <typename S> struct Src {
     static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : sizeof(S) == 2 ? kPitchBytes2 : kPitch;   // staged row pitch, elements
     static constexpr int chunk = 16 / (int)sizeof(S);                      // elements per 16 bytes
-};
-// Tile height, source-row capacity and row groups of a kernel whose OUTPUT pixels are T (ta_footprint.h).
-template <typename T> struct Tile {
-    static constexpr int H = sizeof(T) == 2 ? kTileHHalf : kTileH;
-    static constexpr int ROWS = sizeof(T) == 2 ? kMaxRowsHalf : kMaxRows;
-    static constexpr int GROUPS = ROWS / kGroupRows;
+    static constexpr int stages = sizeof(S) == 4 ? 2 : 3;                  // ring depth: what fits 227 KB of shared memory
+    static constexpr int info_slots = 2 * stages;                          // tile descriptors: two per stage (see AffineSmem)
+    static constexpr int threads = (kConsumerWarps + stages) * 32;         // one producer warp per stage
 };
 // Elements per channel per stage.
-template <typename T, typename S> struct Stage { static constexpr int plane = Tile<T>::ROWS * Src<S>::pitch; };
+template <typename S> struct Stage { static constexpr int plane = kMaxRows * Src<S>::pitch; };
 constexpr float kInv255 = 1.0f / 255.0f;
 
 // Texel of type S -> pixel of type T.
@@ -113,8 +108,7 @@ template <> struct Px<__half, uint8_t> {
     static __device__ __forceinline__ uint8_t lds(uint32_t addr) { return Px<float, uint8_t>::lds(addr); }
 };
 
-constexpr int kNumGroups = kMaxRowsAny / kGroupRows;      // tensor maps built per launch (a kernel uses its first Tile<T>::GROUPS)
-constexpr int kInfoSlots = 2 * kStages;            // tile descriptors: two per stage (see AffineSmem)
+constexpr int kNumGroups = kMaxRows / kGroupRows;         // tensor maps built per launch
 
 // The input seen as [N*C, H, W].  rows[g] copies a box of Src::pitch columns x (g + 1) * kGroupRows
 // rows of one plane: a window tile is one copy per channel.  rows[0] doubles as the per-group
@@ -133,17 +127,18 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int pad3[3];
     Geom g;
     Colour<T, C, F> col;
-    int rowoff[Tile<T>::ROWS + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
+    int rowoff[kMaxRows + 1];         // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
 };
 
-// Shared memory: kStages pixel stages, then kInfoSlots tile descriptors.  Tile number i of a CTA
-// uses stage i % kStages and descriptor i % kInfoSlots, so the producer can write the descriptor
+// Shared memory: Src<S>::stages pixel stages, then Src<S>::info_slots tile descriptors.  Tile number i of a CTA
+// uses stage i % stages and descriptor i % info_slots, so the producer can write the descriptor
 // of the stage's next tile while the consumers still read the current one, and only the copy
 // itself has to wait for the stage to be released.
 template <typename T, int C, unsigned F, typename S = T> struct AffineSmem {
-    static constexpr size_t stage = ((size_t)C * Stage<T, S>::plane * sizeof(S) + 1023) / 1024 * 1024;
+    static constexpr size_t stage = ((size_t)C * Stage<S>::plane * sizeof(S) + 1023) / 1024 * 1024;
     static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
-    static constexpr size_t total = kStages * stage + kInfoSlots * info;
+    static constexpr size_t total = Src<S>::stages * stage + Src<S>::info_slots * info;
+    static_assert(total <= 227 * 1024, "stages and descriptors must fit one CTA's shared memory");
 };
 
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, int x, int y, int z, uint64_t *bar)

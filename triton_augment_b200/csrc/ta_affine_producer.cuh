@@ -1,5 +1,5 @@
 // Producer role of the staged affine kernel.  There is one producer warp per stage of the
-// ring: warp p fills stage p for the CTA's tiles p, p + kStages, p + 2 kStages, ...
+// ring: warp p fills stage p for the CTA's tiles p, p + stages, p + 2 stages, ...
 //
 // Per tile the warp (1) works out the source footprint and writes the tile's descriptor, (2)
 // waits until the consumers have released the stage, (3) issues the copies.  Only (3) sits
@@ -38,9 +38,9 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
 {
     using Info = TileInfo<T, C, F>;
     using Smem = AffineSmem<T, C, F, S>;
-    constexpr int CH = Src<S>::chunk, PITCH = Src<S>::pitch, PLANE = Stage<T, S>::plane;
-    constexpr int TILE_H = Tile<T>::H, MAX_ROWS = Tile<T>::ROWS, GROUPS = Tile<T>::GROUPS;
-    static_assert(GROUPS <= 32 && MAX_ROWS % kGroupRows == 0 && GROUPS <= kNumGroups, "one lane per row group");
+    constexpr int CH = Src<S>::chunk, PITCH = Src<S>::pitch, PLANE = Stage<S>::plane;
+    constexpr int STAGES = Src<S>::stages;
+    static_assert(kNumGroups <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
     const int lane = threadIdx.x & 31;
     const int tiles_per_img = k.tiles_x * k.tiles_y;
     S *stage = reinterpret_cast<S *>(smem + p * Smem::stage);
@@ -49,11 +49,11 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
     Geom g;
     Colour<T, C, F> col;
 
-    // Tile number -> (image, tile row, tile column), then stepped by kStages * gridDim.x tiles per
+    // Tile number -> (image, tile row, tile column), then stepped by STAGES * gridDim.x tiles per
     // round with carries instead of divisions.  Consecutive tile numbers are neighbours along x:
     // the CTAs running at one time then read whole runs of image rows (DRAM page hits) and share
     // the overlap of their boxes in L2; an order that interleaves images was 20-50 % slower.
-    const int first = (int)blockIdx.x + p * (int)gridDim.x, step = kStages * (int)gridDim.x;
+    const int first = (int)blockIdx.x + p * (int)gridDim.x, step = STAGES * (int)gridDim.x;
     int n = first / tiles_per_img, ty = (first % tiles_per_img) / k.tiles_x, tx = (first % tiles_per_img) % k.tiles_x;
     const int step_n = step / tiles_per_img, step_ty = (step % tiles_per_img) / k.tiles_x,
               step_tx = (step % tiles_per_img) % k.tiles_x;
@@ -100,7 +100,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             col.init(k, n);
             cur_n = n;
         }
-        Info *ti = reinterpret_cast<Info *>(smem + kStages * Smem::stage + (size_t)(p + kStages * (use & 1)) * Smem::info);
+        Info *ti = reinterpret_cast<Info *>(smem + STAGES * Smem::stage + (size_t)(p + STAGES * (use & 1)) * Smem::info);
 
         // ---- (1) footprint and descriptor
         TileFootprint fp;
@@ -109,8 +109,8 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         const float m[6] = {g.a, g.b, g.c, g.d, g.e, g.f};
         constexpr int FMODE = MODE == 2 ? 1 : 0;            // footprint rule: nearest or bilinear
         if (k.staged_ok) {
-            if (MODE == 0) tile_footprint_crop(fp, k.oh, k.ow, g.top, g.left, g.flip, tx, ty, TILE_H, MAX_ROWS);
-            else tile_footprint(fp, FMODE, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty, TILE_H, MAX_ROWS);
+            if (MODE == 0) tile_footprint_crop(fp, k.oh, k.ow, g.top, g.left, g.flip, tx, ty);
+            else tile_footprint(fp, FMODE, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
         }
         bool staged = fp.rows > 0, window = false;
         int gxs = 0;
@@ -126,7 +126,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                 column_range(FMODE, fp.xmin, fp.xmax, c0, c1);
                 inside = c0 >= 0 && c1 < k.w;
             } else {
-                // lanes 0 .. GROUPS-1: columns of row group `lane`; the other lanes hold a neutral entry
+                // lanes 0 .. kNumGroups-1: columns of row group `lane`; the other lanes hold a neutral entry
                 staged = tile_edges(fp, FMODE, CH, PITCH, m);
                 int xs = 0, xe = CH;
                 const int r_first = lane * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
@@ -138,12 +138,12 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                 if (staged) {
                     // rowoff[r] = r * PITCH - (first column of r's group); rows lane, lane + 32, ...
 #pragma unroll
-                    for (int base = 0; base < MAX_ROWS; base += 32) {      // same trip count in every lane
+                    for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
                         const int r = base + lane;
-                        const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, GROUPS - 1));
-                        if (r < MAX_ROWS) ti->rowoff[r] = r * PITCH - x_first;
+                        const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, kNumGroups - 1));
+                        if (r < kMaxRows) ti->rowoff[r] = r * PITCH - x_first;
                     }
-                    if (lane == 0) ti->rowoff[MAX_ROWS] = 0;
+                    if (lane == 0) ti->rowoff[kMaxRows] = 0;
                 }
             }
             // fill != 0 cannot rely on the copy's zero fill: stage only tiles that stay inside the image
@@ -155,7 +155,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             ti->col = col;
             ti->n = n;
             ti->x0 = tx * kTileW;
-            ti->y0 = ty * TILE_H;
+            ti->y0 = ty * kTileH;
             ti->rows = staged ? fp.rows : 0;
             ti->row0 = fp.row0;
             ti->window = (window ? 1 : 0) | (phase << 1);

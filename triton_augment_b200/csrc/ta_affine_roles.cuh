@@ -66,7 +66,7 @@ namespace ta {
 //
 // Table path: each row group has its own first column; rowoff[] translates.
 template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSampler {
-    static constexpr int PITCH = Src<S>::pitch, PLANE = Stage<T, S>::plane;
+    static constexpr int PITCH = Src<S>::pitch, PLANE = Stage<S>::plane;
     static constexpr uint32_t ES = sizeof(S), ROWB = ES * PITCH, PLANEB = ES * PLANE;
     using P = Px<T, S>;
     using Pair = typename PairOf<T>::type;
@@ -232,7 +232,7 @@ __device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__hal
 
 // A consumer warp's share of a tile.  Float pixels: 32 columns x kRowsPerWarp rows, a lane owns one
 // column and pairs the rows (full 128-byte lines per store instruction).  Half pixels: all 64
-// columns x Tile<T>::H / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
+// columns x kTileH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
 // so that a store is one 32-bit half2, a warp's store a full 128-byte line again, and shared
 // memory is read at 4-byte lane stride (no bank conflicts) as in the float case.
 // The mean of one image from its partial sums.  The order of the additions is part of the result,
@@ -334,12 +334,13 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     using Sampler = PairSampler<T, C, MODE, CHECK, S>;
     using Smem = AffineSmem<T, C, F, S>;
     using Pair = typename PairOf<T>::type;
+    constexpr int STAGES = Src<S>::stages, INFO_SLOTS = Src<S>::info_slots;
     constexpr bool PAIR_X = sizeof(T) == 2;
     static_assert(!PAIR_X || (!MIX && !REDUCE && !TWO), "the per-pixel recipe and the mean pre-pass exist for float pixels only");
     static_assert(!TWO || (!REDUCE && !MIX && (F & kMean)), "the two-phase kernel is the mean-contrast pipeline");
-    constexpr int ROWS_PER_WARP = PAIR_X ? Tile<T>::H / kConsumerWarps : kRowsPerWarp;
-    static_assert(!PAIR_X || (kTileW == 64 && Tile<T>::H % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
-    static_assert(PAIR_X || Tile<T>::H == 2 * kRowsPerWarp * kConsumerWarps / 4, "two warps side by side per strip of rows");
+    constexpr int ROWS_PER_WARP = PAIR_X ? kTileH / kConsumerWarps : kRowsPerWarp;
+    static_assert(!PAIR_X || (kTileW == 64 && kTileH % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
+    static_assert(PAIR_X || kTileH == 2 * kRowsPerWarp * kConsumerWarps / 4, "two warps side by side per strip of rows");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
@@ -350,13 +351,13 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
     Const2 k2;
     k2.set();
     Colour<T, C, F> col;
-    // the CTA's tile number i uses stage i % kStages (for the (i / kStages)-th time) and descriptor i % kInfoSlots
+    // the CTA's tile number i uses stage i % STAGES (for the (i / STAGES)-th time) and descriptor i % INFO_SLOTS
     int s = 0, slot = 0;
     uint32_t phase = 0;
     for (int tile = blockIdx.x; tile < k.num_tiles; tile += gridDim.x) {
         if (!mbar_wait_or_abort(&full[s], phase, abort_flag, k.wait_ns)) return;
         const S *stage = reinterpret_cast<const S *>(smem + s * Smem::stage);
-        const Info *ti = reinterpret_cast<const Info *>(smem + kStages * Smem::stage + (size_t)slot * Smem::info);
+        const Info *ti = reinterpret_cast<const Info *>(smem + STAGES * Smem::stage + (size_t)slot * Smem::info);
         const int4 h0 = *reinterpret_cast<const int4 *>(&ti->n);       // n, x0, y0, rows
         const int4 h1 = *reinterpret_cast<const int4 *>(&ti->row0);    // row0, window, xs0, -
         const int n = h0.x, rows = h0.w, row0 = h1.x;
@@ -523,8 +524,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         }
         if (lane == 0) mbar_arrive(&empty[s]);
         if (TWO && threadIdx.x == 0) *(volatile unsigned *)&two_phase_checkin[4] += 1u;     // heartbeat for the finisher
-        if (++s == kStages) { s = 0; phase ^= 1u; }
-        if (++slot == kInfoSlots) slot = 0;
+        if (++s == STAGES) { s = 0; phase ^= 1u; }
+        if (++slot == INFO_SLOTS) slot = 0;
     }
     if (CHECK && n_viol && k.counters) atomicAdd(k.counters + kCntViolation, n_viol);
 }
@@ -535,19 +536,19 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 // TWO: reduction and fused pass of the mean-contrast pipeline in one (cooperative) launch.
 template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T, bool REDUCE = false,
           bool TWO = false>
-__global__ void __launch_bounds__(kAffineThreads + (TWO ? 32 : 0), 1)
+__global__ void __launch_bounds__(Src<S>::threads + (TWO ? 32 : 0), 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
     // Used as declared (no pointer arithmetic through integers), so the compiler keeps every
     // access in the shared address space.  Tensor copies without swizzle need 16-byte alignment.
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) uint64_t full[kStages];
-    __shared__ __align__(8) uint64_t empty[kStages];
+    __shared__ __align__(8) uint64_t full[Src<S>::stages];
+    __shared__ __align__(8) uint64_t empty[Src<S>::stages];
     __shared__ int abort_flag;
     __shared__ unsigned two_phase_checkin[5];       // [0..3] consumer check-ins per image in flight, [4] consumer heartbeat
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kStages; ++i) {
+        for (int i = 0; i < Src<S>::stages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], kConsumerWarps);
         }
@@ -557,7 +558,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     }
     __syncthreads();
 
-    if (TWO && (threadIdx.x >> 5) >= kConsumerWarps + kStages)
+    if (TWO && (threadIdx.x >> 5) >= kConsumerWarps + Src<S>::stages)
         two_phase_finisher(k, &abort_flag, &two_phase_checkin[4]);
     else if ((threadIdx.x >> 5) >= kConsumerWarps)
         affine_producer<T, C, MODE, F, S, TWO>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
@@ -575,7 +576,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
                 __threadfence_system();
             }
         }
-        if (threadIdx.x < kStages) {
+        if (threadIdx.x < Src<S>::stages) {
             for (int i = 0; i < 4096; ++i)
                 if (mbar_try_wait(&full[threadIdx.x], 0) || mbar_try_wait(&full[threadIdx.x], 1)) break;
         }

@@ -271,7 +271,7 @@ static EncodeTiledFn encode_tiled_fn()
 }
 
 // Tensor maps over the input seen as [n*c, h, w]: boxes of pitch_of(element size) columns x 8, 16,
-// ... kMaxRowsAny rows x 1 plane, out-of-range elements read as zero.
+// ... kMaxRows rows x 1 plane, out-of-range elements read as zero.
 static int build_tensor_maps(TMaps &maps, const ta_b200_fused_params *p)
 {
     EncodeTiledFn enc = encode_tiled_fn();
@@ -360,9 +360,8 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         k.tiles_y = (p->oh + kDirectRows - 1) / kDirectRows;
         work = ((long long)p->n * k.tiles_x * k.tiles_y + kWarps - 1) / kWarps;      // CTAs needed at one strip per warp
     } else {
-        const int tile_h = tile_h_of((int)out_bytes(p->dtype));
         k.tiles_x = (p->ow + kTileW - 1) / kTileW;
-        k.tiles_y = (p->oh + tile_h - 1) / tile_h;
+        k.tiles_y = (p->oh + kTileH - 1) / kTileH;
         work = (long long)p->n * k.tiles_x * k.tiles_y;
     }
     const long long tiles = (long long)p->n * k.tiles_x * k.tiles_y;

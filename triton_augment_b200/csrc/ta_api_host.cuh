@@ -477,13 +477,11 @@ int ta_b200_debug_tile_footprint(int32_t interp, int32_t elem_bytes, int32_t h, 
     ta::TileFootprint fp;
     const int chunk = 16 / (elem_bytes == 1 ? 1 : elem_bytes == 2 ? 2 : 4), pitch = ta::pitch_of(elem_bytes);
     const int mode = interp == TA_B200_BILINEAR ? 1 : 0;
-    // (the tile shape follows the output pixel: half images give half pixels, the others float here)
-    const int tile_h = ta::tile_h_of(elem_bytes == 2 ? 2 : 4), max_rows = ta::max_rows_of(elem_bytes == 2 ? 2 : 4);
-    ta::tile_footprint(fp, mode, h, w, oh, ow, top, left, flip != 0, matrix, tile_x, tile_y, tile_h, max_rows);
+    ta::tile_footprint(fp, mode, h, w, oh, ow, top, left, flip != 0, matrix, tile_x, tile_y);
     if (row0) *row0 = fp.row0;
-    int group_xs[ta::kMaxRowsAny / ta::kGroupRows];
+    int group_xs[ta::kMaxRows / ta::kGroupRows];
     bool window = false;
-    if (!ta::tile_plan(fp, mode, chunk, pitch, matrix, group_xs, &window, max_rows)) return 0;
+    if (!ta::tile_plan(fp, mode, chunk, pitch, matrix, group_xs, &window)) return 0;
     for (int r = 0; r < fp.rows && r < cap; ++r) {
         xs[r] = group_xs[r / ta::kGroupRows];
         xe[r] = xs[r] + pitch;
@@ -502,7 +500,7 @@ void ta_b200_debug_tile_shape(int32_t out[8])
 {
     out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows;
     out[3] = ta::pitch_of(4); out[4] = ta::pitch_of(2); out[5] = ta::pitch_of(1);
-    out[6] = ta::kTileHHalf; out[7] = ta::kMaxRowsHalf;
+    out[6] = ta::kTileH; out[7] = ta::kMaxRows;      // (half pixels: the same shape as the others)
 }
 
 }  // extern "C"

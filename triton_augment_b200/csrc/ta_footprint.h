@@ -27,18 +27,10 @@
 namespace ta {
 
 constexpr int kTileW = 64;       // output tile width, pixels
-// Tile height and the number of source rows one staged tile may span depend on the size of an
-// OUTPUT pixel.  Float pixels: 64 x 32 tiles, 64 rows (8 groups of 8).  Half pixels move half the
-// bytes per pixel, so a stage of the same size holds a 64 x 64 tile's footprint (96 rows): a
-// consumer thread then handles eight pixels per tile instead of four, which halves what the
-// per-tile bookkeeping (barrier wait, descriptor, pointers, coordinates of the column) costs per
-// pixel - and that bookkeeping is about half of all instructions of these kernels.
-constexpr int kTileH = 32, kMaxRows = 64;
-constexpr int kTileHHalf = 64, kMaxRowsHalf = 96;
-constexpr int kMaxRowsAny = kMaxRowsHalf;
+// Output tile height, and the number of source rows one staged tile may span (12 groups of 8):
+// a 64 x 64 tile under +-15 degrees of rotation, 5 degrees of shear and scale 0.9 reads ~90 rows.
+constexpr int kTileH = 64, kMaxRows = 96;
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
-TA_HD int tile_h_of(int out_bytes) { return out_bytes == 2 ? kTileHHalf : kTileH; }
-TA_HD int max_rows_of(int out_bytes) { return out_bytes == 2 ? kMaxRowsHalf : kMaxRows; }
 // Staged row pitch = width of every tensor-copy box, in elements.  A pitch that is a multiple
 // of 32 words keeps lanes of one warp that sit in different source rows on different banks
 // (narrower boxes of 72 / 80 elements were tried: less L2 traffic, but 2-way bank conflicts cost

@@ -48,16 +48,16 @@ template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename 
     else if constexpr (KIND >= 5) {
         if constexpr ((F & kMean) != 0 && !CHECK)
             return KernelEntry{(const void *)&affine_kernel<T, C, KIND - 5, F, false, false, S, false, true>,
-                               AffineSmem<T, C, F, S>::total, kAffineThreads + 32};      // + the finisher warp
+                               AffineSmem<T, C, F, S>::total, Src<S>::threads + 32};      // + the finisher warp
         else return KernelEntry{nullptr, 0, 0};
     }
     else if constexpr (KIND == 4) {
         if constexpr (CoordRecipe<2, F>::swapped && !CHECK)
             return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true, S>, AffineSmem<T, C, F, S>::total,
-                               kAffineThreads};
+                               Src<S>::threads};
         else return KernelEntry{nullptr, 0, 0};
     } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK, false, S>,
-                              AffineSmem<T, C, F, S>::total, kAffineThreads};
+                              AffineSmem<T, C, F, S>::total, Src<S>::threads};
 }
 
 template <typename T, int C, unsigned F> KernelEntry vec_entry()
@@ -100,7 +100,7 @@ KernelEntry mean_kernel_entry(int mode, bool bright, int channels, bool bytes);
 template <int C, int MODE, unsigned F, typename S> KernelEntry mean_entry()
 {
     return KernelEntry{(const void *)&affine_kernel<float, C, MODE, F, false, false, S, true>,
-                       AffineSmem<float, C, F, S>::total, kAffineThreads};
+                       AffineSmem<float, C, F, S>::total, Src<S>::threads};
 }
 
 // Defined one per translation unit (ta_inst_*.cu).
