@@ -400,37 +400,46 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
                 const float2 xc = MODE == 0 ? f2(truncf(xi0), truncf(xi1)) : f2(centred(xi0, g.half_w), centred(xi1, g.half_w));
                 const bool whole = k.pair_store != 0 && h0.y + kTileW <= k.ow;       // the same for every lane
-                float2 ys_keep = f2(0.0f, 0.0f);
                 static_assert(ROWS_PER_WARP % 2 == 0, "the row coordinates are computed two rows at a time");
+                // The strip's rows, compiled twice: a tile whose rows and pairs all lie inside the
+                // image and whose rows share one window (almost all tiles) needs no row clamps, no
+                // store predicates and no per-row choice of the sampling path.
+                auto rows_of_pairs = [&](auto fast_tile) {
+                    constexpr bool FAST = decltype(fast_tile)::value;
+                    float2 ys_keep = f2(0.0f, 0.0f);
 #pragma unroll
-                for (int r = 0; r < ROWS_PER_WARP; ++r) {
-                    // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred(); two rows at once
-                    float2 ys;
-                    if ((r & 1) == 0) {
-                        const int ya = min(y_first + r, k.oh - 1), yb = min(y_first + r + 1, k.oh - 1);
-                        ys = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
-                        ys = pk_add(ys, g2.top);
-                        if (MODE != 0) ys = pk_add(pk_add(ys, g2.neg_half_h), k2.half);
-                        ys_keep = ys;
-                    } else {
-                        ys = ys_keep;
+                    for (int r = 0; r < ROWS_PER_WARP; ++r) {
+                        // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred(); two rows at once
+                        float2 ys;
+                        if ((r & 1) == 0) {
+                            const int ya = FAST ? y_first + r : min(y_first + r, k.oh - 1);
+                            const int yb = FAST ? y_first + r + 1 : min(y_first + r + 1, k.oh - 1);
+                            ys = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
+                            ys = pk_add(ys, g2.top);
+                            if (MODE != 0) ys = pk_add(pk_add(ys, g2.neg_half_h), k2.half);
+                            ys_keep = ys;
+                        } else {
+                            ys = ys_keep;
+                        }
+                        // no early exit: a row past the image's last row is computed on the last row's geometry
+                        const bool row_ok = FAST || y_first + r < k.oh;
+                        float2 sx, sy;
+                        if (MODE == 0) {
+                            sx = xc;
+                            sy = bcast(truncf((r & 1) ? ys.y : ys.x));
+                        } else {
+                            const float2 yc = bcast((r & 1) ? ys.y : ys.x);
+                            sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                            sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                        }
+                        Pair smp[C];
+                        if (FAST || window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
+                        else                Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
+                        if constexpr (!REDUCE) finish_pair_x<C, F>(k, col, smp, plane, r, row_bytes, FAST || whole, row_ok, FAST || pair_ok);
                     }
-                    // no early exit: a row past the image's last row is computed on the last row's geometry
-                    const bool row_ok = y_first + r < k.oh;
-                    float2 sx, sy;
-                    if (MODE == 0) {
-                        sx = xc;
-                        sy = bcast(truncf((r & 1) ? ys.y : ys.x));
-                    } else {
-                        const float2 yc = bcast((r & 1) ? ys.y : ys.x);
-                        sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                        sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
-                    }
-                    Pair smp[C];
-                    if (window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
-                    else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                    if constexpr (!REDUCE) finish_pair_x<C, F>(k, col, smp, plane, r, row_bytes, whole, row_ok, pair_ok);
-                }
+                };
+                if (window && whole && y_first + ROWS_PER_WARP <= k.oh) rows_of_pairs(std::true_type{});
+                else rows_of_pairs(std::false_type{});
             } else {
                 // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
                 const float2 xc = bcast(MODE == 0 ? truncf(img_x(g, k.ow, x)) : centred(img_x(g, k.ow, x), g.half_w));
