@@ -1,0 +1,106 @@
+"""The staged kernel runs float images on 64 x 64 tiles (ring of two stages) or, for small outputs,
+on 64 x 32 tiles (ring of three).  The arithmetic per pixel is the same, so the two shapes must give
+the same bits; the choice by output height must be the documented one."""
+import pytest
+import torch
+
+from conftest import MEAN, STD
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+@pytest.fixture
+def tile_height():
+    from triton_augment_b200 import _lib
+    yield _lib.tile_height
+    _lib.tile_height(0)
+
+
+def _case(n, c, h, w, oh, ow, seed):
+    import triton_augment_b200 as ta
+    dev = _dev()
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    img = torch.rand(n, c, h, w, generator=g).to(dev)
+    u = lambda lo, hi: torch.empty(n).uniform_(lo, hi, generator=g).to(dev)
+    top = torch.randint(0, h - oh + 1, (n,), generator=g).float().to(dev)
+    left = torch.randint(0, w - ow + 1, (n,), generator=g).float().to(dev)
+    flip = (torch.rand(n, generator=g) < 0.5).to(torch.uint8).to(dev)
+    tr = torch.stack([u(-0.1 * w, 0.1 * w), u(-0.1 * h, 0.1 * h)], 1)
+    sh = torch.stack([u(-5, 5), torch.zeros(n, device=dev)], 1)
+    matrix = ta.functional._prepare_affine_matrix_only(n, dev, h, w, u(-15, 15), tr, u(0.9, 1.1), sh, None).contiguous()
+    colour = (u(0.8, 1.2), u(0.8, 1.2), u(0.8, 1.2), (torch.rand(n, generator=g) < 0.3).to(dev))
+    return img, top, left, flip, matrix, colour
+
+
+def _launch(case, oh, ow, bilinear, flags, matrix=True, checked=False):
+    from triton_augment_b200 import _lib
+    img, top, left, flip, m, (b, cf, s, gray) = case
+    n, c = img.shape[:2]
+    out = torch.full((n, c, oh, ow), -7.0, dtype=torch.float32, device=img.device)
+    norm = bool(flags & 16)
+    p = _lib.make_params(img, out, top, left, flip, m if matrix else None, 0.0, bilinear, flags, b, cf, s, gray,
+                         MEAN if norm else None, STD if norm else None)
+    _lib.launch_fused(p, img.device, checked=checked)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("bilinear", [False, True])
+@pytest.mark.parametrize("shape", [(6, 3, 256, 256, 224, 224), (9, 3, 96, 96, 96, 96), (3, 3, 640, 704, 600, 641),
+                                   (5, 1, 128, 160, 75, 133), (4, 3, 80, 64, 17, 40)])
+def test_both_tile_shapes_give_the_same_bits(tile_height, shape, bilinear):
+    from triton_augment_b200 import _lib
+    n, c, h, w, oh, ow = shape
+    case = _case(n, c, h, w, oh, ow, seed=oh + ow)
+    outs = []
+    for rows in (32, 64):
+        tile_height(rows)
+        for flags in ((31, 0, 21) if c == 3 else (19, 0)):
+            _lib.debug_counters(reset=True)
+            outs.append(_launch(case, oh, ow, bilinear, flags))
+            staged, direct, violations, timeouts = _lib.debug_counters()
+            assert timeouts == 0 and staged + direct == n * -(-ow // 64) * -(-oh // rows)
+    half = len(outs) // 2
+    for a, b in zip(outs[:half], outs[half:]):
+        assert torch.equal(a, b)
+        assert not bool((a == -7.0).any())                 # every pixel written
+
+
+def test_short_tiles_pass_the_staging_checks(tile_height):
+    """The checked build counts every sample that would leave the staged footprint."""
+    from triton_augment_b200 import _lib
+    tile_height(32)
+    for bilinear in (False, True):
+        case = _case(7, 3, 256, 320, 224, 224, seed=3)
+        _lib.debug_counters(reset=True)
+        got = _launch(case, 224, 224, bilinear, 0, checked=True)
+        staged, direct, violations, timeouts = _lib.debug_counters()
+        assert violations == 0 and timeouts == 0 and staged > 0
+        tile_height(64)
+        assert torch.equal(got, _launch(case, 224, 224, bilinear, 0))
+        tile_height(32)
+
+
+def test_shape_is_chosen_by_output_height(tile_height):
+    """64-row tiles unless their last row would be at most half full and a tenth of the rows empty."""
+    from triton_augment_b200 import _lib
+    tile_height(0)
+    for oh, rows in [(224, 32), (96, 32), (32, 32), (288, 32), (352, 64), (112, 64), (128, 64), (608, 64), (48, 64)]:
+        case = _case(2, 3, oh + 8, 136, oh, 128, seed=oh)
+        _lib.debug_counters(reset=True)
+        _launch(case, oh, 128, False, 31)
+        staged, direct, _, _ = _lib.debug_counters()
+        assert staged + direct == 2 * 2 * -(-oh // rows), (oh, rows, staged, direct)
+    # matrix-free calls through the staged kernel follow the same rule
+    _lib.crop_path(2)
+    try:
+        case = _case(2, 3, 232, 136, 224, 128, seed=1)
+        _lib.debug_counters(reset=True)
+        _launch(case, 224, 128, False, 31, matrix=False)
+        assert sum(_lib.debug_counters()[:2]) == 2 * 2 * 7
+    finally:
+        _lib.crop_path(0)

@@ -29,7 +29,7 @@ SYMBOLS = (
     "ta_b200_debug_crop_path", "ta_b200_debug_host_upload", "ta_b200_sample_params",
     "ta_b200_debug_tile_shape", "ta_b200_status", "ta_b200_host_release", "ta_b200_debug_wait",
     "ta_b200_fused_augment_mean", "ta_b200_fused_augment_mean_scratch_bytes", "ta_b200_mean_path",
-    "ta_b200_store_words",
+    "ta_b200_store_words", "ta_b200_debug_tile_height",
 )
 
 
@@ -107,6 +107,8 @@ def load():
     lib.ta_b200_sample_params.restype = C.c_int
     lib.ta_b200_debug_crop_path.argtypes = [C.c_int32]
     lib.ta_b200_debug_crop_path.restype = C.c_int
+    lib.ta_b200_debug_tile_height.argtypes = [C.c_int32]
+    lib.ta_b200_debug_tile_height.restype = C.c_int
     lib.ta_b200_debug_host_upload.argtypes = [C.c_int32]
     lib.ta_b200_debug_host_upload.restype = C.c_int
     lib.ta_b200_debug_counters.argtypes = [C.POINTER(C.c_uint64), C.c_int]
@@ -319,6 +321,11 @@ def store_words(dst: torch.Tensor, a: int, b: int) -> None:
 def crop_path(path: int) -> None:
     """0: pick the kernel for matrix-free calls by size, 1: crop kernels only, 2: staged kernel (tests)."""
     check(load().ta_b200_debug_crop_path(int(path)), "ta_b200_debug_crop_path")
+
+
+def tile_height(rows: int) -> None:
+    """Tile height of the staged kernel for float images: 0 = by output height, 32 or 64 = forced (tests)."""
+    check(load().ta_b200_debug_tile_height(int(rows)), "ta_b200_debug_tile_height")
 
 
 def host_upload(mode: int) -> None:

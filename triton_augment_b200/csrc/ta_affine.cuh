@@ -3,7 +3,7 @@
 //
 // Persistent, warp-specialised, one CTA per SM.  The CTA walks output tiles of
 // kTileW x kTileH pixels (grid-stride).  PRODUCER warps (one per stage) work ahead of the
-// CONSUMER warps through a ring of shared-memory stages (Src<S>::stages of them):
+// CONSUMER warps through a ring of shared-memory stages (Ring<S, TH>::stages of them):
 //
 //   producer  for each tile: map the tile's corners to the source (ta_footprint.h).  When
 //             their bounding box fits one window of columns - the usual case - plan one TMA
@@ -45,9 +45,19 @@ namespace ta {
 //   64x40 tiles, 20 warps x 4 pixels, 3 stages: 3 % faster than 64x32, light variants 20 % slower
 //   64x36 / 64x28 / 64x24 tiles with 18 / 14 / 24 warps x 4 pixels: equal or slower than 64x32
 //   64x32 tiles, 8 warps x 8 pixels: bilinear +2 %, half pixels +12 % (too few warps to hide latency)
-constexpr int kRowsPerWarp = 8;                                // float pixels: a thread's pixels are this many rows of one column
-constexpr int kConsumerWarps = 2 * kTileH / kRowsPerWarp;      // two warps side by side per strip of rows
-static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are handled in pairs");
+// Small outputs of float images take the 64x32 shape with three stages instead (TH = kTileHShort):
+// with few tiles per image many are edge tiles with little work, and then the depth of the ring -
+// how many tiles' copies are in flight - decides: 4096 x 3 x 96^2 nearest 185 us against 228 us,
+// 1024 x 3 x 256^2 -> 224^2 224 against 234 us; from 320 rows on the tall shape wins.
+constexpr int kConsumerWarps = 16;
+// Float pixels: two warps side by side per strip of rows, a thread's pixels are rows_per_warp rows
+// of one column.  Half pixels: a warp covers whole tile rows.
+template <int TH> struct Shape {
+    static constexpr int H = TH, ROWS = TH == kTileHShort ? kMaxRowsShort : kMaxRows, GROUPS = ROWS / kGroupRows;
+    static constexpr int rows_per_warp = 2 * TH / kConsumerWarps;
+    static_assert(TH == kTileH || TH == kTileHShort, "two tile shapes exist");
+    static_assert(rows_per_warp % 2 == 0, "rows are handled in pairs");
+};
 
 // Source element type S of a staged kernel whose pixels are T: S = T for float and half
 // images; S = uint8_t with T = float or half reads bytes and scales them by 1/255 (what ToTensor does
@@ -55,12 +65,15 @@ static_assert(kRowsPerWarp % 2 == 0 && kTileH % kRowsPerWarp == 0, "rows are han
 template <typename S> struct Src {
     static constexpr int pitch = sizeof(S) == 1 ? kPitchBytes1 : sizeof(S) == 2 ? kPitchBytes2 : kPitch;   // staged row pitch, elements
     static constexpr int chunk = 16 / (int)sizeof(S);                      // elements per 16 bytes
-    static constexpr int stages = sizeof(S) == 4 ? 2 : 3;                  // ring depth: what fits 227 KB of shared memory
+};
+// The ring of a kernel with source elements S and tile height TH.
+template <typename S, int TH> struct Ring {
+    static constexpr int stages = sizeof(S) == 4 && TH == kTileH ? 2 : 3;  // depth: what fits 227 KB of shared memory
     static constexpr int info_slots = 2 * stages;                          // tile descriptors: two per stage (see AffineSmem)
     static constexpr int threads = (kConsumerWarps + stages) * 32;         // one producer warp per stage
 };
 // Elements per channel per stage.
-template <typename S> struct Stage { static constexpr int plane = kMaxRows * Src<S>::pitch; };
+template <typename S, int TH> struct Stage { static constexpr int plane = Shape<TH>::ROWS * Src<S>::pitch; };
 constexpr float kInv255 = 1.0f / 255.0f;
 
 // Texel of type S -> pixel of type T.
@@ -117,7 +130,7 @@ struct alignas(64) TMaps {
     CUtensorMap rows[kNumGroups];
 };
 
-template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
+template <typename T, int C, unsigned F, int TH> struct alignas(16) TileInfo {
     int n, x0, y0;        // image, first output column / row of the tile
     int rows, row0;       // staged source rows (rows == 0: gather this tile from global memory)
     int window;           // bit 0: every row starts at column xs0: texel (y, x) sits at element
@@ -127,17 +140,17 @@ template <typename T, int C, unsigned F> struct alignas(16) TileInfo {
     int pad3[3];
     Geom g;
     Colour<T, C, F> col;
-    int rowoff[kMaxRows + 1];         // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
+    int rowoff[Shape<TH>::ROWS + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)
 };
 
-// Shared memory: Src<S>::stages pixel stages, then Src<S>::info_slots tile descriptors.  Tile number i of a CTA
+// Shared memory: Ring::stages pixel stages, then Ring::info_slots tile descriptors.  Tile number i of a CTA
 // uses stage i % stages and descriptor i % info_slots, so the producer can write the descriptor
 // of the stage's next tile while the consumers still read the current one, and only the copy
 // itself has to wait for the stage to be released.
-template <typename T, int C, unsigned F, typename S = T> struct AffineSmem {
-    static constexpr size_t stage = ((size_t)C * Stage<S>::plane * sizeof(S) + 1023) / 1024 * 1024;
-    static constexpr size_t info = (sizeof(TileInfo<T, C, F>) + 15) / 16 * 16;
-    static constexpr size_t total = Src<S>::stages * stage + Src<S>::info_slots * info;
+template <typename T, int C, unsigned F, typename S = T, int TH = kTileH> struct AffineSmem {
+    static constexpr size_t stage = ((size_t)C * Stage<S, TH>::plane * sizeof(S) + 1023) / 1024 * 1024;
+    static constexpr size_t info = (sizeof(TileInfo<T, C, F, TH>) + 15) / 16 * 16;
+    static constexpr size_t total = Ring<S, TH>::stages * stage + Ring<S, TH>::info_slots * info;
     static_assert(total <= 227 * 1024, "stages and descriptors must fit one CTA's shared memory");
 };
 

@@ -32,15 +32,16 @@ __device__ __forceinline__ void two_phase_tile(int v, int n_images, int tpi, int
 }
 
 
-template <typename T, int C, int MODE, unsigned F, typename S, bool TWO>
+template <typename T, int C, int MODE, unsigned F, typename S, bool TWO, int TH>
 __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &maps, unsigned char *smem,
                                                 uint64_t *full, uint64_t *empty, volatile int *abort_flag, int p)
 {
-    using Info = TileInfo<T, C, F>;
-    using Smem = AffineSmem<T, C, F, S>;
-    constexpr int CH = Src<S>::chunk, PITCH = Src<S>::pitch, PLANE = Stage<S>::plane;
-    constexpr int STAGES = Src<S>::stages;
-    static_assert(kNumGroups <= 32 && kMaxRows % kGroupRows == 0, "one lane per row group");
+    using Info = TileInfo<T, C, F, TH>;
+    using Smem = AffineSmem<T, C, F, S, TH>;
+    constexpr int CH = Src<S>::chunk, PITCH = Src<S>::pitch, PLANE = Stage<S, TH>::plane;
+    constexpr int STAGES = Ring<S, TH>::stages;
+    constexpr int TILE_H = Shape<TH>::H, MAX_ROWS = Shape<TH>::ROWS, GROUPS = Shape<TH>::GROUPS;
+    static_assert(GROUPS <= 32 && GROUPS <= kNumGroups && MAX_ROWS % kGroupRows == 0, "one lane per row group");
     const int lane = threadIdx.x & 31;
     const int tiles_per_img = k.tiles_x * k.tiles_y;
     S *stage = reinterpret_cast<S *>(smem + p * Smem::stage);
@@ -109,8 +110,8 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
         const float m[6] = {g.a, g.b, g.c, g.d, g.e, g.f};
         constexpr int FMODE = MODE == 2 ? 1 : 0;            // footprint rule: nearest or bilinear
         if (k.staged_ok) {
-            if (MODE == 0) tile_footprint_crop(fp, k.oh, k.ow, g.top, g.left, g.flip, tx, ty);
-            else tile_footprint(fp, FMODE, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty);
+            if (MODE == 0) tile_footprint_crop(fp, k.oh, k.ow, g.top, g.left, g.flip, tx, ty, TILE_H, MAX_ROWS);
+            else tile_footprint(fp, FMODE, k.h, k.w, k.oh, k.ow, g.top, g.left, g.flip, m, tx, ty, TILE_H, MAX_ROWS);
         }
         bool staged = fp.rows > 0, window = false;
         int gxs = 0;
@@ -126,7 +127,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                 column_range(FMODE, fp.xmin, fp.xmax, c0, c1);
                 inside = c0 >= 0 && c1 < k.w;
             } else {
-                // lanes 0 .. kNumGroups-1: columns of row group `lane`; the other lanes hold a neutral entry
+                // lanes 0 .. GROUPS-1: columns of row group `lane`; the other lanes hold a neutral entry
                 staged = tile_edges(fp, FMODE, CH, PITCH, m);
                 int xs = 0, xe = CH;
                 const int r_first = lane * kGroupRows, r_last = min(r_first + kGroupRows, fp.rows) - 1;
@@ -138,12 +139,12 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
                 if (staged) {
                     // rowoff[r] = r * PITCH - (first column of r's group); rows lane, lane + 32, ...
 #pragma unroll
-                    for (int base = 0; base < kMaxRows; base += 32) {      // same trip count in every lane
+                    for (int base = 0; base < MAX_ROWS; base += 32) {      // same trip count in every lane
                         const int r = base + lane;
-                        const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, kNumGroups - 1));
-                        if (r < kMaxRows) ti->rowoff[r] = r * PITCH - x_first;
+                        const int x_first = __shfl_sync(0xffffffffu, gxs, min(r / kGroupRows, GROUPS - 1));
+                        if (r < MAX_ROWS) ti->rowoff[r] = r * PITCH - x_first;
                     }
-                    if (lane == 0) ti->rowoff[kMaxRows] = 0;
+                    if (lane == 0) ti->rowoff[MAX_ROWS] = 0;
                 }
             }
             // fill != 0 cannot rely on the copy's zero fill: stage only tiles that stay inside the image
@@ -155,7 +156,7 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             ti->col = col;
             ti->n = n;
             ti->x0 = tx * kTileW;
-            ti->y0 = ty * kTileH;
+            ti->y0 = ty * TILE_H;
             ti->rows = staged ? fp.rows : 0;
             ti->row0 = fp.row0;
             ti->window = (window ? 1 : 0) | (phase << 1);

@@ -65,8 +65,8 @@ namespace ta {
 // base, row0, xs0, the two magic offsets) folded into kb once per tile, modulo 2^32.
 //
 // Table path: each row group has its own first column; rowoff[] translates.
-template <typename T, int C, int MODE, bool CHECK, typename S> struct PairSampler {
-    static constexpr int PITCH = Src<S>::pitch, PLANE = Stage<S>::plane;
+template <typename T, int C, int MODE, bool CHECK, typename S, int TH> struct PairSampler {
+    static constexpr int PITCH = Src<S>::pitch, PLANE = Stage<S, TH>::plane;
     static constexpr uint32_t ES = sizeof(S), ROWB = ES * PITCH, PLANEB = ES * PLANE;
     using P = Px<T, S>;
     using Pair = typename PairOf<T>::type;
@@ -230,9 +230,9 @@ __device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__hal
     }
 }
 
-// A consumer warp's share of a tile.  Float pixels: 32 columns x kRowsPerWarp rows, a lane owns one
+// A consumer warp's share of a tile.  Float pixels: 32 columns x Shape::rows_per_warp rows, a lane owns one
 // column and pairs the rows (full 128-byte lines per store instruction).  Half pixels: all 64
-// columns x kTileH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
+// columns x TH / kConsumerWarps rows, a lane owns two neighbouring columns and pairs THEM,
 // so that a store is one 32-bit half2, a warp's store a full 128-byte line again, and shared
 // memory is read at 4-byte lane stride (no bank conflicts) as in the float case.
 // The mean of one image from its partial sums.  The order of the additions is part of the result,
@@ -326,21 +326,21 @@ __device__ __forceinline__ void two_phase_finisher(const KArgs &k, volatile int 
 
 // TWO: tiles of both phases of the two-phase kernel arrive through the same ring; the tile's
 // descriptor says which it is.
-template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S, bool REDUCE, bool TWO>
+template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX, typename S, bool REDUCE, bool TWO, int TH>
 __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *smem, uint64_t *full, uint64_t *empty,
                                                 volatile int *abort_flag, unsigned *two_phase_checkin)
 {
-    using Info = TileInfo<T, C, F>;
-    using Sampler = PairSampler<T, C, MODE, CHECK, S>;
-    using Smem = AffineSmem<T, C, F, S>;
+    using Info = TileInfo<T, C, F, TH>;
+    using Sampler = PairSampler<T, C, MODE, CHECK, S, TH>;
+    using Smem = AffineSmem<T, C, F, S, TH>;
     using Pair = typename PairOf<T>::type;
-    constexpr int STAGES = Src<S>::stages, INFO_SLOTS = Src<S>::info_slots;
+    constexpr int STAGES = Ring<S, TH>::stages, INFO_SLOTS = Ring<S, TH>::info_slots;
     constexpr bool PAIR_X = sizeof(T) == 2;
     static_assert(!PAIR_X || (!MIX && !REDUCE && !TWO), "the per-pixel recipe and the mean pre-pass exist for float pixels only");
     static_assert(!TWO || (!REDUCE && !MIX && (F & kMean)), "the two-phase kernel is the mean-contrast pipeline");
-    constexpr int ROWS_PER_WARP = PAIR_X ? kTileH / kConsumerWarps : kRowsPerWarp;
-    static_assert(!PAIR_X || (kTileW == 64 && kTileH % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
-    static_assert(PAIR_X || kTileH == 2 * kRowsPerWarp * kConsumerWarps / 4, "two warps side by side per strip of rows");
+    constexpr int ROWS_PER_WARP = PAIR_X ? TH / kConsumerWarps : Shape<TH>::rows_per_warp;
+    static_assert(!PAIR_X || (kTileW == 64 && TH % kConsumerWarps == 0), "a warp covers whole tile rows in pairs of columns");
+    static_assert(PAIR_X || TH == ROWS_PER_WARP * kConsumerWarps / 2, "two warps side by side per strip of rows");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int wx = warp & 1, wy = warp >> 1;
     const unsigned oplane = (unsigned)(k.oh * k.ow);
@@ -544,20 +544,20 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
 // REDUCE: the grayscale-mean pre-pass on the same machinery (no colour tier, no image output).
 // TWO: reduction and fused pass of the mean-contrast pipeline in one (cooperative) launch.
 template <typename T, int C, int MODE, unsigned F, bool CHECK, bool MIX = false, typename S = T, bool REDUCE = false,
-          bool TWO = false>
-__global__ void __launch_bounds__(Src<S>::threads + (TWO ? 32 : 0), 1)
+          bool TWO = false, int TH = kTileH>
+__global__ void __launch_bounds__(Ring<S, TH>::threads + (TWO ? 32 : 0), 1)
 affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps maps)
 {
     // Used as declared (no pointer arithmetic through integers), so the compiler keeps every
     // access in the shared address space.  Tensor copies without swizzle need 16-byte alignment.
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(8) uint64_t full[Src<S>::stages];
-    __shared__ __align__(8) uint64_t empty[Src<S>::stages];
+    __shared__ __align__(8) uint64_t full[Ring<S, TH>::stages];
+    __shared__ __align__(8) uint64_t empty[Ring<S, TH>::stages];
     __shared__ int abort_flag;
     __shared__ unsigned two_phase_checkin[5];       // [0..3] consumer check-ins per image in flight, [4] consumer heartbeat
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < Src<S>::stages; ++i) {
+        for (int i = 0; i < Ring<S, TH>::stages; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], kConsumerWarps);
         }
@@ -567,12 +567,12 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
     }
     __syncthreads();
 
-    if (TWO && (threadIdx.x >> 5) >= kConsumerWarps + Src<S>::stages)
+    if (TWO && (threadIdx.x >> 5) >= kConsumerWarps + Ring<S, TH>::stages)
         two_phase_finisher(k, &abort_flag, &two_phase_checkin[4]);
     else if ((threadIdx.x >> 5) >= kConsumerWarps)
-        affine_producer<T, C, MODE, F, S, TWO>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
+        affine_producer<T, C, MODE, F, S, TWO, TH>(k, maps, smem, full, empty, &abort_flag, (int)(threadIdx.x >> 5) - kConsumerWarps);
     else
-        affine_consumer<T, C, MODE, F, CHECK, MIX, S, REDUCE, TWO>(k, smem, full, empty, &abort_flag, two_phase_checkin);
+        affine_consumer<T, C, MODE, F, CHECK, MIX, S, REDUCE, TWO, TH>(k, smem, full, empty, &abort_flag, two_phase_checkin);
 
     // Leave together.  After an abort, copies may still be in flight towards this CTA's shared
     // memory: give each stage one more bounded chance to settle before the memory is released.
@@ -585,7 +585,7 @@ affine_kernel(const __grid_constant__ KArgs k, const __grid_constant__ TMaps map
                 __threadfence_system();
             }
         }
-        if (threadIdx.x < Src<S>::stages) {
+        if (threadIdx.x < Ring<S, TH>::stages) {
             for (int i = 0; i < 4096; ++i)
                 if (mbar_try_wait(&full[threadIdx.x], 0) || mbar_try_wait(&full[threadIdx.x], 1)) break;
         }

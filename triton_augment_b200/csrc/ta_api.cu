@@ -38,12 +38,16 @@ static int cuda_fail(cudaError_t e, const char *what)
 
 // ----------------------------------------------------------------------------- per-device state
 constexpr int kMaxDevices = 16;
-constexpr int kNumKinds = 10, kNumDtypes = 4;     // crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed, mean pre-pass, two-phase x 3
+// crop/flip, nearest, bilinear, crop/flip 128-bit, crop/flip staged, bilinear mixed, mean pre-pass, two-phase x 3;
+// then nearest, bilinear, crop/flip staged, bilinear mixed on short tiles
+constexpr int kNumKinds = 14, kNumDtypes = 4;
 // TA_B200_SCALAR_DIRECT=1 keeps crop/flip launches on the 32-bit kernel (tests compare the two).
 static const bool g_force_scalar_direct = [] { const char *e = getenv("TA_B200_SCALAR_DIRECT"); return e && e[0] == '1'; }();
 // Which kernel runs a call without a matrix: 0 = choose by size, 1 = always the crop kernels,
 // 2 = the staged kernel whenever the tensors allow it (ta_b200_debug_crop_path).
 static std::atomic<int> g_crop_path{0};
+// Tile height of the staged kernel for float images: 0 = by output height (ta_b200_debug_tile_height).
+static std::atomic<int> g_tile_height{0};
 // Limit of the kernels' barrier waits, and (diagnostics) the tile whose producer withholds its
 // arrival in launches of the staged kernel: ta_b200_debug_wait().
 constexpr unsigned long long kDefaultWaitNs = 2000000000ull;
@@ -111,8 +115,11 @@ static int pending_timeout(const DeviceState &s)
 static size_t in_bytes(int dtype) { return dtype == TA_B200_F32 ? 4 : dtype == TA_B200_F16 ? 2 : 1; }
 static size_t out_bytes(int dtype) { return dtype == TA_B200_F16 || dtype == TA_B200_U8_F16 ? 2 : 4; }
 
-static const KernelTable &table_for(int kind, int dtype)
+static const KernelTable &table_for(int kind, int dtype, bool short_tiles)
 {
+    if (short_tiles)              // float images only (launch_fused)
+        return kind == 1 ? table_f32_short_nearest() : kind == 2 ? table_f32_short_bilinear()
+               : kind == 3 ? table_f32_short_crop_staged() : table_f32_short_bilinear_mix();
     if (dtype == TA_B200_U8)      // staged kernels only (launch_fused never asks for kind 0)
         return kind == 1 ? table_u8_nearest() : kind == 2 ? table_u8_bilinear() : kind == 3 ? table_u8_crop_staged()
                                                                                            : table_u8_bilinear_mix();
@@ -327,7 +334,16 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     }
     unsigned f = template_flags(p);
     if (kind == 2 && k.late_x_slot < 8 && !checked) kind = 4;     // only swapped fp32 variants get here (fill_kargs)
-    const KernelTable &tab = table_for(kind, p->dtype);
+    // Float images whose output height leaves the last row of 64-row tiles at most half full, and
+    // wastes a tenth of the tile rows or more, run on 64 x 32 tiles with a ring of three stages:
+    // with few tiles per image the depth of the ring matters more than the pixels per thread
+    // (ta_affine.cuh).  Same arithmetic per pixel, hence the same output.
+    const int last_rows = p->oh % kTileH, forced = g_tile_height.load(std::memory_order_relaxed);
+    const bool short_tiles = kind != 0 && p->dtype == TA_B200_F32 &&
+                             (forced ? forced == kTileHShort
+                                     : last_rows != 0 && last_rows <= kTileHShort && 10 * (kTileH - last_rows) >= p->oh);
+    const int tile_h = short_tiles ? kTileHShort : kTileH;
+    const KernelTable &tab = table_for(kind, p->dtype, short_tiles);
     unsigned slot = f;
     const KernelEntry *ke;
     if (checked && kind != 0) {
@@ -347,7 +363,8 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     if (vec) ke = p->c == 3 ? &tab.c3_vec[f] : &tab.c1_vec[f];
     if (!ke->fn) return fail(TA_B200_ERR_UNSUPPORTED, "no kernel for channels=%d flags=0x%x", p->c, f);
     int blocks = 0;
-    rc = prepare_kernel(*s, *ke, vec ? 3 : kind == 3 ? 4 : kind == 4 ? 5 : kind, p->dtype, p->c, slot, &blocks);
+    const int kind_index = short_tiles ? 9 + kind : vec ? 3 : kind == 3 ? 4 : kind == 4 ? 5 : kind;       // short: 10 .. 13
+    rc = prepare_kernel(*s, *ke, kind_index, p->dtype, p->c, slot, &blocks);
     if (rc != TA_B200_OK) return rc;
 
     long long work;
@@ -361,7 +378,7 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
         work = ((long long)p->n * k.tiles_x * k.tiles_y + kWarps - 1) / kWarps;      // CTAs needed at one strip per warp
     } else {
         k.tiles_x = (p->ow + kTileW - 1) / kTileW;
-        k.tiles_y = (p->oh + kTileH - 1) / kTileH;
+        k.tiles_y = (p->oh + tile_h - 1) / tile_h;
         work = (long long)p->n * k.tiles_x * k.tiles_y;
     }
     const long long tiles = (long long)p->n * k.tiles_x * k.tiles_y;

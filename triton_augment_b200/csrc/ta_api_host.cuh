@@ -496,6 +496,13 @@ int ta_b200_debug_crop_path(int32_t path)
     return TA_B200_OK;
 }
 
+int ta_b200_debug_tile_height(int32_t rows)
+{
+    if (rows != 0 && rows != ta::kTileHShort && rows != ta::kTileH) return ta::fail(TA_B200_ERR_UNSUPPORTED, "tile height %d", rows);
+    ta::g_tile_height.store(rows, std::memory_order_relaxed);
+    return TA_B200_OK;
+}
+
 void ta_b200_debug_tile_shape(int32_t out[8])
 {
     out[0] = ta::kTileW; out[1] = ta::kTileH; out[2] = ta::kMaxRows;

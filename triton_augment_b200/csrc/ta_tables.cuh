@@ -41,23 +41,24 @@ constexpr bool flags_valid(int channels, unsigned f)
 // 5 / 6 / 7 the two-phase kernel (mean reduction + fused pass in one launch) without a matrix /
 // nearest / bilinear: exists for the flag combinations with mean-mode contrast.
 // S: source element type (uint8_t with T = float or half: bytes scaled by 1/255; staged kernels only).
-template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename S = T> KernelEntry kernel_entry()
+// TH: tile height of the staged kernels (kTileH, or kTileHShort for small float outputs).
+template <typename T, int C, int KIND, unsigned F, bool CHECK = false, typename S = T, int TH = kTileH> KernelEntry kernel_entry()
 {
     if constexpr (!flags_valid(C, F)) return KernelEntry{nullptr, 0, 0};
     else if constexpr (KIND == 0) return KernelEntry{(const void *)&direct_kernel<T, C, F>, 0, kThreads};
     else if constexpr (KIND >= 5) {
         if constexpr ((F & kMean) != 0 && !CHECK)
             return KernelEntry{(const void *)&affine_kernel<T, C, KIND - 5, F, false, false, S, false, true>,
-                               AffineSmem<T, C, F, S>::total, Src<S>::threads + 32};      // + the finisher warp
+                               AffineSmem<T, C, F, S>::total, Ring<S, kTileH>::threads + 32};      // + the finisher warp
         else return KernelEntry{nullptr, 0, 0};
     }
     else if constexpr (KIND == 4) {
         if constexpr (CoordRecipe<2, F>::swapped && !CHECK)
-            return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true, S>, AffineSmem<T, C, F, S>::total,
-                               Src<S>::threads};
+            return KernelEntry{(const void *)&affine_kernel<T, C, 2, F, false, true, S, false, false, TH>,
+                               AffineSmem<T, C, F, S, TH>::total, Ring<S, TH>::threads};
         else return KernelEntry{nullptr, 0, 0};
-    } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK, false, S>,
-                              AffineSmem<T, C, F, S>::total, Src<S>::threads};
+    } else return KernelEntry{(const void *)&affine_kernel<T, C, KIND == 3 ? 0 : KIND, F, CHECK, false, S, false, false, TH>,
+                              AffineSmem<T, C, F, S, TH>::total, Ring<S, TH>::threads};
 }
 
 template <typename T, int C, unsigned F> KernelEntry vec_entry()
@@ -66,16 +67,16 @@ template <typename T, int C, unsigned F> KernelEntry vec_entry()
     else return KernelEntry{(const void *)&direct_vec_kernel<T, C, F>, 0, kThreads};
 }
 
-template <typename T, int KIND, typename S, unsigned... Fs>
+template <typename T, int KIND, typename S, int TH, unsigned... Fs>
 void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
 {
-    ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs, false, S>()), ...);
-    ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs, false, S>()), ...);
+    ((t.c3[Fs] = kernel_entry<T, 3, KIND, Fs, false, S, TH>()), ...);
+    ((t.c1[Fs] = kernel_entry<T, 1, KIND, Fs, false, S, TH>()), ...);
     if constexpr (KIND >= 5) {
         t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
     } else if constexpr (KIND != 0) {
-        t.c3_checked = kernel_entry<T, 3, KIND, 0u, true, S>();
-        t.c1_checked = kernel_entry<T, 1, KIND, 0u, true, S>();
+        t.c3_checked = kernel_entry<T, 3, KIND, 0u, true, S, TH>();
+        t.c1_checked = kernel_entry<T, 1, KIND, 0u, true, S, TH>();
     } else {
         t.c3_checked = t.c1_checked = KernelEntry{nullptr, 0, 0};
         ((t.c3_vec[Fs] = vec_entry<T, 3, Fs>()), ...);
@@ -83,11 +84,11 @@ void fill_table(KernelTable &t, std::integer_sequence<unsigned, Fs...>)
     }
 }
 
-template <typename T, int KIND, typename S = T> const KernelTable &make_table()
+template <typename T, int KIND, typename S = T, int TH = kTileH> const KernelTable &make_table()
 {
     static KernelTable t = [] {
         KernelTable x{};
-        fill_table<T, KIND, S>(x, std::make_integer_sequence<unsigned, kNumFlagCombos>{});
+        fill_table<T, KIND, S, TH>(x, std::make_integer_sequence<unsigned, kNumFlagCombos>{});
         return x;
     }();
     return t;
@@ -100,7 +101,7 @@ KernelEntry mean_kernel_entry(int mode, bool bright, int channels, bool bytes);
 template <int C, int MODE, unsigned F, typename S> KernelEntry mean_entry()
 {
     return KernelEntry{(const void *)&affine_kernel<float, C, MODE, F, false, false, S, true>,
-                       AffineSmem<float, C, F, S>::total, Src<S>::threads};
+                       AffineSmem<float, C, F, S>::total, Ring<S, kTileH>::threads};
 }
 
 // Defined one per translation unit (ta_inst_*.cu).
@@ -117,6 +118,10 @@ const KernelTable &table_u8h_nearest();
 const KernelTable &table_u8h_bilinear();
 const KernelTable &table_f32_nearest();
 const KernelTable &table_f32_bilinear();
+const KernelTable &table_f32_short_nearest();        // float images on 64 x 32 tiles (small outputs)
+const KernelTable &table_f32_short_bilinear();
+const KernelTable &table_f32_short_crop_staged();
+const KernelTable &table_f32_short_bilinear_mix();
 const KernelTable &table_f16_direct();
 const KernelTable &table_f16_nearest();
 const KernelTable &table_f16_bilinear();
