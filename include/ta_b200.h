@@ -361,10 +361,11 @@ int ta_b200_mean_path(int32_t one_launch);
  * the crop kernels), 1 = always the crop kernels, 2 = the staged kernel whenever the tensors
  * allow it.  Both produce identical output; the switch exists so that tests can compare them. */
 int ta_b200_debug_crop_path(int32_t path);
-/* Tile height of the staged kernel for float images, process-wide: 0 = chosen by the output
- * height (default: 64 rows; 32 rows with a deeper ring when the last row of 64-row tiles would be
- * at most half full and a tenth of the tile rows or more would be empty), 32 / 64 = that height
- * for every call.  Identical output; the switch exists so that tests can compare the shapes. */
+/* Tile height of the staged kernel for float32 and float16 images, process-wide: 0 = chosen by
+ * the output height (default: 64 rows; 32 rows with a deeper ring for outputs of at most 256 rows
+ * (float32) or 96 rows (float16) whose last row of 64-row tiles would be at most half full),
+ * 32 / 64 = that height for every call.  Identical output; the switch exists so that tests can
+ * compare the shapes. */
 int ta_b200_debug_tile_height(int32_t rows);
 /* ta_b200_fused_augment_host(): 1 = upload only the box of each large image that the call reads
  * when the copy plan is cheaper than whole slices (default), 0 = upload every image whole, 2 =

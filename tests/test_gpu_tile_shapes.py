@@ -1,6 +1,6 @@
-"""The staged kernel runs float images on 64 x 64 tiles (ring of two stages) or, for small outputs,
-on 64 x 32 tiles (ring of three).  The arithmetic per pixel is the same, so the two shapes must give
-the same bits; the choice by output height must be the documented one."""
+"""The staged kernel runs float32 and float16 images on 64 x 64 tiles or, for small outputs, on
+64 x 32 tiles with a deeper ring.  The arithmetic per pixel is the same, so the two shapes must
+give the same bits; the choice by output height must be the documented one."""
 import pytest
 import torch
 
@@ -20,11 +20,11 @@ def tile_height():
     _lib.tile_height(0)
 
 
-def _case(n, c, h, w, oh, ow, seed):
+def _case(n, c, h, w, oh, ow, seed, dtype=torch.float32):
     import triton_augment_b200 as ta
     dev = _dev()
     g = torch.Generator(device="cpu").manual_seed(seed)
-    img = torch.rand(n, c, h, w, generator=g).to(dev)
+    img = torch.rand(n, c, h, w, generator=g).to(dev).to(dtype)
     u = lambda lo, hi: torch.empty(n).uniform_(lo, hi, generator=g).to(dev)
     top = torch.randint(0, h - oh + 1, (n,), generator=g).float().to(dev)
     left = torch.randint(0, w - ow + 1, (n,), generator=g).float().to(dev)
@@ -32,7 +32,7 @@ def _case(n, c, h, w, oh, ow, seed):
     tr = torch.stack([u(-0.1 * w, 0.1 * w), u(-0.1 * h, 0.1 * h)], 1)
     sh = torch.stack([u(-5, 5), torch.zeros(n, device=dev)], 1)
     matrix = ta.functional._prepare_affine_matrix_only(n, dev, h, w, u(-15, 15), tr, u(0.9, 1.1), sh, None).contiguous()
-    colour = (u(0.8, 1.2), u(0.8, 1.2), u(0.8, 1.2), (torch.rand(n, generator=g) < 0.3).to(dev))
+    colour = (u(0.8, 1.2).to(dtype), u(0.8, 1.2).to(dtype), u(0.8, 1.2).to(dtype), (torch.rand(n, generator=g) < 0.3).to(dev))
     return img, top, left, flip, matrix, colour
 
 
@@ -40,7 +40,7 @@ def _launch(case, oh, ow, bilinear, flags, matrix=True, checked=False):
     from triton_augment_b200 import _lib
     img, top, left, flip, m, (b, cf, s, gray) = case
     n, c = img.shape[:2]
-    out = torch.full((n, c, oh, ow), -7.0, dtype=torch.float32, device=img.device)
+    out = torch.full((n, c, oh, ow), -7.0, dtype=img.dtype, device=img.device)
     norm = bool(flags & 16)
     p = _lib.make_params(img, out, top, left, flip, m if matrix else None, 0.0, bilinear, flags, b, cf, s, gray,
                          MEAN if norm else None, STD if norm else None)
@@ -49,13 +49,16 @@ def _launch(case, oh, ow, bilinear, flags, matrix=True, checked=False):
     return out
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("bilinear", [False, True])
 @pytest.mark.parametrize("shape", [(6, 3, 256, 256, 224, 224), (9, 3, 96, 96, 96, 96), (3, 3, 640, 704, 600, 641),
                                    (5, 1, 128, 160, 75, 133), (4, 3, 80, 64, 17, 40)])
-def test_both_tile_shapes_give_the_same_bits(tile_height, shape, bilinear):
+def test_both_tile_shapes_give_the_same_bits(tile_height, shape, bilinear, dtype):
     from triton_augment_b200 import _lib
     n, c, h, w, oh, ow = shape
-    case = _case(n, c, h, w, oh, ow, seed=oh + ow)
+    if dtype == torch.float16:
+        w = (w + 7) // 8 * 8                       # rows of whole 16-byte units, as staging needs
+    case = _case(n, c, h, w, oh, ow, seed=oh + ow, dtype=dtype)
     outs = []
     for rows in (32, 64):
         tile_height(rows)
@@ -86,11 +89,14 @@ def test_short_tiles_pass_the_staging_checks(tile_height):
 
 
 def test_shape_is_chosen_by_output_height(tile_height):
-    """64-row tiles unless their last row would be at most half full and a tenth of the rows empty."""
+    """64-row tiles unless the output is small (float32: at most 256 rows, float16: 96) and their
+    last row would be at most half full."""
     from triton_augment_b200 import _lib
     tile_height(0)
-    for oh, rows in [(224, 32), (96, 32), (32, 32), (288, 32), (352, 64), (112, 64), (128, 64), (608, 64), (48, 64)]:
-        case = _case(2, 3, oh + 8, 136, oh, 128, seed=oh)
+    for dtype, oh, rows in [(torch.float32, 224, 32), (torch.float32, 96, 32), (torch.float32, 32, 32), (torch.float32, 288, 64),
+                            (torch.float32, 112, 64), (torch.float32, 128, 64), (torch.float32, 608, 64), (torch.float32, 48, 64),
+                            (torch.float16, 96, 32), (torch.float16, 17, 32), (torch.float16, 224, 64), (torch.float16, 128, 64)]:
+        case = _case(2, 3, oh + 8, 136, oh, 128, seed=oh, dtype=dtype)
         _lib.debug_counters(reset=True)
         _launch(case, oh, 128, False, 31)
         staged, direct, _, _ = _lib.debug_counters()

@@ -324,7 +324,7 @@ def crop_path(path: int) -> None:
 
 
 def tile_height(rows: int) -> None:
-    """Tile height of the staged kernel for float images: 0 = by output height, 32 or 64 = forced (tests)."""
+    """Tile height of the staged kernel for float32 / float16 images: 0 = by output height, 32 or 64 = forced (tests)."""
     check(load().ta_b200_debug_tile_height(int(rows)), "ta_b200_debug_tile_height")
 
 

@@ -23,6 +23,7 @@ LIB = os.path.join(HERE, "lib", "libta_b200.so")
 UNITS = (["ta_api.cu", "ta_inst_f32_crop_staged.cu", "ta_inst_f32_bilinear_mix.cu", "ta_inst_f32_mean.cu",
           "ta_inst_f32_two_phase.cu"]
          + [f"ta_inst_f32_short_{k}.cu" for k in ("crop_staged", "nearest", "bilinear", "bilinear_mix")]
+         + [f"ta_inst_f16_short_{k}.cu" for k in ("nearest", "bilinear")]
          + [f"ta_inst_u8_{k}.cu" for k in ("crop_staged", "nearest", "bilinear", "bilinear_mix")]
          + [f"ta_inst_u8h_{k}.cu" for k in ("crop_staged", "nearest", "bilinear")]
          + [f"ta_inst_{t}_{k}.cu" for t in ("f32", "f16") for k in ("direct", "nearest", "bilinear")])

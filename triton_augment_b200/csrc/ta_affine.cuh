@@ -45,10 +45,11 @@ namespace ta {
 //   64x40 tiles, 20 warps x 4 pixels, 3 stages: 3 % faster than 64x32, light variants 20 % slower
 //   64x36 / 64x28 / 64x24 tiles with 18 / 14 / 24 warps x 4 pixels: equal or slower than 64x32
 //   64x32 tiles, 8 warps x 8 pixels: bilinear +2 %, half pixels +12 % (too few warps to hide latency)
-// Small outputs of float images take the 64x32 shape with three stages instead (TH = kTileHShort):
-// with few tiles per image many are edge tiles with little work, and then the depth of the ring -
-// how many tiles' copies are in flight - decides: 4096 x 3 x 96^2 nearest 185 us against 228 us,
-// 1024 x 3 x 256^2 -> 224^2 224 against 234 us; from 320 rows on the tall shape wins.
+// Small outputs take the 64x32 shape with a deeper ring instead (TH = kTileHShort; three stages
+// for float sources, four for half): with few tiles per image many are edge tiles with little
+// work, and then the depth of the ring - how many tiles' copies are in flight - decides:
+// 4096 x 3 x 96^2 float nearest 179 us against 228 us, 1024 x 3 x 256^2 -> 224^2 224 against 236 us;
+// above 256 output rows (half pixels: above 96) the tall shape wins.
 constexpr int kConsumerWarps = 16;
 // Float pixels: two warps side by side per strip of rows, a thread's pixels are rows_per_warp rows
 // of one column.  Half pixels: a warp covers whole tile rows.
@@ -68,7 +69,8 @@ template <typename S> struct Src {
 };
 // The ring of a kernel with source elements S and tile height TH.
 template <typename S, int TH> struct Ring {
-    static constexpr int stages = sizeof(S) == 4 && TH == kTileH ? 2 : 3;  // depth: what fits 227 KB of shared memory
+    // depth: what fits 227 KB of shared memory (float sources), four for the short tiles of half images
+    static constexpr int stages = sizeof(S) == 4 ? (TH == kTileH ? 2 : 3) : (TH == kTileH ? 3 : 4);
     static constexpr int info_slots = 2 * stages;                          // tile descriptors: two per stage (see AffineSmem)
     static constexpr int threads = (kConsumerWarps + stages) * 32;         // one producer warp per stage
 };

@@ -117,8 +117,9 @@ static size_t out_bytes(int dtype) { return dtype == TA_B200_F16 || dtype == TA_
 
 static const KernelTable &table_for(int kind, int dtype, bool short_tiles)
 {
-    if (short_tiles)              // float images only (launch_fused)
-        return kind == 1 ? table_f32_short_nearest() : kind == 2 ? table_f32_short_bilinear()
+    if (short_tiles)              // float and half images only (launch_fused)
+        return dtype == TA_B200_F16 ? (kind == 1 ? table_f16_short_nearest() : table_f16_short_bilinear())
+               : kind == 1 ? table_f32_short_nearest() : kind == 2 ? table_f32_short_bilinear()
                : kind == 3 ? table_f32_short_crop_staged() : table_f32_short_bilinear_mix();
     if (dtype == TA_B200_U8)      // staged kernels only (launch_fused never asks for kind 0)
         return kind == 1 ? table_u8_nearest() : kind == 2 ? table_u8_bilinear() : kind == 3 ? table_u8_crop_staged()
@@ -334,14 +335,17 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     }
     unsigned f = template_flags(p);
     if (kind == 2 && k.late_x_slot < 8 && !checked) kind = 4;     // only swapped fp32 variants get here (fill_kargs)
-    // Float images whose output height leaves the last row of 64-row tiles at most half full, and
-    // wastes a tenth of the tile rows or more, run on 64 x 32 tiles with a ring of three stages:
-    // with few tiles per image the depth of the ring matters more than the pixels per thread
-    // (ta_affine.cuh).  Same arithmetic per pixel, hence the same output.
+    // Small outputs whose height leaves the last row of 64-row tiles at most half full run on 64 x 32
+    // tiles with a deeper ring: with few tiles per image the number of tiles in flight matters more
+    // than the pixels per thread (ta_affine.cuh).  Measured limits: float images up to 256 output
+    // rows (224: 224 against 236 us per 1024 images; 288: 369 against 357), half images up to 96
+    // (96: 164 / 222 against 169 / 250 us per 4096 images; 224: 189 against 167).  Same arithmetic
+    // per pixel, hence the same output.
     const int last_rows = p->oh % kTileH, forced = g_tile_height.load(std::memory_order_relaxed);
-    const bool short_tiles = kind != 0 && p->dtype == TA_B200_F32 &&
+    const bool has_short = p->dtype == TA_B200_F32 || p->dtype == TA_B200_F16;
+    const bool short_tiles = kind != 0 && has_short &&
                              (forced ? forced == kTileHShort
-                                     : last_rows != 0 && last_rows <= kTileHShort && 10 * (kTileH - last_rows) >= p->oh);
+                                     : last_rows != 0 && last_rows <= kTileHShort && p->oh <= (p->dtype == TA_B200_F32 ? 256 : 96));
     const int tile_h = short_tiles ? kTileHShort : kTileH;
     const KernelTable &tab = table_for(kind, p->dtype, short_tiles);
     unsigned slot = f;

@@ -122,6 +122,8 @@ const KernelTable &table_f32_short_nearest();        // float images on 64 x 32 
 const KernelTable &table_f32_short_bilinear();
 const KernelTable &table_f32_short_crop_staged();
 const KernelTable &table_f32_short_bilinear_mix();
+const KernelTable &table_f16_short_nearest();          // half images on 64 x 32 tiles
+const KernelTable &table_f16_short_bilinear();
 const KernelTable &table_f16_direct();
 const KernelTable &table_f16_nearest();
 const KernelTable &table_f16_bilinear();
