@@ -30,8 +30,8 @@ constexpr int kTileW = 64;       // output tile width, pixels
 // Output tile height, and the number of source rows one staged tile may span (12 groups of 8):
 // a 64 x 64 tile under +-15 degrees of rotation, 5 degrees of shear and scale 0.9 reads ~90 rows.
 constexpr int kTileH = 64, kMaxRows = 96;
-// The short tile shape of float images with small outputs (64 x 32 pixels, 64 source rows): half
-// the stage, so that a ring of three fits where the tall shape has room for two.
+// The short tile shape of small outputs (64 x 32 pixels, 64 source rows): two thirds of the stage,
+// so that the ring holds one stage more than with the tall shape.
 constexpr int kTileHShort = 32, kMaxRowsShort = 64;
 TA_HD int max_rows_of(int tile_h) { return tile_h == kTileHShort ? kMaxRowsShort : kMaxRows; }
 constexpr int kGroupRows = 8;    // rows fetched by one tensor copy
