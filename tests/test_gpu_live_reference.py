@@ -63,7 +63,8 @@ def _err(a, b):
 
 # ----------------------------------------------------------------------------- every compiled variant
 SIZES = {"div16": (3, 272, 304, 208, 240),       # both output sizes multiples of 16: vectorised stores in the reference
-         "odd": (3, 300, 340, 211, 203)}          # neither: scalar stores, per-pixel contraction rule
+         "odd": (3, 300, 340, 211, 203),          # neither: scalar stores, per-pixel contraction rule
+         "rows320": (2, 400, 432, 320, 336)}      # whole 64-row tiles (the two sizes above take the 64 x 32 tile shape for float32)
 
 
 @pytest.mark.parametrize("size", sorted(SIZES))
