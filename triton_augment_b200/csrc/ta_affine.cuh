@@ -140,6 +140,12 @@ template <typename T, int C, unsigned F, int TH> struct alignas(16) TileInfo {
     int real_tile;        //   reduction phase (two-phase kernel).  real_tile = n * tiles per image + tile in image
     int r_count;          // two-phase kernel: > 0 on this CTA's last reduction tile of an image = how many it had
     int pad3[3];
+    // Per tile row (clamped to the image's last row), computed once by the producer because every
+    // lane of every consumer warp would otherwise repeat it: row_y = the row's source coordinate
+    // term - (int)(y + top) without a matrix, else yc = ((y + top) - h/2) + 0.5, each step rounded as
+    // in img_y() and centred() - and the two products of yc that the coordinate recipes fuse nothing
+    // into (b * yc, e * yc).  Pairs of rows are read as one 8-byte load.
+    float row_y[TH], row_b[TH], row_e[TH];
     Geom g;
     Colour<T, C, F> col;
     int rowoff[Shape<TH>::ROWS + 1];   // otherwise: rowoff[r] + x = element index of texel (row0 + r, x)

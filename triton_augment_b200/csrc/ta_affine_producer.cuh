@@ -151,6 +151,20 @@ __device__ __forceinline__ void affine_producer(const KArgs &k, const TMaps &map
             inside = inside && fp.row0 >= 0 && fp.row0 + fp.rows <= k.h;
             staged = staged && (MODE == 0 || (k.fill[0] == 0.0f && k.fill[1] == 0.0f && k.fill[2] == 0.0f) || inside);
         }
+        // per-row terms of the source coordinates (see TileInfo)
+#pragma unroll
+        for (int r = lane; r < TILE_H; r += 32) {
+            const int y = min(ty * TILE_H + r, k.oh - 1);
+            float yv = __fadd_rn(__fadd_rn(__int_as_float(0x4B000000 | y), -8388608.0f), g.top);
+            if (MODE == 0) {
+                ti->row_y[r] = truncf(yv);
+            } else {
+                yv = __fadd_rn(__fadd_rn(yv, -g.half_h), 0.5f);
+                ti->row_y[r] = yv;
+                ti->row_b[r] = __fmul_rn(g.b, yv);
+                ti->row_e[r] = __fmul_rn(g.e, yv);
+            }
+        }
         if (lane == 0) {
             ti->g = g;
             ti->col = col;

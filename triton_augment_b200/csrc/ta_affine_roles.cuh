@@ -48,6 +48,16 @@ __device__ __forceinline__ float2 src_coord2(float2 xc, float2 a, float2 b, floa
     u = pk_add(half, u);
     return pk_add(u, neg_half);
 }
+// The same with the row's terms taken from the tile descriptor: yc and byc = b * yc (TileInfo).
+template <int R>
+__device__ __forceinline__ float2 src_coord2_rows(float2 xc, float2 a, float2 b, float2 yc, float2 byc, float2 c, float2 half,
+                                                  float2 neg_half)
+{
+    float2 u = R == 1 ? pk_fma(xc, a, byc) : pk_fma(yc, b, pk_mul(a, xc));
+    u = pk_add(u, c);
+    u = pk_add(half, u);
+    return pk_add(u, neg_half);
+}
 
 }  // namespace ta
 
@@ -400,37 +410,25 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
                 const float2 xc = MODE == 0 ? f2(truncf(xi0), truncf(xi1)) : f2(centred(xi0, g.half_w), centred(xi1, g.half_w));
                 const bool whole = k.pair_store != 0 && h0.y + kTileW <= k.ow;       // the same for every lane
-                static_assert(ROWS_PER_WARP % 2 == 0, "the row coordinates are computed two rows at a time");
                 // The strip's rows, compiled twice: a tile whose rows and pairs all lie inside the
                 // image and whose rows share one window (almost all tiles) needs no row clamps, no
                 // store predicates and no per-row choice of the sampling path.
                 auto rows_of_pairs = [&](auto fast_tile) {
                     constexpr bool FAST = decltype(fast_tile)::value;
-                    float2 ys_keep = f2(0.0f, 0.0f);
 #pragma unroll
                     for (int r = 0; r < ROWS_PER_WARP; ++r) {
-                        // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred(); two rows at once
-                        float2 ys;
-                        if ((r & 1) == 0) {
-                            const int ya = FAST ? y_first + r : min(y_first + r, k.oh - 1);
-                            const int yb = FAST ? y_first + r + 1 : min(y_first + r + 1, k.oh - 1);
-                            ys = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
-                            ys = pk_add(ys, g2.top);
-                            if (MODE != 0) ys = pk_add(pk_add(ys, g2.neg_half_h), k2.half);
-                            ys_keep = ys;
-                        } else {
-                            ys = ys_keep;
-                        }
                         // no early exit: a row past the image's last row is computed on the last row's geometry
+                        // (the descriptor's row terms are clamped)
                         const bool row_ok = FAST || y_first + r < k.oh;
+                        const int tr = warp * ROWS_PER_WARP + r;           // row within the tile
                         float2 sx, sy;
                         if (MODE == 0) {
                             sx = xc;
-                            sy = bcast(truncf((r & 1) ? ys.y : ys.x));
+                            sy = bcast(ti->row_y[tr]);
                         } else {
-                            const float2 yc = bcast((r & 1) ? ys.y : ys.x);
-                            sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                            sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                            const float2 yc = bcast(ti->row_y[tr]);
+                            sx = src_coord2_rows<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, bcast(ti->row_b[tr]), g2.c, g2.half_w, k2.neg_half);
+                            sy = src_coord2_rows<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, bcast(ti->row_e[tr]), g2.f, g2.half_h, k2.neg_half);
                         }
                         Pair smp[C];
                         if (FAST || window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
@@ -455,27 +453,28 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                         // independent and their instructions can interleave.
                         const int y_raw = y_first + 2 * pr;
                         const bool a_ok = INSIDE || y_raw < k.oh, b_ok = INSIDE || y_raw + 1 < k.oh;
-                        const int ya = INSIDE ? y_raw : min(y_raw, k.oh - 1), yb = INSIDE ? y_raw + 1 : min(y_raw + 1, k.oh - 1);
-                        // (float)y as 2^23 + y minus 2^23, then + top, - half_h, + 0.5: img_y() and centred()
-                        float2 yc = pk_add(f2(__int_as_float(0x4B000000 | ya), __int_as_float(0x4B000000 | yb)), k2.neg_two23);
-                        yc = pk_add(yc, g2.top);
+                        // the rows' coordinate terms from the descriptor (clamped to the image's last row there)
+                        const int tr = wy * ROWS_PER_WARP + 2 * pr;          // first row of the pair within the tile
+                        const float2 yc = *reinterpret_cast<const float2 *>(&ti->row_y[tr]);
                         float2 sx, sy;
                         if (MODE == 0) {
                             sx = xc;
-                            sy = f2(truncf(yc.x), truncf(yc.y));
+                            sy = yc;
                         } else {
-                            yc = pk_add(pk_add(yc, g2.neg_half_h), k2.half);
+                            const float2 byc = *reinterpret_cast<const float2 *>(&ti->row_b[tr]);
+                            const float2 eyc = *reinterpret_cast<const float2 *>(&ti->row_e[tr]);
                             // (the reduction uses the contraction of its own stand-alone kernel, whose
                             // flags are brightness or nothing: the two paths must add up the same samples)
                             if (TWO && CoordRecipe<MODE, F>::swapped && reduce) {
-                                sx = src_coord2<CoordRecipe<MODE, F & kB>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                                sy = src_coord2<CoordRecipe<MODE, F & kB>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                                sx = src_coord2_rows<CoordRecipe<MODE, F & kB>::x>(xc, g2.a, g2.b, yc, byc, g2.c, g2.half_w, k2.neg_half);
+                                sy = src_coord2_rows<CoordRecipe<MODE, F & kB>::y>(xc, g2.d, g2.e, yc, eyc, g2.f, g2.half_h, k2.neg_half);
                             } else {
-                                sx = src_coord2<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
-                                sy = src_coord2<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, g2.f, g2.half_h, k2.neg_half);
+                                sx = src_coord2_rows<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, byc, g2.c, g2.half_w, k2.neg_half);
+                                sy = src_coord2_rows<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, eyc, g2.f, g2.half_h, k2.neg_half);
                             }
                             if constexpr (MIX) {                  // see late_x()
-                                const float2 alt = src_coord2<1>(xc, g2.a, g2.b, yc, g2.c, g2.half_w, k2.neg_half);
+                                const float2 alt = src_coord2_rows<1>(xc, g2.a, g2.b, yc, byc, g2.c, g2.half_w, k2.neg_half);
+                                const int ya = INSIDE ? y_raw : min(y_raw, k.oh - 1), yb = INSIDE ? y_raw + 1 : min(y_raw + 1, k.oh - 1);
                                 const uint32_t base = k.lin_base + (uint32_t)n * oplane + (uint32_t)x;
                                 if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
                                 if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
