@@ -192,14 +192,14 @@ template <typename T, int C, int MODE, bool CHECK, typename S, int TH> struct Pa
 // the byte pitch of an output row, so every store address is one multiply-add on a per-tile
 // pointer.  Packed colour arithmetic measured 3 % faster than per-pixel scalar code, although
 // most of its operands are broadcast pairs.
-template <int C, unsigned F>
+template <int C, unsigned F, int G = 0>
 __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<float, C, F> &col, float2 (&v2)[C],
                                             float *const (&plane)[C], int row, unsigned row_bytes, bool a_ok, bool b_ok)
 {
     auto at = [&](int c, int r) {
         return reinterpret_cast<float *>(reinterpret_cast<char *>(plane[c]) + (size_t)row_bytes * (unsigned)r);
     };
-    col.apply2(k, v2);
+    col.template apply2<G>(k, v2);
 #pragma unroll
     for (int c = 0; c < C; ++c) {
         if (a_ok) Elem<float>::store(at(c, row), v2[c].x);
@@ -212,13 +212,13 @@ __device__ __forceinline__ void finish_pair(const KArgs &k, const Colour<float, 
 // is whole and output rows keep pairs 4-byte aligned (vec), else element stores.
 // whole: every pair of the tile row is inside the image and aligned (uniform over the warp), so
 // the stores need no per-lane tests.
-template <int C, unsigned F>
+template <int C, unsigned F, int G = 0>
 __device__ __forceinline__ void finish_pair_x(const KArgs &k, const Colour<__half, C, F> &col, const __half2 (&smp)[C],
                                               __half *const (&plane)[C], int row, unsigned row_bytes, bool whole,
                                               bool row_ok, bool pair_ok)
 {
     float2 v2[C];
-    col.apply2(k, smp, v2);
+    col.template apply2<G>(k, smp, v2);
     unsigned h[C];
 #pragma unroll
     for (int c = 0; c < C; ++c) {
@@ -413,8 +413,9 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 // The strip's rows, compiled twice: a tile whose rows and pairs all lie inside the
                 // image and whose rows share one window (almost all tiles) needs no row clamps, no
                 // store predicates and no per-row choice of the sampling path.
-                auto rows_of_pairs = [&](auto fast_tile) {
+                auto rows_of_pairs = [&](auto fast_tile, auto gray_known) {
                     constexpr bool FAST = decltype(fast_tile)::value;
+                    constexpr int G = decltype(gray_known)::value;
 #pragma unroll
                     for (int r = 0; r < ROWS_PER_WARP; ++r) {
                         // no early exit: a row past the image's last row is computed on the last row's geometry
@@ -433,11 +434,16 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                         Pair smp[C];
                         if (FAST || window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                         else                Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                        if constexpr (!REDUCE) finish_pair_x<C, F>(k, col, smp, plane, r, row_bytes, FAST || whole, row_ok, FAST || pair_ok);
+                        if constexpr (!REDUCE) finish_pair_x<C, F, G>(k, col, smp, plane, r, row_bytes, FAST || whole, row_ok, FAST || pair_ok);
                     }
                 };
-                if (window && whole && y_first + ROWS_PER_WARP <= k.oh) rows_of_pairs(std::true_type{});
-                else rows_of_pairs(std::false_type{});
+                // (the whole-tile copy twice more where grayscale is compiled in: the image's flag is then
+                // tested once per tile, not once per pixel pair - 512 x 3 x 512^2 -> 448^2 nearest 260 -> 248 us)
+                using g_any = std::integral_constant<int, 0>;
+                if (!(window && whole && y_first + ROWS_PER_WARP <= k.oh)) rows_of_pairs(std::false_type{}, g_any{});
+                else if (!(C == 3 && (F & kG))) rows_of_pairs(std::true_type{}, g_any{});
+                else if (col.gray) rows_of_pairs(std::true_type{}, std::integral_constant<int, 2>{});
+                else rows_of_pairs(std::true_type{}, std::integral_constant<int, 1>{});
             } else {
                 // MODE 0 (no matrix): the source column is (int)x_img, as in the crop kernels
                 const float2 xc = bcast(MODE == 0 ? truncf(img_x(g, k.ow, x)) : centred(img_x(g, k.ow, x), g.half_w));
@@ -499,6 +505,8 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 };
                 using yes = std::true_type;
                 using no = std::false_type;
+                // (testing the grayscale flag once per tile, as the half-pixel path does, measured no
+                // gain here: bilinear 298 -> 297 us, fastest block 275 -> 278 us)
                 if (!window) row_pairs(no{}, no{});
                 else if (y_first + ROWS_PER_WARP <= k.oh) row_pairs(yes{}, yes{});
                 else row_pairs(no{}, yes{});

@@ -299,7 +299,9 @@ template <int C, unsigned F> struct Colour<float, C, F> {
     // Two pixels at once (.x and .y of each channel): everything that does not clamp goes
     // through the packed fp32 pipe, the clamping steps stay scalar because only scalar
     // multiplies / FMAs carry the saturate modifier.  Same arithmetic per pixel as apply().
-    __device__ __forceinline__ void apply2(const KArgs &k, float2 (&v)[C]) const
+    // G: what is known about the image's grayscale flag at compile time (0 nothing: test it here,
+    // 1 not set, 2 set), for callers that branch on it once per tile instead of once per pixel pair.
+    template <int G = 0> __device__ __forceinline__ void apply2(const KArgs &k, float2 (&v)[C]) const
     {
         if (F & kB) {
 #pragma unroll
@@ -326,7 +328,7 @@ template <int C, unsigned F> struct Colour<float, C, F> {
                 v[i] = make_float2(__saturatef(__fmaf_rn(v[i].x, sf, g.x)), __saturatef(__fmaf_rn(v[i].y, sf, g.y)));
         }
         if (C == 3 && (F & kG)) {
-            if (gray) {
+            if (G == 2 || (G == 0 && gray)) {
                 float2 g = pk_mul(make_float2(0.2989f, 0.2989f), v[0]);
                 g = pk_fma(make_float2(0.587f, 0.587f), v[1], g);
                 g = pk_fma(make_float2(0.114f, 0.114f), v[C - 1], g);
@@ -466,7 +468,7 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
             : "r"(*reinterpret_cast<const unsigned *>(&a)), "r"(*reinterpret_cast<const unsigned *>(&b)));
         return r;
     }
-    __device__ __forceinline__ void apply2(const KArgs &k, const __half2 (&in)[C], float2 (&v)[C]) const
+    template <int G = 0> __device__ __forceinline__ void apply2(const KArgs &k, const __half2 (&in)[C], float2 (&v)[C]) const
     {
         __half2 hv[C];
 #pragma unroll
@@ -510,7 +512,7 @@ template <int C, unsigned F> struct Colour<__half, C, F> {
             }
         }
         if (C == 3 && (F & kG)) {
-            if (gray) {
+            if (G == 2 || (G == 0 && gray)) {
                 if (wide_after_s) {
                     const float2 g = gray_f2(v);
 #pragma unroll
