@@ -50,7 +50,7 @@ MIN_TIMED_MS = 150.0          # every measurement times at least this much GPU w
 MIN_BLOCKS = 10               # ... in at least this many blocks of `steps` steps
 # dram__bytes_read.sum + dram__bytes_write.sum of one full 64-image affine-kernel launch (single-pass
 # ncu capture with `--profile-case 64`, summarised in profiles/affine_kernel_c3_fp32.md), divided by 64.
-NCU_TRAFFIC_PER_IMAGE = {"bilinear": (830531072 + 759378944) / 64, "nearest": (829506816 + 756525568) / 64}
+NCU_TRAFFIC_PER_IMAGE = {"bilinear": (830525696 + 759459840) / 64, "nearest": (829769984 + 756168704) / 64}
 
 
 def workload_name(interp):
