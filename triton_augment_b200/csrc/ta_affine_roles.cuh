@@ -382,6 +382,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
         const int x = PAIR_X ? h0.y + 2 * lane : h0.y + wx * 32 + lane;
         const int y_first = h0.z + (PAIR_X ? warp : wy) * ROWS_PER_WARP;
         float mean_acc = 0.0f;               // REDUCE: this lane's share of the tile's sum
+        bool released = false;               // the stage has been handed back before the end of the tile
 
         if (rows == 0) {
             if constexpr (TWO) {
@@ -416,11 +417,10 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 auto rows_of_pairs = [&](auto fast_tile, auto gray_known) {
                     constexpr bool FAST = decltype(fast_tile)::value;
                     constexpr int G = decltype(gray_known)::value;
-#pragma unroll
-                    for (int r = 0; r < ROWS_PER_WARP; ++r) {
+                    // sample row r of the strip
+                    auto sample = [&](int r, Pair (&smp)[C]) {
                         // no early exit: a row past the image's last row is computed on the last row's geometry
                         // (the descriptor's row terms are clamped)
-                        const bool row_ok = FAST || y_first + r < k.oh;
                         const int tr = warp * ROWS_PER_WARP + r;           // row within the tile
                         float2 sx, sy;
                         if (MODE == 0) {
@@ -431,10 +431,32 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                             sx = src_coord2_rows<CoordRecipe<MODE, F>::x>(xc, g2.a, g2.b, yc, bcast(ti->row_b[tr]), g2.c, g2.half_w, k2.neg_half);
                             sy = src_coord2_rows<CoordRecipe<MODE, F>::y>(xc, g2.d, g2.e, yc, bcast(ti->row_e[tr]), g2.f, g2.half_h, k2.neg_half);
                         }
-                        Pair smp[C];
                         if (FAST || window) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                         else                Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                        if constexpr (!REDUCE) finish_pair_x<C, F, G>(k, col, smp, plane, r, row_bytes, FAST || whole, row_ok, FAST || pair_ok);
+                    };
+                    if constexpr (FAST && !REDUCE && MODE != 2) {
+                        // Whole tiles, one texel per pixel: all samples first, then the stage goes back to the
+                        // producer - its next copies travel while this warp runs the colour tier and the
+                        // stores, which touch neither the stage nor the descriptor (512 x 3 x 512^2 -> 448^2
+                        // nearest 240 -> 230 us; bilinear: no gain).  FAST means that the tile has all its 64
+                        // columns, so all 32 lanes are here, as __syncwarp() requires.
+                        Pair smp[ROWS_PER_WARP][C];
+#pragma unroll
+                        for (int r = 0; r < ROWS_PER_WARP; ++r) sample(r, smp[r]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&empty[s]);
+                        released = true;
+#pragma unroll
+                        for (int r = 0; r < ROWS_PER_WARP; ++r)
+                            finish_pair_x<C, F, G>(k, col, smp[r], plane, r, row_bytes, true, true, true);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < ROWS_PER_WARP; ++r) {
+                            const bool row_ok = FAST || y_first + r < k.oh;
+                            Pair smp[C];
+                            sample(r, smp);
+                            if constexpr (!REDUCE) finish_pair_x<C, F, G>(k, col, smp, plane, r, row_bytes, FAST || whole, row_ok, FAST || pair_ok);
+                        }
                     }
                 };
                 // (the whole-tile copy twice more where grayscale is compiled in: the image's flag is then
@@ -452,14 +474,11 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 // table choice is made once per tile instead of once per pair.
                 auto row_pairs = [&](auto inside_rows, auto use_window) {
                     constexpr bool INSIDE = decltype(inside_rows)::value, WINDOW = decltype(use_window)::value;
-#pragma unroll
-                    for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
+                    // sample pair pr of the strip (rows 2 pr and 2 pr + 1)
+                    auto sample = [&](int pr, Pair (&smp)[C]) {
                         // No early exit: rows past the image's last row are computed on the last row's
-                        // geometry (always staged) and only their stores are dropped, so the pairs stay
-                        // independent and their instructions can interleave.
-                        const int y_raw = y_first + 2 * pr;
-                        const bool a_ok = INSIDE || y_raw < k.oh, b_ok = INSIDE || y_raw + 1 < k.oh;
-                        // the rows' coordinate terms from the descriptor (clamped to the image's last row there)
+                        // geometry (always staged; the descriptor's row terms are clamped) and only their
+                        // stores are dropped, so the pairs stay independent and their instructions can interleave.
                         const int tr = wy * ROWS_PER_WARP + 2 * pr;          // first row of the pair within the tile
                         const float2 yc = *reinterpret_cast<const float2 *>(&ti->row_y[tr]);
                         float2 sx, sy;
@@ -480,26 +499,50 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                             }
                             if constexpr (MIX) {                  // see late_x()
                                 const float2 alt = src_coord2_rows<1>(xc, g2.a, g2.b, yc, byc, g2.c, g2.half_w, k2.neg_half);
+                                const int y_raw = y_first + 2 * pr;
                                 const int ya = INSIDE ? y_raw : min(y_raw, k.oh - 1), yb = INSIDE ? y_raw + 1 : min(y_raw + 1, k.oh - 1);
                                 const uint32_t base = k.lin_base + (uint32_t)n * oplane + (uint32_t)x;
                                 if (late_x(k, base + (uint32_t)(ya * k.ow))) sx.x = alt.x;
                                 if (late_x(k, base + (uint32_t)(yb * k.ow))) sx.y = alt.y;
                             }
                         }
-                        Pair smp[C];
                         if (WINDOW) Sampler::window(k2, stage_addr, kb, rows, row0, xs0, sx, sy, smp, n_viol);
                         else        Sampler::table(k2, stage, ti->rowoff, rows, row0, sx, sy, smp, n_viol);
-                        if constexpr (REDUCE || TWO) {
-                            if (reduce) {
-                                float pa[C], pb[C];
+                    };
+                    if constexpr (INSIDE && !REDUCE && !TWO && MODE != 2) {
+                        // Whole strips, one texel per pixel: all samples first, then the stage goes back to
+                        // the producer - its next copies travel while this warp runs the colour tier and
+                        // the stores, which touch neither the stage nor the descriptor (64 x 3 x 1280^2 ->
+                        // 1024^2 nearest 260 -> 256 us).  Not for bilinear sampling, where holding every
+                        // pair's blended texels until the release measured 1-2 % slower.  INSIDE means that
+                        // all 32 lanes are here (see the call), as __syncwarp() requires.
+                        Pair smp[ROWS_PER_WARP / 2][C];
 #pragma unroll
-                                for (int c = 0; c < C; ++c) { pa[c] = smp[c].x; pb[c] = smp[c].y; }
-                                if (a_ok) mean_acc += mean_term<C, F>(col, pa);
-                                if (b_ok) mean_acc += mean_term<C, F>(col, pb);
+                        for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) sample(pr, smp[pr]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&empty[s]);
+                        released = true;
+#pragma unroll
+                        for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) finish_pair<C, F>(k, col, smp[pr], plane, 2 * pr, row_bytes, true, true);
+                    } else {
+#pragma unroll
+                        for (int pr = 0; pr < ROWS_PER_WARP / 2; ++pr) {
+                            const int y_raw = y_first + 2 * pr;
+                            const bool a_ok = INSIDE || y_raw < k.oh, b_ok = INSIDE || y_raw + 1 < k.oh;
+                            Pair smp[C];
+                            sample(pr, smp);
+                            if constexpr (REDUCE || TWO) {
+                                if (reduce) {
+                                    float pa[C], pb[C];
+#pragma unroll
+                                    for (int c = 0; c < C; ++c) { pa[c] = smp[c].x; pb[c] = smp[c].y; }
+                                    if (a_ok) mean_acc += mean_term<C, F>(col, pa);
+                                    if (b_ok) mean_acc += mean_term<C, F>(col, pb);
+                                }
                             }
-                        }
-                        if constexpr (!REDUCE) {
-                            if (!reduce) finish_pair<C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
+                            if constexpr (!REDUCE) {
+                                if (!reduce) finish_pair<C, F>(k, col, smp, plane, 2 * pr, row_bytes, a_ok, b_ok);
+                            }
                         }
                     }
                 };
@@ -507,8 +550,9 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 using no = std::false_type;
                 // (testing the grayscale flag once per tile, as the half-pixel path does, measured no
                 // gain here: bilinear 298 -> 297 us, fastest block 275 -> 278 us)
+                // (whole strip: all its rows above the image's last row and all 32 columns inside)
                 if (!window) row_pairs(no{}, no{});
-                else if (y_first + ROWS_PER_WARP <= k.oh) row_pairs(yes{}, yes{});
+                else if (y_first + ROWS_PER_WARP <= k.oh && h0.y + wx * 32 + 32 <= k.ow) row_pairs(yes{}, yes{});
                 else row_pairs(no{}, yes{});
             }
         }
@@ -538,7 +582,7 @@ __device__ __forceinline__ void affine_consumer(const KArgs &k, unsigned char *s
                 }
             }
         }
-        if (lane == 0) mbar_arrive(&empty[s]);
+        if (lane == 0 && !released) mbar_arrive(&empty[s]);
         if (TWO && threadIdx.x == 0) *(volatile unsigned *)&two_phase_checkin[4] += 1u;     // heartbeat for the finisher
         if (++s == STAGES) { s = 0; phase ^= 1u; }
         if (++slot == INFO_SLOTS) slot = 0;
