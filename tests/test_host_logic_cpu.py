@@ -183,6 +183,14 @@ def test_library_exports_every_declared_symbol():
     assert ctypes.sizeof(_lib.SampleSpec) == 272 and _lib.SampleSpec.torch_compat.offset == 216     # the older layout ends at 216        # sizeof(ta_b200_sample_spec) on LP64
 
 
+def test_diagnostic_switches_refuse_values_they_do_not_know():
+    """The process-wide switches touch no device, so their argument checks run on any host."""
+    for call, bad in ((_lib.tile_height, 48), (_lib.crop_path, 3), (_lib.host_upload, 5)):
+        with pytest.raises(_lib.LibraryError):
+            call(bad)
+        call(0 if call is not _lib.host_upload else 1)          # back to the default
+
+
 def test_a_failing_shard_does_not_stop_the_others():
     """ShardedAugment runs every shard even when one raises and reports the failure per shard
     (host logic only: the 'devices' are the CPU and the transform's kernel call is a stand-in)."""
