@@ -362,9 +362,9 @@ int ta_b200_mean_path(int32_t one_launch);
  * allow it.  Both produce identical output; the switch exists so that tests can compare them. */
 int ta_b200_debug_crop_path(int32_t path);
 /* Tile height of the staged kernel for float32 and float16 images, process-wide: 0 = chosen by
- * the output height (default: 64 rows; 32 rows with a deeper ring for outputs of at most 256 rows
- * (float32) or 96 rows (float16) whose last row of 64-row tiles would be at most half full),
- * 32 / 64 = that height for every call.  Identical output; the switch exists so that tests can
+ * the call (default: 64 rows; 32 rows with a deeper ring for outputs of at most 256 rows
+ * (float32) or 96 rows (float16) whose last row of 64-row tiles would be at most half full, and for
+ * every float32 call without a matrix), 32 / 64 = that height for every call.  Identical output; the switch exists so that tests can
  * compare the shapes. */
 int ta_b200_debug_tile_height(int32_t rows);
 /* ta_b200_fused_augment_host(): 1 = upload only the box of each large image that the call reads

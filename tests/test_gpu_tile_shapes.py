@@ -101,12 +101,13 @@ def test_shape_is_chosen_by_output_height(tile_height):
         _launch(case, oh, 128, False, 31)
         staged, direct, _, _ = _lib.debug_counters()
         assert staged + direct == 2 * 2 * -(-oh // rows), (oh, rows, staged, direct)
-    # matrix-free calls through the staged kernel follow the same rule
+    # float32 calls without a matrix that go through the staged kernel always take the short shape
     _lib.crop_path(2)
     try:
-        case = _case(2, 3, 232, 136, 224, 128, seed=1)
-        _lib.debug_counters(reset=True)
-        _launch(case, 224, 128, False, 31, matrix=False)
-        assert sum(_lib.debug_counters()[:2]) == 2 * 2 * 7
+        for oh in (224, 320):
+            case = _case(2, 3, oh + 8, 136, oh, 128, seed=1)
+            _lib.debug_counters(reset=True)
+            _launch(case, oh, 128, False, 31, matrix=False)
+            assert sum(_lib.debug_counters()[:2]) == 2 * 2 * (oh // 32)
     finally:
         _lib.crop_path(0)

@@ -339,13 +339,17 @@ static int launch_fused(const ta_b200_fused_params *p, cudaStream_t stream, bool
     // tiles with a deeper ring: with few tiles per image the number of tiles in flight matters more
     // than the pixels per thread (ta_affine.cuh).  Measured limits: float images up to 256 output
     // rows (224: 224 against 236 us per 1024 images; 288: 369 against 357), half images up to 96
-    // (96: 164 / 222 against 169 / 250 us per 4096 images; 224: 189 against 167).  Same arithmetic
-    // per pixel, hence the same output.
+    // (96: 164 / 222 against 169 / 250 us per 4096 images; 224: 189 against 167).  Float images
+    // without a matrix always do: their consumers have so little to do per pixel that the ring is
+    // what matters (160 x 3 x 704^2 -> 640^2: 252 against 290 us on two GPUs; 80 x 3 x 1024^2 -> 896^2:
+    // 246 against 283 us on one GPU, 252 against 246 us on another; 64 x 3 x 1280^2 -> 1024^2: 261
+    // against 258 us: never more than 2.5 % behind, up to 15 % ahead).  Same arithmetic per pixel,
+    // hence the same output.
     const int last_rows = p->oh % kTileH, forced = g_tile_height.load(std::memory_order_relaxed);
     const bool has_short = p->dtype == TA_B200_F32 || p->dtype == TA_B200_F16;
+    const bool small = last_rows != 0 && last_rows <= kTileHShort && p->oh <= (p->dtype == TA_B200_F32 ? 256 : 96);
     const bool short_tiles = kind != 0 && has_short &&
-                             (forced ? forced == kTileHShort
-                                     : last_rows != 0 && last_rows <= kTileHShort && p->oh <= (p->dtype == TA_B200_F32 ? 256 : 96));
+                             (forced ? forced == kTileHShort : small || (kind == 3 && p->dtype == TA_B200_F32));
     const int tile_h = short_tiles ? kTileHShort : kTileH;
     const KernelTable &tab = table_for(kind, p->dtype, short_tiles);
     unsigned slot = f;
